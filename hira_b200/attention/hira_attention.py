@@ -1,0 +1,114 @@
+"""hira_attention: range-searching sparse attention for decode, in the shape of a
+Hugging Face attention function (see AttentionInterface in transformers.modeling_utils;
+the reference ships only that pointer, attention/hira_attention.py:1-3, and the hook in
+examples/patch_llama.py:59-74).
+
+`key` is what `HiraCache.update` returned: a `CacheOutput`.  Prefill (`prefill_keys`
+present) attends densely over the prompt; a decode step
+  1. normalises the query (the tree bound assumes a unit query, searcher/cpu.py:61-63)
+     and folds its norm and the softmax scale into the per-head `scaling`,
+  2. finds a threshold on the device (THRESHOLD_METHODS) unless one is given,
+  3. searches the index for the keys with `q.k >= threshold`,
+  4. runs softmax over those keys plus the not-yet-indexed queue and multiplies by the
+     slot-aligned values.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import _lib as L
+from .. import index_state as S
+from ..cache.threshold_finder import THRESHOLD_METHODS
+from ..searcher import CUDASearcher
+
+
+def _samples_for(indexer, sample_size: int) -> torch.Tensor:
+    """(H_kv, S, D) key rows drawn once per built index from its filled slots."""
+    st = indexer.state
+    cached = getattr(indexer, "_tau_samples", None)
+    if cached is not None and cached[0] is st and cached[1].shape[1] == min(sample_size, 4096):
+        return cached[1]
+    s = min(sample_size, 4096)
+    g = torch.Generator(device=st.device)
+    g.manual_seed(getattr(indexer, "seed", 0) + 17)
+    filled = st.slot2token >= 0                                   # (H, capC)
+    # random filled slots per head: top-s of random scores masked to filled slots
+    r = torch.rand(filled.shape, generator=g, device=st.device).masked_fill_(~filled, -1.0)
+    n_filled = int(filled.sum(dim=1).min().item())
+    s = max(1, min(s, n_filled))
+    slots = r.topk(s, dim=1).indices                              # (H, s)
+    rows = st.children.gather(1, slots.unsqueeze(-1).expand(-1, -1, st.dim)).contiguous()
+    indexer._tau_samples = (st, rows)
+    return rows
+
+
+def _attn_searcher(searcher, gate: str) -> CUDASearcher:
+    s = getattr(searcher, "_attn_searcher", None)
+    if s is None:
+        s = CUDASearcher(getattr(searcher, "block_c", None), gate=gate, leaf=gate)
+        try:
+            searcher._attn_searcher = s
+        except AttributeError:
+            pass
+    return s
+
+
+def hira_decode_attention(query: torch.Tensor, cache_output, *, scaling: Optional[float] = None,
+                          threshold: Optional[torch.Tensor] = None, threshold_method: str = "sample_mean_topk",
+                          sample_size: int = 1000, topk: int = 16, gate: str = "ge",
+                          q_head_to_kv: Optional[torch.Tensor] = None, return_compact: bool = False):
+    """query (B, H_q, 1, D) -> (B, H_q, 1, V) float32.  `threshold` (B*H_q,) is on the scale of
+    `q_hat . k` with `q_hat = q / ||q||`."""
+    indexer, searcher = cache_output.indexer, cache_output.searcher
+    st: S.IndexState = indexer.state
+    b, hq, lq, d = query.shape
+    if lq != 1:
+        raise NotImplementedError("hira_decode_attention handles one query token per step")
+    q = query.reshape(b * hq, d).to(device=st.device, dtype=torch.float32)
+    qn = q.norm(dim=-1).clamp_min(1e-20)
+    q_hat = (q / qn[:, None]).contiguous()
+    sm_scale = float(scaling) if scaling is not None else d ** -0.5
+    logit_scale = (qn * sm_scale).contiguous()
+    if threshold is None:
+        samples = _samples_for(indexer, sample_size)
+        fn = THRESHOLD_METHODS[threshold_method]
+        if threshold_method == "sample_max":
+            threshold = fn(samples, q_hat, q_head_to_kv)
+        else:
+            threshold = fn(samples, q_hat, min(topk, samples.shape[1]), q_head_to_kv)
+    srch = _attn_searcher(searcher, gate)
+    compact = srch.search_compact(q_hat, threshold, indexer, q_head_to_kv=q_head_to_kv, scaling=logit_scale)
+    qk = cache_output.queued_keys
+    queued_k = queued_v = None
+    if qk is not None and qk.shape[-2] > 0:
+        queued_k = qk.reshape(-1, qk.shape[-2], qk.shape[-1]).to(st.dtype).contiguous()
+        qv = cache_output.queued_values
+        queued_v = qv.reshape(-1, qv.shape[-2], qv.shape[-1]).to(st.vdtype).contiguous()
+    q2kv, _ = srch._coerce_q2kv(q_head_to_kv, b * hq, st.n_heads, st.device)
+    out = S.sparse_attn(st, q_hat, logit_scale, compact, q2kv=q2kv, queued_k=queued_k, queued_v=queued_v)
+    out = out.reshape(b, hq, 1, st.vdim)
+    return (out, compact) if return_compact else out
+
+
+def hira_attention(module, query: torch.Tensor, key, value=None, attention_mask: Optional[torch.Tensor] = None,
+                   dropout: float = 0.0, scaling: Optional[float] = None, **kwargs):
+    """Hugging Face attention-function signature.  Returns (attn_output (B, L_q, H_q, V), None)."""
+    from ..cache.hira_cache import CacheOutput
+    if not isinstance(key, CacheOutput):
+        raise TypeError("hira_attention expects the CacheOutput returned by HiraCache.update as `key`")
+    if key.prefill_keys is not None:
+        k, v = key.prefill_keys, key.prefill_values
+        is_causal = attention_mask is None and query.shape[2] > 1
+        out = torch.nn.functional.scaled_dot_product_attention(
+            query, k, v, attn_mask=attention_mask, dropout_p=0.0, is_causal=is_causal, scale=scaling,
+            enable_gqa=query.shape[1] != k.shape[1])
+        return out.transpose(1, 2).contiguous(), None
+    cfg = kwargs.get("hira_config")
+    opts = {}
+    if cfg is not None:
+        opts = dict(threshold_method=cfg.threshold_method, sample_size=cfg.sample_size,
+                    topk=getattr(cfg, "topk", 16), gate=getattr(cfg, "gate", "ge"))
+    out = hira_decode_attention(query, key, scaling=scaling, threshold=kwargs.get("threshold"), **opts)
+    return out.to(query.dtype).transpose(1, 2).contiguous(), None

@@ -1,0 +1,288 @@
+// Decode-time key insertion: nearest valid parent, slot claim, K/V row write,
+// radius widening up the path, overflow into pre-allocated spare blocks.
+//
+// Follows CUDAIndexer.update (indexer/cuda.py:544-701, 1200-1231) and its
+// Triton kernels (kernels/triton_update_kernels.py:6-364):
+//   score(p) = ||c_p||^2 - 2 x.c_p over valid parents, arg-min, ties -> lowest p
+//   free slot  -> children[p*bf + count] = x, count += 1,
+//                 r_p = max(r_p, ||x - c_p||), r_g = max(r_g, ||c_p - c_g|| + r_p)
+//   parent full -> x becomes a new parent (centre x, radius 0, one child); with
+//                 three levels it goes under the nearest grandparent if that has
+//                 a free parent slot, else under a new grandparent (centre x).
+// Differences by design: counts, validity and ||c||^2 are persistent device
+// state (the reference recomputes them by scanning the whole index after every
+// call, indexer/cuda.py:1233-1298), the arrays are pre-allocated (no torch.cat
+// growth, :644-657) and nothing synchronises with the host.  One CTA owns one
+// head and inserts its keys one after another, so results are deterministic.
+#include "common.cuh"
+#include <math_constants.h>
+
+namespace hira {
+
+constexpr int APPEND_THREADS = 512;
+constexpr int APPEND_HW = APPEND_THREADS / 16;
+constexpr int APPEND_UNROLL = 4;
+
+struct AppendParams {
+    hira_index_t ix;
+    const void* new_k;
+    const void* new_v;
+    int n_new;
+    long long k_head_stride, v_head_stride;
+    int token_base;
+    int32_t* status;
+};
+
+struct Best { float s; int i; };
+
+__device__ __forceinline__ bool better(float s, int i, const Best& b) {
+    return s < b.s || (s == b.s && i < b.i);
+}
+
+// arg-min of sq[p] - 2 x.c_p over p in [0, n) with valid(p); all threads get it
+template <typename T, int NCH, typename Valid>
+__device__ Best nearest_row(const T* rows, const float* sq, int n, const float (&x)[NCH][8], int dim,
+                            Valid valid, Best* s_best) {
+    const int tid = threadIdx.x, lane = tid & 15, hw = tid >> 4;
+    Best best{CUDART_INF_F, 0x7fffffff};
+    for (int p0 = 0; p0 < n; p0 += APPEND_HW * APPEND_UNROLL) {  // uniform trip count
+        RawChunk<T> raw[APPEND_UNROLL][NCH];
+        bool ok[APPEND_UNROLL];
+#pragma unroll
+        for (int u = 0; u < APPEND_UNROLL; ++u) {
+            const int p = p0 + u * APPEND_HW + hw;
+            ok[u] = p < n && valid(p);
+#pragma unroll
+            for (int i = 0; i < NCH; ++i) {
+                const int c = lane + 16 * i;
+                if (ok[u] && c * 8 < dim) raw[u][i] = load_chunk_coherent<T>(rows + (size_t)p * dim, c);
+                else raw[u][i] = zero_chunk<T>();
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < APPEND_UNROLL; ++u) {
+            const int p = p0 + u * APPEND_HW + hw;
+            Acc2 acc{0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < NCH; ++i) {
+                float a[8];
+                to_float(raw[u][i], a);
+                chunk_fma(acc, a, x[i]);
+            }
+            const float d = halfwarp_sum(__fadd_rn(acc.e, acc.o));
+            if (ok[u]) {
+                const float s = __fsub_rn(sq[p], __fmul_rn(2.0f, d));
+                if (better(s, p, best)) best = Best{s, p};
+            }
+        }
+    }
+    __syncthreads();
+    if (lane == 0) s_best[hw] = best;
+    __syncthreads();
+    Best b = s_best[0];
+    for (int w = 1; w < APPEND_HW; ++w)
+        if (better(s_best[w].s, s_best[w].i, b)) b = s_best[w];
+    __syncthreads();
+    return b;
+}
+
+template <typename T, typename TV, int NCH, int NVCH>
+__global__ void __launch_bounds__(APPEND_THREADS)
+append_kernel(const AppendParams P) {
+    __shared__ Best s_best[APPEND_HW];
+    const hira_index_t& ix = P.ix;
+    const int h = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 15, hw = tid >> 4;
+    const int bf = ix.bf, dim = ix.dim, vdim = ix.vdim;
+    const size_t capP = ix.cap_parents, capC = capP * bf, capG = ix.cap_gp;
+    T* children = reinterpret_cast<T*>(ix.children) + (size_t)h * capC * dim;
+    T* parents = reinterpret_cast<T*>(ix.parents) + (size_t)h * capP * dim;
+    T* gps = ix.depth == 3 ? reinterpret_cast<T*>(ix.grand_parents) + (size_t)h * capG * dim : nullptr;
+    TV* values = ix.values ? reinterpret_cast<TV*>(ix.values) + (size_t)h * capC * vdim : nullptr;
+    float* pr = ix.parent_radii + (size_t)h * capP;
+    float* psq = ix.parent_sqnorm + (size_t)h * capP;
+    int32_t* cc = ix.child_counts + (size_t)h * capP;
+    float* gr = ix.depth == 3 ? ix.gp_radii + (size_t)h * capG : nullptr;
+    float* gsq = ix.depth == 3 ? ix.gp_sqnorm + (size_t)h * capG : nullptr;
+    int32_t* gc = ix.depth == 3 ? ix.gp_counts + (size_t)h * capG : nullptr;
+    int32_t* used = ix.used + (size_t)h * 4;
+    int32_t* s2t = ix.slot2token ? ix.slot2token + (size_t)h * capC : nullptr;
+    const T* new_k = reinterpret_cast<const T*>(P.new_k) + (size_t)h * P.k_head_stride;
+    const TV* new_v = P.new_v ? reinterpret_cast<const TV*>(P.new_v) + (size_t)h * P.v_head_stride : nullptr;
+
+    for (int key = 0; key < P.n_new; ++key) {
+        // every thread reads the state written by thread 0 in the previous round
+        int used_p = used[0];
+        int used_g = used[1];
+        const int n_keys = used[2];
+        float x[NCH][8];
+        load_vec<T, NCH>(new_k + (size_t)key * dim, x, lane, dim);
+
+        // ---- nearest valid parent ---------------------------------------------
+        Best bp;
+        if (ix.depth == 3) {
+            const int n_scan = used_g * bf;
+            bp = nearest_row<T, NCH>(parents, psq, n_scan, x, dim,
+                                     [&](int p) { return (p % bf) < gc[p / bf]; }, s_best);
+        } else {
+            bp = nearest_row<T, NCH>(parents, psq, used_p, x, dim, [&](int) { return true; }, s_best);
+        }
+        const bool have_parent = bp.i != 0x7fffffff;
+        const bool placed = have_parent && cc[bp.i] < bf;
+
+        int p_dst = -1, g_dst = -1;
+        bool new_gp = false;
+        if (!placed) {
+            if (ix.depth == 3) {
+                // nearest grandparent among those in use (no validity mask: indexer/cuda.py:918-920)
+                const Best bg = nearest_row<T, NCH>(gps, gsq, used_g, x, dim, [&](int) { return true; }, s_best);
+                if (bg.i != 0x7fffffff && gc[bg.i] < bf) {
+                    g_dst = bg.i;
+                    p_dst = g_dst * bf + gc[g_dst];
+                } else if (used_g < (int)capG) {
+                    g_dst = used_g;
+                    p_dst = g_dst * bf;
+                    new_gp = true;
+                } else {
+                    if (tid == 0) atomicOr(P.status, HIRA_STATUS_GP_FULL);
+                }
+            } else {
+                if (used_p < (int)capP) p_dst = used_p;
+                else if (tid == 0) atomicOr(P.status, HIRA_STATUS_PARENTS_FULL);
+            }
+        }
+        __syncthreads();  // all reads of the old state are done
+
+        // ---- warp 0 applies the insertion ---------------------------------------
+        if (tid < 32) {
+            const int token = P.token_base < 0 ? n_keys : P.token_base + key;
+            if (placed) {
+                const int p = bp.i;
+                const int slot = p * bf + cc[p];
+                const float d2 = row_dist2_reg<T, NCH>(parents + (size_t)p * dim, x, lane, dim);
+                const float r_new = fmaxf(pr[p], __fsqrt_rn(d2));
+                float rg_new = 0.f;
+                if (ix.depth == 3) {
+                    const int g = p / bf;
+                    const float dg2 = row_dist2_coherent<T, T, NCH>(parents + (size_t)p * dim, gps + (size_t)g * dim, lane, dim);
+                    rg_new = fmaxf(gr[g], __fadd_rn(__fsqrt_rn(dg2), r_new));
+                }
+                if (hw == 0) {
+#pragma unroll
+                    for (int i = 0; i < NCH; ++i) {
+                        const int c = lane + 16 * i;
+                        if (c * 8 < dim) store_chunk(children + (size_t)slot * dim, c, x[i]);
+                    }
+                    if (values) {
+#pragma unroll
+                        for (int i = 0; i < NVCH; ++i) {
+                            const int c = lane + 16 * i;
+                            if (c * 8 < vdim) {
+                                float v[8];
+                                to_float(load_chunk<TV>(new_v + (size_t)key * vdim, c), v);
+                                store_chunk(values + (size_t)slot * vdim, c, v);
+                            }
+                        }
+                    }
+                    if (lane == 0) {
+                        pr[p] = r_new;
+                        if (ix.depth == 3) gr[p / bf] = rg_new;
+                        cc[p] += 1;
+                        used[2] = n_keys + 1;
+                        if (s2t) s2t[slot] = token;
+                    }
+                }
+            } else if (p_dst >= 0) {
+                const int slot = p_dst * bf;
+                const float xsq = reg_sqnorm<NCH>(x);
+                float rg_new = 0.f;
+                if (ix.depth == 3 && !new_gp) {
+                    const float dg2 = row_dist2_reg<T, NCH>(gps + (size_t)g_dst * dim, x, lane, dim);
+                    rg_new = fmaxf(gr[g_dst], __fsqrt_rn(dg2));  // ||x - g|| + radius 0
+                }
+                if (hw == 0) {
+#pragma unroll
+                    for (int i = 0; i < NCH; ++i) {
+                        const int c = lane + 16 * i;
+                        if (c * 8 < dim) {
+                            store_chunk(children + (size_t)slot * dim, c, x[i]);
+                            store_chunk(parents + (size_t)p_dst * dim, c, x[i]);
+                            if (new_gp) store_chunk(gps + (size_t)g_dst * dim, c, x[i]);
+                        }
+                    }
+                    if (values) {
+#pragma unroll
+                        for (int i = 0; i < NVCH; ++i) {
+                            const int c = lane + 16 * i;
+                            if (c * 8 < vdim) {
+                                float v[8];
+                                to_float(load_chunk<TV>(new_v + (size_t)key * vdim, c), v);
+                                store_chunk(values + (size_t)slot * vdim, c, v);
+                            }
+                        }
+                    }
+                    if (lane == 0) {
+                        pr[p_dst] = 0.f;
+                        psq[p_dst] = xsq;
+                        cc[p_dst] = 1;
+                        if (ix.depth == 3) {
+                            if (new_gp) {
+                                gr[g_dst] = 0.f;
+                                gsq[g_dst] = xsq;
+                                gc[g_dst] = 1;
+                                used[1] = used_g + 1;
+                            } else {
+                                gr[g_dst] = rg_new;
+                                gc[g_dst] += 1;
+                            }
+                        }
+                        if (p_dst + 1 > used_p) used[0] = p_dst + 1;
+                        used[2] = n_keys + 1;
+                        if (s2t) s2t[slot] = token;
+                    }
+                }
+            }
+        }
+        __syncthreads();  // make the insertion visible to the next key's scan
+    }
+}
+
+template <typename T, typename TV>
+static int launch_append(const AppendParams& P, cudaStream_t s) {
+    const bool k2 = P.ix.dim > 128, v2 = P.ix.vdim > 128;
+    const int grid = P.ix.n_heads;
+    if (!k2 && !v2) append_kernel<T, TV, 1, 1><<<grid, APPEND_THREADS, 0, s>>>(P);
+    else if (k2 && !v2) append_kernel<T, TV, 2, 1><<<grid, APPEND_THREADS, 0, s>>>(P);
+    else if (!k2 && v2) append_kernel<T, TV, 1, 2><<<grid, APPEND_THREADS, 0, s>>>(P);
+    else append_kernel<T, TV, 2, 2><<<grid, APPEND_THREADS, 0, s>>>(P);
+    HIRA_CHECK_LAUNCH("hira_append launch");
+    return HIRA_OK;
+}
+
+}  // namespace hira
+
+using namespace hira;
+
+extern "C" int hira_append(const hira_index_t* ix, const void* new_k, const void* new_v, int32_t n_new,
+                           int64_t k_head_stride, int64_t v_head_stride, int32_t token_base,
+                           int32_t* status, void* stream) {
+    int rc = validate_index(ix, false);
+    if (rc != HIRA_OK) return rc;
+    HIRA_CHECK_ARG(new_k && status, HIRA_ERR_ARG, "hira_append: new_k and status must not be NULL");
+    HIRA_CHECK_ARG(n_new >= 0, HIRA_ERR_SHAPE, "hira_append: n_new=%d", n_new);
+    HIRA_CHECK_ARG((ix->values == nullptr) == (new_v == nullptr), HIRA_ERR_ARG,
+                   "hira_append: values must be given iff the index stores values");
+    HIRA_CHECK_ARG(ix->parent_sqnorm && (ix->depth == 2 || ix->gp_sqnorm), HIRA_ERR_ARG,
+                   "hira_append: the index needs its parent_sqnorm / gp_sqnorm caches");
+    if (n_new == 0) return HIRA_OK;
+    AppendParams P;
+    P.ix = *ix; P.new_k = new_k; P.new_v = new_v; P.n_new = n_new;
+    P.k_head_stride = k_head_stride; P.v_head_stride = v_head_stride;
+    P.token_base = token_base; P.status = status;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const bool kb = ix->dtype == HIRA_BF16, vb = ix->vdtype == HIRA_BF16 || !ix->values;
+    if (kb && vb) return launch_append<__nv_bfloat16, __nv_bfloat16>(P, s);
+    if (kb && !vb) return launch_append<__nv_bfloat16, float>(P, s);
+    if (!kb && vb && ix->values) return launch_append<float, __nv_bfloat16>(P, s);
+    return launch_append<float, float>(P, s);
+}

@@ -1,0 +1,336 @@
+// Gather-sparse flash-decode attention over the compacted search output, plus
+// the log-sum-exp merge used for split-KV partials and for sequence shards.
+//
+// The reference names this step (attention/hira_attention.py:1-3) but ships no
+// implementation; the contract here follows its searcher API: emitted scores
+// already are the logits (scaling * q.k, searcher/cpu.py:58-63), the value rows
+// sit in the same slots as the keys (indexer/cuda.py:397-423), and the keys not
+// yet indexed arrive as a dense queue (cache/hira_cache.py:121-140).
+//
+// One CTA per (query head, split of the tile range).  16-lane groups each
+// gather one value row (256 B for V=128 bf16) with a 128-bit load per lane,
+// four rows in flight per thread; softmax is online in fp32.
+#include "common.cuh"
+#include <math_constants.h>
+
+namespace hira {
+
+constexpr int ATTN_THREADS = 256;
+constexpr int ATTN_HW = ATTN_THREADS / 16;
+constexpr int ATTN_CHUNK = 2048;  // list entries staged in shared memory (>= rows of one search tile)
+constexpr int ATTN_UNROLL = 4;
+constexpr int QUEUE_FLAG = 0x40000000;
+
+struct AttnParams {
+    const void* values;
+    const float* q;
+    const float* scaling;
+    const int32_t* q2kv;
+    const int32_t* idx;
+    const float* score;
+    const int32_t* count;
+    const void* queued_k;
+    const void* queued_v;
+    float* ws;
+    int n_heads, n_qheads, group, dim, vdim, n_tiles, tile_rows, n_splits, n_queued;
+    long long cap_children;
+    long long queued_head_stride;
+};
+
+template <typename TV, int NVCH>
+__device__ __forceinline__ void accumulate_row(float (&acc)[NVCH][8], const RawChunk<TV> (&raw)[NVCH], float p) {
+#pragma unroll
+    for (int i = 0; i < NVCH; ++i) {
+        float v[8];
+        to_float(raw[i], v);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[i][e] = __fmaf_rn(p, v[e], acc[i][e]);
+    }
+}
+
+template <typename TK, typename TV, int NCH, int NVCH>
+__global__ void __launch_bounds__(ATTN_THREADS)
+sparse_attn_kernel(const AttnParams P) {
+    __shared__ int s_idx[ATTN_CHUNK];
+    __shared__ float s_logit[ATTN_CHUNK];
+    __shared__ float s_red[ATTN_HW];
+    __shared__ float s_bcast;
+    extern __shared__ __align__(16) float s_out[];  // [ATTN_HW][vdim]
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 15;
+    const int hw = tid >> 4;
+    const int qh = blockIdx.y;
+    const int split = blockIdx.x;
+    const int h = P.q2kv ? P.q2kv[qh] : qh / P.group;
+    const TV* values = reinterpret_cast<const TV*>(P.values) + (size_t)h * P.cap_children * P.vdim;
+    const int t0 = (int)(((long long)split * P.n_tiles) / P.n_splits);
+    const int t1 = (int)(((long long)(split + 1) * P.n_tiles) / P.n_splits);
+
+    float m = -CUDART_INF_F;
+    float l = 0.f;  // this half-warp's share of the denominator
+    float acc[NVCH][8];
+#pragma unroll
+    for (int i = 0; i < NVCH; ++i)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
+
+    int fill = 0;
+
+    auto flush = [&]() {
+        __syncthreads();
+        // block max of the staged logits
+        float mx = -CUDART_INF_F;
+        for (int i = tid; i < fill; i += ATTN_THREADS) mx = fmaxf(mx, s_logit[i]);
+#pragma unroll
+        for (int s = 16; s >= 1; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
+        if ((tid & 31) == 0) s_red[tid >> 5] = mx;
+        __syncthreads();
+        if (tid == 0) {
+            float v = s_red[0];
+            for (int w = 1; w < ATTN_THREADS / 32; ++w) v = fmaxf(v, s_red[w]);
+            s_bcast = v;
+        }
+        __syncthreads();
+        const float new_m = fmaxf(m, s_bcast);
+        if (new_m > -CUDART_INF_F) {
+            const float alpha = (m > -CUDART_INF_F) ? __expf(m - new_m) : 0.f;
+            l *= alpha;
+#pragma unroll
+            for (int i = 0; i < NVCH; ++i)
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[i][e] *= alpha;
+            m = new_m;
+            for (int base = 0; base < fill; base += ATTN_HW * ATTN_UNROLL) {
+                RawChunk<TV> raw[ATTN_UNROLL][NVCH];
+                float p[ATTN_UNROLL];
+#pragma unroll
+                for (int u = 0; u < ATTN_UNROLL; ++u) {
+                    const int e = base + u * ATTN_HW + hw;
+                    p[u] = 0.f;
+                    const TV* row = nullptr;
+                    if (e < fill) {
+                        const int id = s_idx[e];
+                        p[u] = __expf(s_logit[e] - m);
+                        if (id & QUEUE_FLAG)
+                            row = reinterpret_cast<const TV*>(P.queued_v) + (size_t)h * P.queued_head_stride +
+                                  (size_t)(id & ~QUEUE_FLAG) * P.vdim;
+                        else
+                            row = values + (size_t)id * P.vdim;
+                    }
+#pragma unroll
+                    for (int i = 0; i < NVCH; ++i) {
+                        const int c = lane + 16 * i;
+                        if (row != nullptr && c * 8 < P.vdim) raw[u][i] = load_chunk_stream<TV>(row, c);
+                        else raw[u][i] = zero_chunk<TV>();
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < ATTN_UNROLL; ++u) {
+                    accumulate_row<TV, NVCH>(acc, raw[u], p[u]);
+                    l += p[u];
+                }
+            }
+        }
+        __syncthreads();
+        fill = 0;
+    };
+
+    // ---- emitted children of this split's tiles -------------------------------
+    for (int t = t0; t < t1; ++t) {
+        const int c = P.count[(size_t)qh * P.n_tiles + t];
+        if (c == 0) continue;
+        if (fill + c > ATTN_CHUNK) flush();
+        const size_t base = (size_t)qh * P.cap_children + (size_t)t * P.tile_rows;
+        for (int i = tid; i < c; i += ATTN_THREADS) {
+            s_idx[fill + i] = P.idx[base + i];
+            s_logit[fill + i] = P.score[base + i];
+        }
+        fill += c;
+    }
+
+    // ---- queued (not yet indexed) keys: split 0 only ---------------------------
+    if (split == 0 && P.n_queued > 0) {
+        float qreg[NCH][8];
+        load_vec_f32<NCH>(P.q + (size_t)qh * P.dim, qreg, lane, P.dim);
+        const float scale = P.scaling ? P.scaling[qh] : 1.0f;
+        const TK* qk = reinterpret_cast<const TK*>(P.queued_k) + (size_t)h * P.queued_head_stride;
+        int j0 = 0;
+        while (j0 < P.n_queued) {
+            if (fill == ATTN_CHUNK) flush();
+            const int n = min(P.n_queued - j0, ATTN_CHUNK - fill);
+            for (int b = 0; b < n; b += ATTN_HW) {  // uniform trip count: shuffles inside
+                const int j = b + hw;
+                float d = 0.f;
+                {
+                    Acc2 a2{0.f, 0.f};
+                    if (j < n) {
+#pragma unroll
+                        for (int i = 0; i < NCH; ++i) {
+                            const int c = lane + 16 * i;
+                            if (c * 8 < P.dim) {
+                                float a[8];
+                                to_float(load_chunk<TK>(qk + (size_t)(j0 + j) * P.dim, c), a);
+                                chunk_fma(a2, a, qreg[i]);
+                            }
+                        }
+                    }
+                    d = halfwarp_sum(__fadd_rn(a2.e, a2.o));
+                }
+                if (lane == 0 && j < n) {
+                    s_idx[fill + j] = QUEUE_FLAG | (j0 + j);
+                    s_logit[fill + j] = __fmul_rn(d, scale);
+                }
+            }
+            fill += n;
+            j0 += n;
+        }
+    }
+    if (fill > 0) flush();
+
+    // ---- combine the half-warps ------------------------------------------------
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < NVCH; ++i) {
+        const int c = lane + 16 * i;
+        if (c * 8 < P.vdim) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) s_out[(size_t)hw * P.vdim + c * 8 + e] = acc[i][e];
+        }
+    }
+    if (lane == 0) s_red[hw] = l;
+    __syncthreads();
+    float* ws = P.ws + ((size_t)qh * P.n_splits + split) * (P.vdim + 2);
+    for (int d = tid; d < P.vdim; d += ATTN_THREADS) {
+        float s = 0.f;
+        for (int w = 0; w < ATTN_HW; ++w) s += s_out[(size_t)w * P.vdim + d];
+        ws[2 + d] = s;
+    }
+    if (tid == 0) {
+        float s = 0.f;
+        for (int w = 0; w < ATTN_HW; ++w) s += s_red[w];
+        ws[0] = m;
+        ws[1] = s;
+    }
+}
+
+// out = sum_s w_s * o_s / sum_s w_s * (normalised ? 1 : l_s-free) ... see below.
+// Partials are (m_s, l_s, o_s).  With unnormalised o_s (split-KV workspace):
+//   out = sum_s e^{m_s-M} o_s / sum_s e^{m_s-M} l_s.
+// With normalised o_s (sequence shards): o_s is first scaled back by l_s.
+__global__ void merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                             long long o_part_stride, long long o_head_stride,
+                             long long ml_part_stride, long long ml_head_stride,
+                             int n_parts, int vdim, int normalised, float* __restrict__ out,
+                             float* __restrict__ out_ml) {
+    const int qh = blockIdx.x;
+    float M = -CUDART_INF_F;
+    for (int s = 0; s < n_parts; ++s)
+        M = fmaxf(M, part_ml[s * ml_part_stride + qh * ml_head_stride]);
+    float L = 0.f;
+    for (int s = 0; s < n_parts; ++s) {
+        const float ms = part_ml[s * ml_part_stride + qh * ml_head_stride];
+        const float ls = part_ml[s * ml_part_stride + qh * ml_head_stride + 1];
+        if (ms > -CUDART_INF_F) L += ls * __expf(ms - M);
+    }
+    for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
+        float o = 0.f;
+        for (int s = 0; s < n_parts; ++s) {
+            const float ms = part_ml[s * ml_part_stride + qh * ml_head_stride];
+            if (ms > -CUDART_INF_F) {
+                float w = __expf(ms - M);
+                if (normalised) w *= part_ml[s * ml_part_stride + qh * ml_head_stride + 1];
+                o += w * part_o[s * o_part_stride + qh * o_head_stride + d];
+            }
+        }
+        out[(size_t)qh * vdim + d] = L > 0.f ? o / L : 0.f;
+    }
+    if (out_ml && threadIdx.x == 0) {
+        out_ml[2 * qh] = M;
+        out_ml[2 * qh + 1] = L;
+    }
+}
+
+template <typename TK, typename TV>
+static int launch_attn(const AttnParams& P, cudaStream_t s) {
+    dim3 grid((unsigned)P.n_splits, (unsigned)P.n_qheads);
+    const size_t smem = (size_t)ATTN_HW * P.vdim * sizeof(float);
+    const bool k2 = P.dim > 128, v2 = P.vdim > 128;
+    if (!k2 && !v2) sparse_attn_kernel<TK, TV, 1, 1><<<grid, ATTN_THREADS, smem, s>>>(P);
+    else if (k2 && !v2) sparse_attn_kernel<TK, TV, 2, 1><<<grid, ATTN_THREADS, smem, s>>>(P);
+    else if (!k2 && v2) sparse_attn_kernel<TK, TV, 1, 2><<<grid, ATTN_THREADS, smem, s>>>(P);
+    else sparse_attn_kernel<TK, TV, 2, 2><<<grid, ATTN_THREADS, smem, s>>>(P);
+    HIRA_CHECK_LAUNCH("hira_sparse_attn launch");
+    return HIRA_OK;
+}
+
+}  // namespace hira
+
+using namespace hira;
+
+extern "C" int hira_attn_default_splits(int32_t n_qheads, int32_t n_tiles) {
+    if (n_qheads < 1 || n_tiles < 1) return 1;
+    int s = (8 * 148 + n_qheads - 1) / n_qheads;
+    if (s > n_tiles) s = n_tiles;
+    if (s > 64) s = 64;
+    return s < 1 ? 1 : s;
+}
+
+extern "C" int hira_sparse_attn(const hira_index_t* ix, const float* q, const float* scaling,
+                                const int32_t* q2kv, int32_t n_qheads, int32_t tile_parents,
+                                const int32_t* idx, const float* score, const int32_t* count,
+                                const void* queued_k, const void* queued_v, int32_t n_queued,
+                                int64_t queued_head_stride, int32_t n_splits, float* workspace,
+                                float* out, float* out_ml, void* stream) {
+    int rc = validate_index(ix, true);
+    if (rc != HIRA_OK) return rc;
+    HIRA_CHECK_ARG(idx && score && count && workspace && out, HIRA_ERR_ARG,
+                   "hira_sparse_attn: idx, score, count, workspace and out must not be NULL");
+    HIRA_CHECK_ARG(n_qheads >= 1 && n_splits >= 1, HIRA_ERR_SHAPE, "hira_sparse_attn: n_qheads=%d n_splits=%d",
+                   n_qheads, n_splits);
+    HIRA_CHECK_ARG(q2kv || n_qheads % ix->n_heads == 0, HIRA_ERR_SHAPE,
+                   "hira_sparse_attn: n_qheads=%d not divisible by n_heads=%d and no q2kv given", n_qheads, ix->n_heads);
+    HIRA_CHECK_ARG(tile_parents >= 1 && (long long)tile_parents * ix->bf <= ATTN_CHUNK, HIRA_ERR_SHAPE,
+                   "hira_sparse_attn: tile of %d parents x bf %d exceeds %d rows", tile_parents, ix->bf, ATTN_CHUNK);
+    HIRA_CHECK_ARG(n_queued >= 0, HIRA_ERR_SHAPE, "hira_sparse_attn: n_queued=%d", n_queued);
+    if (n_queued > 0) {
+        HIRA_CHECK_ARG(q && queued_k && queued_v, HIRA_ERR_ARG,
+                       "hira_sparse_attn: q, queued_k and queued_v are required when n_queued > 0");
+        HIRA_CHECK_ARG(n_queued < QUEUE_FLAG, HIRA_ERR_SHAPE, "hira_sparse_attn: n_queued too large");
+    }
+    AttnParams P;
+    P.values = ix->values; P.q = q; P.scaling = scaling; P.q2kv = q2kv;
+    P.idx = idx; P.score = score; P.count = count;
+    P.queued_k = queued_k; P.queued_v = queued_v; P.ws = workspace;
+    P.n_heads = ix->n_heads; P.n_qheads = n_qheads;
+    P.group = q2kv ? 1 : n_qheads / ix->n_heads;
+    P.dim = ix->dim; P.vdim = ix->vdim;
+    P.n_tiles = (ix->cap_parents + tile_parents - 1) / tile_parents;
+    P.tile_rows = tile_parents * ix->bf;
+    P.n_splits = n_splits; P.n_queued = n_queued;
+    P.cap_children = (long long)ix->cap_parents * ix->bf;
+    P.queued_head_stride = queued_head_stride;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (ix->dtype == HIRA_BF16 && ix->vdtype == HIRA_BF16) rc = launch_attn<__nv_bfloat16, __nv_bfloat16>(P, s);
+    else if (ix->dtype == HIRA_F32 && ix->vdtype == HIRA_F32) rc = launch_attn<float, float>(P, s);
+    else if (ix->dtype == HIRA_F32 && ix->vdtype == HIRA_BF16) rc = launch_attn<float, __nv_bfloat16>(P, s);
+    else rc = launch_attn<__nv_bfloat16, float>(P, s);
+    if (rc != HIRA_OK) return rc;
+    const long long pstride = ix->vdim + 2;
+    merge_kernel<<<n_qheads, 128, 0, s>>>(workspace + 2, workspace, pstride, pstride * n_splits, pstride,
+                                          pstride * n_splits, n_splits, ix->vdim, 0, out, out_ml);
+    HIRA_CHECK_LAUNCH("hira_sparse_attn merge launch");
+    return HIRA_OK;
+}
+
+extern "C" int hira_merge_partials(const float* part_o, const float* part_ml, int32_t n_parts,
+                                   int32_t n_qheads, int32_t vdim, float* out, float* out_ml, void* stream) {
+    HIRA_CHECK_ARG(part_o && part_ml && out, HIRA_ERR_ARG, "hira_merge_partials: NULL argument");
+    HIRA_CHECK_ARG(n_parts >= 1 && n_qheads >= 1 && vdim >= 1, HIRA_ERR_SHAPE,
+                   "hira_merge_partials: n_parts=%d n_qheads=%d vdim=%d", n_parts, n_qheads, vdim);
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    merge_kernel<<<n_qheads, 128, 0, s>>>(part_o, part_ml, (long long)n_qheads * vdim, vdim,
+                                          (long long)n_qheads * 2, 2, n_parts, vdim, 1, out, out_ml);
+    HIRA_CHECK_LAUNCH("hira_merge_partials launch");
+    return HIRA_OK;
+}

@@ -1,0 +1,300 @@
+"""Device-resident index arrays and thin typed wrappers over the C ABI.
+
+`IndexState` owns the torch tensors behind one `hira_index_t` (torch only supplies
+memory and the stream); the functions below forward to libhira_b200.so.  Names of
+the arrays follow the reference's CUDAIndexer attributes (indexer/cuda.py:40-54).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib as L
+
+
+class IndexState:
+    def __init__(self, *, n_heads: int, dim: int, vdim: int, bf: int, depth: int, cap_parents: int,
+                 dtype: torch.dtype, vdtype: Optional[torch.dtype], device, with_values: bool = True):
+        if depth not in (2, 3):
+            raise ValueError(f"Unsupported depth {depth}")
+        self.n_heads, self.dim, self.vdim, self.bf, self.depth = n_heads, dim, vdim if with_values else 0, bf, depth
+        self.dtype, self.vdtype = dtype, (vdtype if with_values else dtype)
+        self.device = torch.device(device)
+        if depth == 3:
+            self.cap_gp = max(1, -(-cap_parents // bf))
+            self.cap_parents = self.cap_gp * bf
+        else:
+            self.cap_gp = 0
+            self.cap_parents = max(1, cap_parents)
+        capC = self.cap_parents * bf
+        dev = self.device
+        z = torch.zeros
+        self.children = z((n_heads, capC, dim), dtype=dtype, device=dev)
+        self.values = z((n_heads, capC, self.vdim), dtype=self.vdtype, device=dev) if with_values else None
+        self.slot2token = torch.full((n_heads, capC), -1, dtype=torch.int32, device=dev)
+        self.parents = z((n_heads, self.cap_parents, dim), dtype=dtype, device=dev)
+        self.parent_radii = z((n_heads, self.cap_parents), dtype=torch.float32, device=dev)
+        self.parent_sqnorm = z((n_heads, self.cap_parents), dtype=torch.float32, device=dev)
+        self.child_counts = z((n_heads, self.cap_parents), dtype=torch.int32, device=dev)
+        if depth == 3:
+            self.grand_parents = z((n_heads, self.cap_gp, dim), dtype=dtype, device=dev)
+            self.gp_radii = z((n_heads, self.cap_gp), dtype=torch.float32, device=dev)
+            self.gp_sqnorm = z((n_heads, self.cap_gp), dtype=torch.float32, device=dev)
+            self.gp_counts = z((n_heads, self.cap_gp), dtype=torch.int32, device=dev)
+        else:
+            self.grand_parents = self.gp_radii = self.gp_sqnorm = self.gp_counts = None
+        self.used = z((n_heads, 4), dtype=torch.int32, device=dev)
+        self.status = z((1,), dtype=torch.int32, device=dev)
+        self._struct = None
+        self.refresh_struct()
+
+    ARRAYS = ("children", "values", "slot2token", "parents", "parent_radii", "parent_sqnorm", "child_counts",
+              "grand_parents", "gp_radii", "gp_sqnorm", "gp_counts", "used")
+
+    @property
+    def cap_children(self) -> int:
+        return self.cap_parents * self.bf
+
+    def refresh_struct(self):
+        s = L.HiraIndexStruct()
+        s.dtype = L.dtype_code(self.dtype)
+        s.vdtype = L.dtype_code(self.vdtype)
+        s.depth, s.bf, s.dim, s.vdim = self.depth, self.bf, self.dim, self.vdim
+        s.n_heads, s.cap_parents, s.cap_gp = self.n_heads, self.cap_parents, self.cap_gp
+        for name in self.ARRAYS:
+            setattr(s, name, L.ptr(getattr(self, name)))
+        self._struct = s
+        return s
+
+    @property
+    def struct(self):
+        return C.byref(self._struct)
+
+    def state_dict(self) -> dict:
+        d = {name: getattr(self, name) for name in self.ARRAYS if getattr(self, name) is not None}
+        d["meta"] = dict(n_heads=self.n_heads, dim=self.dim, vdim=self.vdim, bf=self.bf, depth=self.depth,
+                         cap_parents=self.cap_parents, dtype=str(self.dtype), vdtype=str(self.vdtype))
+        return d
+
+    def load_arrays(self, arrays: dict):
+        """Copies host/device arrays with matching shapes into the index (checkpoint import,
+        moving an index between the oracle and the device)."""
+        for name in self.ARRAYS:
+            dst = getattr(self, name)
+            if dst is None or name not in arrays or arrays[name] is None:
+                continue
+            src = arrays[name]
+            if not torch.is_tensor(src):
+                src = torch.as_tensor(src)
+            if src.dtype == torch.uint16 or (dst.dtype == torch.bfloat16 and src.dtype == torch.int16):
+                src = src.view(torch.bfloat16)
+            dst.copy_(src.reshape(dst.shape).to(dst.dtype))
+
+    def grown(self, new_cap_parents: int) -> "IndexState":
+        """A copy with more parent slots (and grandparent slots); existing slots keep their positions."""
+        new = IndexState(n_heads=self.n_heads, dim=self.dim, vdim=self.vdim, bf=self.bf, depth=self.depth,
+                         cap_parents=new_cap_parents, dtype=self.dtype, vdtype=self.vdtype, device=self.device,
+                         with_values=self.values is not None)
+        for name in self.ARRAYS:
+            src = getattr(self, name)
+            if src is None or name == "used":
+                continue
+            getattr(new, name)[:, : src.shape[1]].copy_(src)
+        new.used.copy_(self.used)
+        new.status.copy_(self.status)
+        return new
+
+
+@dataclass
+class CompactResult:
+    """Compacted search output (see hira_search in include/hira_b200.h)."""
+    idx: torch.Tensor      # (H_q, cap_children) int32, slot ids, valid in the first count entries of each tile segment
+    score: torch.Tensor    # (H_q, cap_children) float32
+    count: torch.Tensor    # (H_q, n_tiles) int32
+    tile_parents: int
+    tile_rows: int
+
+    def to_lists(self):
+        """Per query head: (slots, scores) as 1-D CPU tensors, ascending slot order."""
+        idx, score, count = self.idx.cpu(), self.score.cpu(), self.count.cpu()
+        out = []
+        for qh in range(idx.shape[0]):
+            sl, sc = [], []
+            for t in range(count.shape[1]):
+                c = int(count[qh, t])
+                if c:
+                    b = t * self.tile_rows
+                    sl.append(idx[qh, b:b + c])
+                    sc.append(score[qh, b:b + c])
+            out.append((torch.cat(sl) if sl else torch.empty(0, dtype=torch.int32),
+                        torch.cat(sc) if sc else torch.empty(0)))
+        return out
+
+
+def tile_parents(st: IndexState) -> int:
+    return int(L.load().hira_search_tile_parents(st.struct))
+
+
+def n_tiles(st: IndexState, tp: Optional[int] = None) -> int:
+    tp = tp or tile_parents(st)
+    return -(-st.cap_parents // tp)
+
+
+def _f32(t: Optional[torch.Tensor], dev) -> Optional[torch.Tensor]:
+    if t is None:
+        return None
+    return t.to(device=dev, dtype=torch.float32).contiguous()
+
+
+def search(st: IndexState, q: torch.Tensor, tau: torch.Tensor, *, scaling=None, qnorm=None, q2kv=None,
+           max_group: int = 0, flags: int = 0, out_dense=None, compact: Optional[CompactResult] = None,
+           want_compact: bool = False, stats=None, tp: Optional[int] = None):
+    """q (H_q, D) fp32, tau (H_q,) fp32 on the index device.  Returns (out_dense, CompactResult|None)."""
+    lib = L.load()
+    hq = q.shape[0]
+    tp = tp or tile_parents(st)
+    if want_compact and compact is None:
+        compact = alloc_compact(st, hq, tp)
+    rc = lib.hira_search(st.struct, L.ptr(q), L.ptr(tau), L.ptr(scaling), L.ptr(qnorm), L.ptr(q2kv), hq,
+                         max_group, flags, tp, L.ptr(out_dense),
+                         L.ptr(compact.idx) if compact else None, L.ptr(compact.score) if compact else None,
+                         L.ptr(compact.count) if compact else None, L.ptr(stats), L.current_stream(st.device))
+    L.check(rc, "hira_search")
+    return out_dense, compact
+
+
+def alloc_compact(st: IndexState, hq: int, tp: Optional[int] = None) -> CompactResult:
+    tp = tp or tile_parents(st)
+    dev = st.device
+    return CompactResult(
+        idx=torch.empty((hq, st.cap_children), dtype=torch.int32, device=dev),
+        score=torch.empty((hq, st.cap_children), dtype=torch.float32, device=dev),
+        count=torch.zeros((hq, n_tiles(st, tp)), dtype=torch.int32, device=dev),
+        tile_parents=tp, tile_rows=tp * st.bf)
+
+
+def attn_splits(st: IndexState, hq: int, tp: Optional[int] = None) -> int:
+    return int(L.load().hira_attn_default_splits(hq, n_tiles(st, tp)))
+
+
+def sparse_attn(st: IndexState, q, scaling, compact: CompactResult, *, q2kv=None, queued_k=None, queued_v=None,
+                n_splits: Optional[int] = None, workspace=None, out=None, out_ml=None):
+    lib = L.load()
+    hq = q.shape[0]
+    n_splits = n_splits or attn_splits(st, hq, compact.tile_parents)
+    dev = st.device
+    if workspace is None:
+        workspace = torch.empty((hq * n_splits * (st.vdim + 2),), dtype=torch.float32, device=dev)
+    if out is None:
+        out = torch.empty((hq, st.vdim), dtype=torch.float32, device=dev)
+    n_queued, qstride = 0, 0
+    if queued_k is not None and queued_k.shape[-2] > 0:
+        assert queued_k.is_contiguous() and queued_v.is_contiguous()
+        assert queued_k.dtype == st.dtype and queued_v.dtype == st.vdtype
+        n_queued = queued_k.shape[-2]
+        qstride = n_queued * st.dim
+        if st.vdim != st.dim:
+            raise ValueError("queued keys/values with vdim != dim are not supported")
+    rc = lib.hira_sparse_attn(st.struct, L.ptr(q), L.ptr(scaling), L.ptr(q2kv), hq, compact.tile_parents,
+                              L.ptr(compact.idx), L.ptr(compact.score), L.ptr(compact.count),
+                              L.ptr(queued_k) if n_queued else None, L.ptr(queued_v) if n_queued else None,
+                              n_queued, qstride, n_splits, L.ptr(workspace), L.ptr(out), L.ptr(out_ml),
+                              L.current_stream(dev))
+    L.check(rc, "hira_sparse_attn")
+    return out
+
+
+def merge_partials(part_o, part_ml, out=None, out_ml=None):
+    lib = L.load()
+    n_parts, hq, vdim = part_o.shape
+    if out is None:
+        out = torch.empty((hq, vdim), dtype=torch.float32, device=part_o.device)
+    rc = lib.hira_merge_partials(L.ptr(part_o), L.ptr(part_ml), n_parts, hq, vdim, L.ptr(out), L.ptr(out_ml),
+                                 L.current_stream(part_o.device))
+    L.check(rc, "hira_merge_partials")
+    return out
+
+
+def append(st: IndexState, new_k: torch.Tensor, new_v: Optional[torch.Tensor], token_base: int = -1):
+    """new_k (n_heads, M, D), new_v (n_heads, M, V) contiguous, index dtypes."""
+    lib = L.load()
+    assert new_k.is_contiguous() and new_k.dtype == st.dtype
+    m = new_k.shape[1]
+    if new_v is not None:
+        assert new_v.is_contiguous() and new_v.dtype == st.vdtype
+    rc = lib.hira_append(st.struct, L.ptr(new_k), L.ptr(new_v), m, m * st.dim,
+                         m * st.vdim if new_v is not None else 0, token_base, L.ptr(st.status),
+                         L.current_stream(st.device))
+    L.check(rc, "hira_append")
+
+
+def threshold(samples: torch.Tensor, q: torch.Tensor, method: int, k: int = 1, q2kv=None, out=None):
+    """samples (H_kv, S, D) contiguous fp32/bf16, q (H_q, D) fp32 -> tau (H_q,)."""
+    lib = L.load()
+    hkv, s, d = samples.shape
+    hq = q.shape[0]
+    if out is None:
+        out = torch.empty((hq,), dtype=torch.float32, device=q.device)
+    rc = lib.hira_threshold(L.ptr(samples), L.dtype_code(samples.dtype), hkv, s, d, s * d, L.ptr(q), L.ptr(q2kv),
+                            hq, method, k, L.ptr(out), L.current_stream(q.device))
+    L.check(rc, "hira_threshold")
+    return out
+
+
+def kth_score(st: IndexState, compact: CompactResult, k: torch.Tensor, out=None):
+    lib = L.load()
+    hq = compact.idx.shape[0]
+    if out is None:
+        out = torch.empty((hq,), dtype=torch.float32, device=st.device)
+    rc = lib.hira_kth_score(st.struct, hq, compact.tile_parents, L.ptr(compact.score), L.ptr(compact.count),
+                            L.ptr(k), L.ptr(out), L.current_stream(st.device))
+    L.check(rc, "hira_kth_score")
+    return out
+
+
+def build(st: IndexState, keys: torch.Tensor, values: Optional[torch.Tensor], *, cent_idx1=None, cent_idx2=None,
+          n_iters: int = 1, use_tensor_cores: bool = True, token_base: int = 0):
+    """keys (n_heads, n, D), values (n_heads, n, V) contiguous, index dtypes."""
+    lib = L.load()
+    assert keys.is_contiguous() and keys.dtype == st.dtype
+    n = keys.shape[1]
+    if values is not None:
+        assert values.is_contiguous() and values.dtype == st.vdtype
+    nbytes = int(lib.hira_build_workspace_bytes(st.struct, n))
+    ws = torch.empty((max(nbytes, 1),), dtype=torch.uint8, device=st.device)
+    rc = lib.hira_build(st.struct, L.ptr(keys), L.ptr(values), n, n * st.dim,
+                        n * st.vdim if values is not None else 0, token_base, L.ptr(cent_idx1), L.ptr(cent_idx2),
+                        n_iters, 1 if use_tensor_cores else 0, L.ptr(ws), nbytes, L.current_stream(st.device))
+    L.check(rc, "hira_build")
+    st.status.zero_()
+
+
+def recompute_radii(st: IndexState):
+    L.check(L.load().hira_recompute_radii(st.struct, L.current_stream(st.device)), "hira_recompute_radii")
+
+
+def export(st: IndexState, n_out: int, token_base: int = 0):
+    lib = L.load()
+    out_k = torch.zeros((st.n_heads, n_out, st.dim), dtype=st.dtype, device=st.device)
+    out_v = torch.zeros((st.n_heads, n_out, st.vdim), dtype=st.vdtype, device=st.device) if st.values is not None else None
+    rc = lib.hira_export(st.struct, token_base, n_out, L.ptr(out_k), L.ptr(out_v), L.current_stream(st.device))
+    L.check(rc, "hira_export")
+    return out_k, out_v
+
+
+def assign(points: torch.Tensor, cents: torch.Tensor, use_tensor_cores: bool = False):
+    """points (H, n, D), cents (H, k, D) -> (idx (H, n) int32, dist2 (H, n) fp32)."""
+    lib = L.load()
+    h, n, d = points.shape
+    k = cents.shape[1]
+    dev = points.device
+    idx = torch.empty((h, n), dtype=torch.int32, device=dev)
+    d2 = torch.empty((h, n), dtype=torch.float32, device=dev)
+    csq = torch.empty((h, k), dtype=torch.float32, device=dev)
+    rc = lib.hira_assign(L.ptr(points.contiguous()), L.ptr(cents.contiguous()), L.dtype_code(points.dtype), h, n, k, d,
+                         1 if use_tensor_cores else 0, L.ptr(csq), L.ptr(idx), L.ptr(d2), L.current_stream(dev))
+    L.check(rc, "hira_assign")
+    return idx, d2

@@ -1,0 +1,249 @@
+"""CUDAIndexer: the reference's blocked 2/3-level index (indexer/cuda.py:16-1302) with
+the same constructor, `build` / `update` entry points and tensor attributes, backed by
+the CUDA library instead of torch op chains and Triton kernels.
+
+Attribute parity (indexer/cuda.py:40-54): `children (H, P*bf, D)`, `values (1, H, P*bf, V)`,
+`parents (H, P, D)`, `parent_radii (H, P)`, `grand_parents (H, G, D)`, `grand_parent_radii
+(H, G)`, `_child_counts`, `_parent_valid`, `_gp_child_counts`, `branching_factor`, `depth`,
+`pad_value`, `dim`, `num_heads`.  They are views over the memory the kernels use.
+
+Differences by design:
+  * children keep the dtype of the keys given to `build` (the reference always casts to
+    float32, indexer/cuda.py:365-368), so a bf16 cache is searched as bf16;
+  * validity is explicit state (`_child_counts`, `_gp_child_counts`, `used`), not "row is
+    all pad_value";
+  * `max_context` pre-allocates room for that many keys per head so that `update` never
+    reallocates and never synchronises with the host; without it the arrays are sized
+    exactly as the reference sizes them and grow (by reallocation) when needed;
+  * a batch larger than 1 is folded into the head axis (the reference is batch-1,
+    indexer/cuda.py:61).
+"""
+from __future__ import annotations
+
+from enum import Enum
+from typing import Optional
+
+import torch
+
+from .. import index_state as S
+from .base import BaseIndexer
+
+DEFAULT_PAD_VALUE = 0.0
+
+
+class CUDAIndexer(BaseIndexer):
+
+    class DEPTH(Enum):
+        TWO_LEVELS = 2
+        THREE_LEVELS = 3
+
+    def __init__(self, num_levels, max_iterations: int, branching_factor: int, verbose: bool = False,
+                 pad_value: float = DEFAULT_PAD_VALUE, *, max_context: Optional[int] = None,
+                 use_tensor_cores: bool = True, seed: int = 1234):
+        self.depth = num_levels if isinstance(num_levels, CUDAIndexer.DEPTH) else CUDAIndexer.DEPTH(num_levels)
+        self.max_iterations = max_iterations
+        self.branching_factor = int(branching_factor)
+        self.verbose = verbose
+        self.pad_value = pad_value
+        self.max_context = max_context
+        self.use_tensor_cores = use_tensor_cores
+        self.seed = seed
+        self.dim: int = 0
+        self.num_heads: int = 0
+        self.state: Optional[S.IndexState] = None
+        self._parents_bound = 0   # host-side upper bounds on used parent / grandparent slots
+        self._gp_bound = 0
+        self._n_keys = 0
+
+    # ---- reference attribute names as views ---------------------------------
+    @property
+    def children(self):
+        return None if self.state is None else self.state.children
+
+    @property
+    def values(self):
+        return None if self.state is None or self.state.values is None else self.state.values.unsqueeze(0)
+
+    @property
+    def parents(self):
+        return None if self.state is None else self.state.parents
+
+    @property
+    def parent_radii(self):
+        return None if self.state is None else self.state.parent_radii
+
+    @property
+    def grand_parents(self):
+        return None if self.state is None else self.state.grand_parents
+
+    @property
+    def grand_parent_radii(self):
+        return None if self.state is None else self.state.gp_radii
+
+    @property
+    def _child_counts(self):
+        return None if self.state is None else self.state.child_counts
+
+    @property
+    def _gp_child_counts(self):
+        return None if self.state is None else self.state.gp_counts
+
+    @property
+    def _parent_valid(self):
+        st = self.state
+        if st is None:
+            return None
+        p = torch.arange(st.cap_parents, device=st.device)
+        if st.depth == 3:
+            g = p // st.bf
+            ok = (g[None, :] < st.used[:, 1:2]) & ((p % st.bf)[None, :] < st.gp_counts.gather(1, g[None, :].expand(st.n_heads, -1).long()))
+        else:
+            ok = p[None, :] < st.used[:, 0:1]
+        return ok
+
+    @property
+    def slot2token(self):
+        return None if self.state is None else self.state.slot2token
+
+    # ---- build --------------------------------------------------------------
+    @staticmethod
+    def _fold(t: torch.Tensor) -> torch.Tensor:
+        if t.ndim != 4:
+            raise ValueError(f"expected a (B, H, L, D) tensor, got {tuple(t.shape)}")
+        b, h, l, d = t.shape
+        return t.reshape(b * h, l, d).contiguous()
+
+    def _capacity_parents(self, n_keys: int) -> int:
+        bf = self.branching_factor
+        if self.max_context is None:
+            return max(1, -(-n_keys // bf))
+        # room for max_context keys: full parents for the built prefix plus, in the
+        # worst case, one new parent per appended key
+        n_ctx = max(self.max_context, n_keys)
+        return max(1, -(-n_keys // bf)) + (n_ctx - n_keys)
+
+    @torch.no_grad()
+    def build(self, keys: torch.Tensor, values: Optional[torch.Tensor] = None):
+        """keys (B, H, L, D); values optional (B, H, L, V)."""
+        if not torch.cuda.is_available():
+            raise RuntimeError("CUDAIndexer needs a CUDA device (there is no CPU fallback)")
+        keys = self._fold(keys.to("cuda"))
+        h, n, d = keys.shape
+        if values is not None:
+            values = self._fold(values.to("cuda"))
+            if values.shape[:2] != keys.shape[:2]:
+                raise ValueError("values must have the same (B, H, L) as keys")
+        self.num_heads, self.dim = h, d
+        bf = self.branching_factor
+        cap_p = self._capacity_parents(n)
+        if self.depth == CUDAIndexer.DEPTH.THREE_LEVELS and self.max_context is not None:
+            cap_p = cap_p + bf  # whole spare grandparent blocks
+        st = S.IndexState(n_heads=h, dim=d, vdim=values.shape[-1] if values is not None else 0, bf=bf,
+                          depth=self.depth.value, cap_parents=cap_p, dtype=keys.dtype,
+                          vdtype=values.dtype if values is not None else None, device=keys.device,
+                          with_values=values is not None)
+        k1 = -(-n // bf) if n else 0
+        k2 = -(-k1 // bf) if k1 else 0
+        g = torch.Generator(device=keys.device)
+        g.manual_seed(self.seed)
+        cent1 = cent2 = None
+        if n:
+            # distinct random points as initial centres (indexer/cuda.py:229-237)
+            cent1 = torch.rand((h, n), generator=g, device=keys.device).topk(k1, dim=1).indices.to(torch.int32).contiguous()
+            if st.depth == 3:
+                cent2 = torch.rand((h, k1), generator=g, device=keys.device).topk(k2, dim=1).indices.to(torch.int32).contiguous()
+        S.build(st, keys, values, cent_idx1=cent1, cent_idx2=cent2, n_iters=max(1, int(self.max_iterations)),
+                use_tensor_cores=self.use_tensor_cores)
+        self.state = st
+        self._n_keys = n
+        self._parents_bound = k2 * bf if st.depth == 3 else k1
+        self._gp_bound = k2
+        return self
+
+    # ---- update -------------------------------------------------------------
+    def _ensure_capacity(self, m: int):
+        st = self.state
+        need_p = self._parents_bound + m
+        need_g = self._gp_bound + m
+        short = (need_g > st.cap_gp) if st.depth == 3 else (need_p > st.cap_parents)
+        if not short:
+            return
+        # tighten the bounds from the device state before paying for a reallocation
+        used = st.used.max(dim=0).values.tolist()
+        self._parents_bound, self._gp_bound = int(used[0]), int(used[1])
+        need_p, need_g = self._parents_bound + m, self._gp_bound + m
+        if st.depth == 3:
+            if need_g <= st.cap_gp:
+                return
+            new_cap = max(need_g, st.cap_gp + max(1, st.cap_gp // 2)) * st.bf
+        else:
+            if need_p <= st.cap_parents:
+                return
+            new_cap = max(need_p, st.cap_parents + max(1, st.cap_parents // 2))
+        self.state = st.grown(new_cap)
+
+    @torch.no_grad()
+    def update(self, new_keys: torch.Tensor, new_values: Optional[torch.Tensor] = None):
+        """new_keys (B, H, M, D), new_values optional (B, H, M, V) -- appended one after another."""
+        if self.state is None:
+            raise ValueError("Indexer is not built")
+        assert new_values is None or new_keys.shape[:3] == new_values.shape[:3]
+        if new_keys.ndim != 4:
+            raise ValueError(f"new_keys must be (B, H, M, D), got {tuple(new_keys.shape)}")
+        k = self._fold(new_keys.to(self.state.device))
+        h, m, d = k.shape
+        if h != self.num_heads or d != self.dim:
+            raise ValueError(f"new_keys has (heads, dim)=({h}, {d}), index has ({self.num_heads}, {self.dim})")
+        has_values = self.state.values is not None
+        v = None
+        if has_values:
+            if new_values is None:
+                raise ValueError("the index stores values: new_values is required")
+            v = self._fold(new_values.to(self.state.device)).to(self.state.vdtype)
+        if m == 0:
+            return self
+        self._ensure_capacity(m)
+        S.append(self.state, k.to(self.state.dtype), v)
+        self._parents_bound += m
+        self._gp_bound += m
+        self._n_keys += m
+        return self
+
+    def check_status(self):
+        """Raises if an append ran out of pre-allocated slots (reads one word from the device)."""
+        code = int(self.state.status.item())
+        if code:
+            raise RuntimeError(f"index capacity exhausted during update (status {code}); raise max_context")
+
+    @torch.no_grad()
+    def rebuild(self):
+        """Full rebuild over the keys currently stored (token order), e.g. every N decode steps."""
+        st = self.state
+        n = self._n_keys
+        keys, values = S.export(st, n)
+        b = self.__class__(self.depth, self.max_iterations, self.branching_factor, self.verbose, self.pad_value,
+                           max_context=self.max_context, use_tensor_cores=self.use_tensor_cores, seed=self.seed)
+        b.build(keys.unsqueeze(0), None if values is None else values.unsqueeze(0))
+        self.state, self._parents_bound, self._gp_bound = b.state, b._parents_bound, b._gp_bound
+        return self
+
+    # ---- checkpoint ---------------------------------------------------------
+    def state_dict(self) -> dict:
+        d = self.state.state_dict()
+        d["meta"].update(n_keys=self._n_keys, parents_bound=self._parents_bound, gp_bound=self._gp_bound)
+        return d
+
+    @classmethod
+    def from_state_dict(cls, sd: dict, device="cuda", **kw) -> "CUDAIndexer":
+        m = sd["meta"]
+        dt = {"torch.float32": torch.float32, "torch.bfloat16": torch.bfloat16}
+        self = cls(m["depth"], kw.pop("max_iterations", 1), m["bf"], **kw)
+        st = S.IndexState(n_heads=m["n_heads"], dim=m["dim"], vdim=m["vdim"], bf=m["bf"], depth=m["depth"],
+                          cap_parents=m["cap_parents"], dtype=dt[m["dtype"]], vdtype=dt[m["vdtype"]], device=device,
+                          with_values=sd.get("values") is not None)
+        st.load_arrays(sd)
+        self.state, self.num_heads, self.dim = st, m["n_heads"], m["dim"]
+        self._n_keys = m.get("n_keys", 0)
+        self._parents_bound = m.get("parents_bound", st.cap_parents)
+        self._gp_bound = m.get("gp_bound", st.cap_gp)
+        return self

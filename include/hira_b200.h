@@ -1,0 +1,263 @@
+/*
+ * hira_b200.h -- C ABI of libhira_b200.so: the decode-time hot path of HIRA
+ * ("Louver" hierarchical range-searching sparse attention) as hand-written
+ * CUDA kernels for NVIDIA B200 (sm_100a).
+ *
+ * Conventions (all entry points unless stated otherwise)
+ *   - Every pointer inside hira_index_t and every data argument is a DEVICE
+ *     pointer; the hira_index_t struct itself lives in host memory.
+ *   - Nothing is allocated, freed or synchronised: the caller owns all memory
+ *     (including workspaces) and all work is enqueued on `stream`.
+ *   - Return value: HIRA_OK, or a negative HIRA_ERR_* detected on the host
+ *     before any launch; hira_last_error() gives the message for the calling
+ *     thread.  Problems only the device can see (index capacity exhausted
+ *     during an append) are reported through a caller-provided `int32_t*
+ *     status` word in device memory (0 = ok), never by a trap.
+ *   - Heads: the batch is folded into the head axis.  `n_heads` counts
+ *     (batch, kv_head) pairs, `n_qheads` counts (batch, query_head) pairs.
+ *
+ * Blocked index layout (same as the reference's CUDAIndexer tensors,
+ * indexer/cuda.py:40-54, 350-356, 440-446):
+ *   parent p owns child slots [p*bf, (p+1)*bf); with depth 3 grandparent g owns
+ *   parent slots [g*bf, (g+1)*bf).  Unlike the reference, which infers
+ *   validity from "row is all pad_value" on every call
+ *   (indexer/cuda.py:1241-1298), validity is explicit persistent state:
+ *   child_counts / gp_counts / used.
+ */
+#ifndef HIRA_B200_H
+#define HIRA_B200_H
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HIRA_OK 0
+#define HIRA_ERR_ARG (-1)      /* null pointer / bad enum / bad flag            */
+#define HIRA_ERR_SHAPE (-2)    /* sizes inconsistent with the index             */
+#define HIRA_ERR_DTYPE (-3)    /* unsupported element type                      */
+#define HIRA_ERR_CAPACITY (-4) /* workspace or fixed scratch too small          */
+#define HIRA_ERR_CUDA (-5)     /* a CUDA runtime call or launch failed          */
+
+/* element types */
+#define HIRA_F32 0
+#define HIRA_BF16 1
+
+/* device status word bits written by hira_append */
+#define HIRA_STATUS_PARENTS_FULL 1 /* no free parent slot left for an orphan key */
+#define HIRA_STATUS_GP_FULL 2      /* no free grandparent slot left              */
+
+/* search flags */
+#define HIRA_GATE_GT 0x0          /* keep node iff q.c + r >  tau (reference Triton kernels, kernels/triton_search_kernels.py:49,114,131) */
+#define HIRA_GATE_GE 0x1          /* keep node iff q.c + r >= tau (reference CPU kernels, kernels/cpp/torch_ext_v3.cpp:182,212)         */
+#define HIRA_LEAF_CANDIDATES 0x0  /* emit every child of a kept parent (reference Triton kernels: no leaf test)                         */
+#define HIRA_LEAF_GE 0x2          /* emit child iff q.k >= tau (reference CPU kernels, torch_ext_v3.cpp:237-240)                        */
+#define HIRA_LEAF_GT 0x4          /* emit child iff q.k >  tau                                                                          */
+
+/* threshold methods */
+#define HIRA_TAU_SAMPLE_MAX 0       /* max of the sample scores                      (cache/threshold_finder.py:1-3)   */
+#define HIRA_TAU_SAMPLE_MEAN_TOPK 1 /* mean of the k largest sample scores           (cache/threshold_finder.py:6-8)   */
+#define HIRA_TAU_SAMPLE_KTH 2       /* k-th largest sample score                                                        */
+
+typedef struct hira_index {
+    int32_t dtype;        /* HIRA_F32 | HIRA_BF16: children, parents, grand_parents   */
+    int32_t vdtype;       /* element type of values                                    */
+    int32_t depth;        /* 2 or 3 (CUDAIndexer.DEPTH, indexer/cuda.py:18-21)         */
+    int32_t bf;           /* branching factor, 1..1024                                 */
+    int32_t dim;          /* D, multiple of 8, <= 256                                  */
+    int32_t vdim;         /* V, multiple of 8, <= 256; 0 when values == NULL           */
+    int32_t n_heads;      /* (batch, kv_head) pairs                                    */
+    int32_t cap_parents;  /* parent slots allocated per head (depth 3: cap_gp * bf)    */
+    int32_t cap_gp;       /* grandparent slots allocated per head (depth 3), else 0    */
+    int32_t reserved0;
+    void* children;        /* [n_heads][cap_parents*bf][dim]                           */
+    void* values;          /* [n_heads][cap_parents*bf][vdim] or NULL                  */
+    int32_t* slot2token;   /* [n_heads][cap_parents*bf] token position in slot, -1 empty */
+    void* parents;         /* [n_heads][cap_parents][dim]                              */
+    float* parent_radii;   /* [n_heads][cap_parents]                                   */
+    float* parent_sqnorm;  /* [n_heads][cap_parents] cached ||c||^2                    */
+    int32_t* child_counts; /* [n_heads][cap_parents] filled child slots (contiguous from 0) */
+    void* grand_parents;   /* [n_heads][cap_gp][dim]   (depth 3)                       */
+    float* gp_radii;       /* [n_heads][cap_gp]                                        */
+    float* gp_sqnorm;      /* [n_heads][cap_gp]                                        */
+    int32_t* gp_counts;    /* [n_heads][cap_gp] filled parent slots per grandparent    */
+    int32_t* used;         /* [n_heads][4]: {parent slots in use (high-water mark),
+                              grandparents in use, keys stored, reserved}             */
+} hira_index_t;
+
+const char* hira_last_error(void);
+const char* hira_version(void);
+
+/* ------------------------------------------------------------------------- */
+/* Search.  Replaces CUDASearcher.search -> triton_two_level_filter /
+ * triton_three_level_filter (searcher/cuda.py:56-143,
+ * kernels/triton_search_wrappers.py:113-211,287-358,
+ * kernels/triton_search_kernels.py:6-148) and, with HIRA_GATE_GE|HIRA_LEAF_GE,
+ * the CPU fused_tree_search_v3 semantics (kernels/cpp/torch_ext_v3.cpp:36-247)
+ * on the blocked layout.
+ *
+ *   q        [n_qheads][dim] fp32     tau [n_qheads] fp32
+ *   scaling  [n_qheads] fp32 or NULL (1.0): multiplies emitted scores only
+ *   qnorm    [n_qheads] fp32 or NULL: gate uses q.c + qnorm*r; NULL = unit query
+ *            (the reference assumes a unit query, searcher/cpu.py:61-63)
+ *   q2kv     [n_qheads] int32 or NULL: NULL = query head i belongs to kv head
+ *            i / (n_qheads / n_heads)
+ *   max_group: with an explicit q2kv, the largest number of query heads that
+ *            map to one kv head (0 = unknown: n_qheads is assumed); ignored
+ *            when q2kv is NULL
+ *   out_dense  [n_qheads][cap_parents*bf] fp32 or NULL: score*scaling where
+ *            emitted, 0 elsewhere; every element is written (no memset needed)
+ *   out_idx / out_score [n_qheads][cap_parents*bf], out_count
+ *            [n_qheads][n_tiles] or all NULL: compacted output.  Tile t of a
+ *            head covers parent slots [t*tile_parents, (t+1)*tile_parents);
+ *            its emitted child slots are written in ascending slot order to
+ *            out_idx/out_score starting at element t*tile_parents*bf, and their
+ *            number to out_count[qh][t].
+ *   stats    [n_qheads][8] uint32 or NULL; added to, not cleared:
+ *            {gp tested, gp kept, parents tested, parents kept, child rows read
+ *             on behalf of this head, children emitted, U, P} where U and P
+ *            (booked on the first query head of each group) count the child
+ *            rows and parent rows actually loaded, i.e. for the union of the
+ *            group's heads -- the kernel's real memory traffic
+ *   tile_parents: use hira_search_tile_parents(); n_tiles =
+ *            ceil(cap_parents / tile_parents).
+ */
+int hira_search_tile_parents(const hira_index_t* index);
+int hira_search(const hira_index_t* index, const float* q, const float* tau,
+                const float* scaling, const float* qnorm, const int32_t* q2kv,
+                int32_t n_qheads, int32_t max_group, int32_t flags,
+                int32_t tile_parents,
+                float* out_dense, int32_t* out_idx, float* out_score,
+                int32_t* out_count, uint32_t* stats, void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Sparse attention over the compacted search output (the reference names
+ * hira_attention but ships only a stub, attention/hira_attention.py:1-3).
+ * Softmax over {emitted children} U {queued keys}; logits of emitted children
+ * are out_score (so pass scaling = ||q|| * softmax_scale to hira_search);
+ * logits of queued keys are scaling * (q . k_queued) computed here.
+ *
+ *   queued_k/queued_v [n_heads][n_queued][dim|vdim] in index dtype/vdtype with
+ *            row strides queued_head_stride (elements between heads); may be
+ *            NULL when n_queued == 0
+ *   workspace: n_qheads * n_splits * (vdim + 2) floats of scratch
+ *   out      [n_qheads][vdim] fp32, normalised attention output
+ *   out_ml   [n_qheads][2] fp32 or NULL: (running max m, denominator l) so that
+ *            shards can be merged with hira_merge_partials
+ *   n_splits: CTAs per query head (>= 1); use hira_attn_default_splits()
+ */
+int hira_attn_default_splits(int32_t n_qheads, int32_t n_tiles);
+int hira_sparse_attn(const hira_index_t* index, const float* q,
+                     const float* scaling, const int32_t* q2kv,
+                     int32_t n_qheads, int32_t tile_parents,
+                     const int32_t* idx, const float* score,
+                     const int32_t* count, const void* queued_k,
+                     const void* queued_v, int32_t n_queued,
+                     int64_t queued_head_stride, int32_t n_splits,
+                     float* workspace, float* out, float* out_ml, void* stream);
+
+/* Log-sum-exp merge of partial softmax results (used across sequence shards
+ * after an all-gather).  part_o [n_parts][n_qheads][vdim] holds NORMALISED
+ * outputs, part_ml [n_parts][n_qheads][2] their (m, l).  Writes the normalised
+ * merged output and optionally its (m, l). */
+int hira_merge_partials(const float* part_o, const float* part_ml,
+                        int32_t n_parts, int32_t n_qheads, int32_t vdim,
+                        float* out, float* out_ml, void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Append.  Replaces CUDAIndexer.update (indexer/cuda.py:544-701) and its
+ * Triton kernels (kernels/triton_update_kernels.py:6-418) for decode-time
+ * insertion: nearest valid parent by ||c||^2 - 2 x.c (ties -> lowest index),
+ * slot claim, K/V row write, parent radius widen, grandparent radius widen
+ * (indexer/cuda.py:1200-1231); a key whose nearest parent is full becomes a
+ * new parent of radius 0 holding itself (the reference's behaviour for one
+ * key per head, indexer/cuda.py:730-733,818-820,877-887), placed under its
+ * nearest grandparent if that has a free parent slot (:917-962), else under a
+ * new grandparent (:1070-1072).  The n_new keys of a head are inserted one
+ * after another in order, so the result is deterministic.
+ *
+ *   new_k [n_heads][n_new][dim], new_v [n_heads][n_new][vdim]: index dtypes,
+ *          head strides in elements
+ *   token_base: token position of new key 0 is token_base + used[h][2]
+ *          when token_base < 0, else token_base + i
+ *   status: device int32, OR-ed with HIRA_STATUS_* on capacity exhaustion
+ */
+int hira_append(const hira_index_t* index, const void* new_k, const void* new_v,
+                int32_t n_new, int64_t k_head_stride, int64_t v_head_stride,
+                int32_t token_base, int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Threshold finder (the reference names sample_max / sample_mean_topk but
+ * both raise NotImplementedError, cache/threshold_finder.py:1-14).
+ *   samples [n_heads][n_samples][dim] in `dtype`, head stride in elements
+ *   tau_out [n_qheads]: method applied to the scores q . sample
+ *   n_samples <= 4096;  k in [1, n_samples] for the top-k methods. */
+int hira_threshold(const void* samples, int32_t dtype, int32_t n_heads,
+                   int32_t n_samples, int32_t dim, int64_t head_stride,
+                   const float* q, const int32_t* q2kv, int32_t n_qheads,
+                   int32_t method, int32_t k, float* tau_out, void* stream);
+
+/* Exact k-th largest of the scores in a compacted search output (run
+ * hira_search with HIRA_LEAF_CANDIDATES, tau = -inf and scaling = NULL first).
+ * k [n_qheads] int32 per-head ranks (1 = largest).  tau_out[qh] = that score,
+ * or -inf when fewer than k scores exist. */
+int hira_kth_score(const hira_index_t* index, int32_t n_qheads,
+                   int32_t tile_parents, const float* score,
+                   const int32_t* count, const int32_t* k, float* tau_out,
+                   void* stream);
+
+/* ------------------------------------------------------------------------- */
+/* Build.  Replaces CUDAIndexer.build (indexer/cuda.py:56-108) with its
+ * helpers (:114-538): per level, nearest-centroid assignment, capacity-bf
+ * grouping closest-first with overflow into free slots, blocked layout,
+ * radii from the layout.  n_iters = 1 assigns once to the sampled points (the
+ * reference CUDA behaviour, :229-245); n_iters > 1 runs n_iters-1 Lloyd mean
+ * updates first.
+ *
+ *   keys [n_heads][n_keys][dim], values [n_heads][n_keys][vdim] (index dtypes),
+ *          head strides in elements; n_keys <= cap_parents*bf
+ *   cent_idx1 [n_heads][ceil(n_keys/bf)] int32: key positions used as initial
+ *          parent centres; cent_idx2 [n_heads][ceil(n1/bf)] (depth 3): parent
+ *          ids used as initial grandparent centres.  NULL = evenly strided.
+ *   The index arrays are fully (re)initialised: unused slots are zero rows,
+ *   radius 0, count 0, slot2token -1.
+ *   use_tensor_cores: 1 = tcgen05 assignment GEMM when dtype is bf16 and the
+ *          shapes allow it, 0 = CUDA-core fp32 assignment.
+ */
+size_t hira_build_workspace_bytes(const hira_index_t* index, int32_t n_keys);
+int hira_build(const hira_index_t* index, const void* keys, const void* values,
+               int32_t n_keys, int64_t k_head_stride, int64_t v_head_stride,
+               int32_t token_base, const int32_t* cent_idx1,
+               const int32_t* cent_idx2, int32_t n_iters,
+               int32_t use_tensor_cores, void* workspace,
+               size_t workspace_bytes, void* stream);
+
+/* Radii recomputed from the layout (indexer/cuda.py:114-198): parent radius =
+ * max over filled children of ||child - parent||; grandparent radius = max
+ * over filled parents of (||parent - gp|| + parent radius); empty -> 0.  Also
+ * refreshes the ||c||^2 caches. */
+int hira_recompute_radii(const hira_index_t* index, void* stream);
+
+/* Gather the stored keys/values back into token order (slot2token) for a
+ * rebuild: out_k [n_heads][n_out][dim]; rows of tokens not present are left
+ * untouched.  token_base is subtracted from slot2token. */
+int hira_export(const hira_index_t* index, int32_t token_base, int32_t n_out,
+                void* out_k, void* out_v, void* stream);
+
+/* Nearest-centroid assignment on its own (the dense contraction of the build,
+ * torch.cdist + argmin at indexer/cuda.py:244-245): for each point the index
+ * of the centroid minimising ||c||^2 - 2 x.c (ties -> lowest index) and that
+ * minimum plus ||x||^2 clamped at 0 (squared distance).
+ *   points [n_heads][n][dim], cents [n_heads][k][dim] in `dtype` (dense);
+ *   csq_scratch: n_heads*k floats of scratch (receives ||c||^2). */
+int hira_assign(const void* points, const void* cents, int32_t dtype,
+                int32_t n_heads, int32_t n, int32_t k, int32_t dim,
+                int32_t use_tensor_cores, float* csq_scratch, int32_t* out_idx,
+                float* out_dist2, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HIRA_B200_H */

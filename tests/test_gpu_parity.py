@@ -1,0 +1,294 @@
+"""CUDA library vs CPU oracle on the same seeded inputs, through the C ABI.  Integer and
+index results (selected slots, layouts, counts) and fp32 scores must be bit-exact;
+attention outputs within the stated tolerances (1e-5 fp32, 2e-3 relative bf16)."""
+import numpy as np
+import pytest
+import torch
+
+from hira_b200 import _lib as L
+from hira_b200 import index_state as S
+from oracle import oracle as O
+
+from util import (assert_index_equal, build_both, compact_sets, exact_tau, make_keys, make_queries, new_state)
+
+pytestmark = pytest.mark.gpu
+
+BUILD_CASES = [
+    # h, n, d, bf, depth, dtype, n_iters
+    (2, 256, 32, 8, 2, torch.float32, 1),
+    (3, 1000, 64, 8, 3, torch.float32, 1),
+    (2, 777, 128, 16, 3, torch.bfloat16, 1),
+    (2, 1024, 128, 32, 3, torch.bfloat16, 2),
+    (1, 130, 16, 10, 2, torch.float32, 3),
+    (2, 4096, 128, 64, 2, torch.float32, 1),
+    (1, 300, 256, 4, 3, torch.bfloat16, 1),
+]
+
+
+@pytest.mark.parametrize("h,n,d,bf,depth,dtype,n_iters", BUILD_CASES)
+def test_build_matches_oracle(h, n, d, bf, depth, dtype, n_iters):
+    st, ox, keys, vals = build_both(h, n, d, bf, depth, dtype, seed=7, n_iters=n_iters, spare=2 * bf)
+    assert_index_equal(st, ox, "build")
+    # structural invariants the reference's tests pin (tests/test_cuda_indexer_searcher.py:134-195)
+    assert int((st.slot2token >= 0).sum()) == h * n
+    assert int(st.child_counts.sum()) == h * n
+    assert int(st.child_counts.max()) <= bf
+
+
+SEARCH_CASES = [
+    # h, n, d, bf, depth, dtype, group
+    (2, 512, 32, 8, 2, torch.float32, 1),
+    (2, 1000, 64, 8, 3, torch.float32, 2),
+    (2, 2048, 128, 32, 3, torch.bfloat16, 4),
+    (1, 4096, 128, 64, 3, torch.bfloat16, 8),
+    (2, 900, 128, 16, 2, torch.bfloat16, 3),
+    (1, 640, 128, 4, 3, torch.float32, 12),
+    (2, 700, 256, 10, 3, torch.float32, 4),
+    (1, 300, 64, 1, 2, torch.float32, 2),
+]
+FLAG_CASES = [
+    L.HIRA_GATE_GT | L.HIRA_LEAF_CANDIDATES,
+    L.HIRA_GATE_GE | L.HIRA_LEAF_GE,
+    L.HIRA_GATE_GT | L.HIRA_LEAF_GT,
+]
+
+
+def _run_search_case(st, ox, q, tau, flags, scaling=None, qnorm=None, q2kv=None, max_group=0):
+    hq = q.shape[0]
+    dense = torch.full((hq, st.cap_children), float("nan"), device="cuda")
+    stats = torch.zeros((hq, 8), dtype=torch.int32, device="cuda")
+    _, compact = S.search(st, q, tau, scaling=scaling, qnorm=qnorm, q2kv=q2kv, max_group=max_group, flags=flags,
+                          out_dense=dense, want_compact=True, stats=stats)
+    torch.cuda.synchronize()
+    o_dense, o_keep, o_stats = O.search(ox, q, tau, scaling=scaling, qnorm=qnorm, q2kv=q2kv, flags=flags,
+                                        want_stats=True)
+    d = dense.cpu().numpy()
+    assert np.array_equal(d.view(np.uint32), o_dense.view(np.uint32)), "dense output differs from the oracle"
+    sets = compact_sets(compact)
+    for qh in range(hq):
+        slots, scores = sets[qh]
+        want = np.nonzero(o_keep[qh])[0]
+        assert np.array_equal(slots, want), f"head {qh}: selected slots differ ({len(slots)} vs {len(want)})"
+        assert np.array_equal(scores.view(np.uint32), o_dense[qh, want].view(np.uint32))
+    s = stats.cpu().numpy().astype(np.uint32)
+    assert np.array_equal(s[:, :6], o_stats[:, :6]), "visit counters differ"
+    return o_keep
+
+
+@pytest.mark.parametrize("h,n,d,bf,depth,dtype,group", SEARCH_CASES)
+@pytest.mark.parametrize("flags", FLAG_CASES)
+def test_search_matches_oracle(h, n, d, bf, depth, dtype, group, flags):
+    st, ox, keys, vals = build_both(h, n, d, bf, depth, dtype, seed=11, spare=bf)
+    hq = h * group
+    q = make_queries(hq, d, seed=5)
+    sc = torch.einsum("hnd,hgd->hgn", keys.float(), q.view(h, group, d)).reshape(hq, n).cpu().numpy()
+    # threshold = one of the canonical scores themselves (the 10% boundary), so that the
+    # >= / > edge is exercised with a key sitting exactly on it
+    all_d, all_k = O.search(ox, q, np.full((hq,), -np.inf, np.float32), flags=O.GATE_GT)
+    tau_np = np.stack([exact_tau(all_d[i][all_k[i] > 0][None, :], 0.10)[0] for i in range(hq)])
+    tau = torch.from_numpy(tau_np).cuda()
+    scaling = torch.linspace(0.5, 2.0, hq, device="cuda")
+    keep = _run_search_case(st, ox, q, tau, flags, scaling=scaling)
+    if flags & L.HIRA_LEAF_GE:
+        # against brute force in token space, away from the boundary: every key with
+        # score > tau + eps is selected, none with score < tau - eps
+        s2t = ox.slot2token
+        for qh in range(hq):
+            toks = set(s2t[qh // group, np.nonzero(keep[qh])[0]].tolist())
+            must = set(np.nonzero(sc[qh] > tau[qh].item() + 1e-5)[0].tolist())
+            never = set(np.nonzero(sc[qh] < tau[qh].item() - 1e-5)[0].tolist())
+            assert must <= toks and not (toks & never)
+
+
+def test_search_explicit_map_qnorm_and_empty():
+    h, n, d, bf = 2, 1536, 128, 16
+    st, ox, keys, _ = build_both(h, n, d, bf, 3, torch.bfloat16, seed=21, spare=bf)
+    hq = 6
+    q = make_queries(hq, d, seed=9, normalize=False)
+    q2kv = torch.tensor([1, 0, 1, 1, 0, 1], dtype=torch.int32, device="cuda")  # non-monotone, uneven groups
+    qn = q.norm(dim=-1).contiguous()
+    tau = torch.tensor([0.5, 1.0, -1e30, 1e30, 0.0, 2.0], device="cuda")  # includes keep-all and keep-none
+    for flags in FLAG_CASES:
+        _run_search_case(st, ox, q, tau, flags, qnorm=qn, q2kv=q2kv, max_group=4)
+        _run_search_case(st, ox, q, tau, flags, qnorm=None, q2kv=q2kv, max_group=0)
+
+
+def test_search_is_deterministic():
+    st, ox, keys, _ = build_both(2, 2048, 128, 32, 3, torch.bfloat16, seed=3)
+    q = make_queries(8, 128, seed=1)
+    tau = torch.full((8,), 0.05, device="cuda")
+    outs = []
+    for _ in range(2):
+        _, c = S.search(st, q, tau, flags=L.HIRA_GATE_GE | L.HIRA_LEAF_GE, want_compact=True)
+        torch.cuda.synchronize()
+        outs.append((c.idx.clone(), c.score.clone(), c.count.clone()))
+    assert torch.equal(outs[0][2], outs[1][2])
+    for (a, b) in zip(compact_sets(S.CompactResult(*outs[0], c.tile_parents, c.tile_rows)),
+                      compact_sets(S.CompactResult(*outs[1], c.tile_parents, c.tile_rows))):
+        assert np.array_equal(a[0], b[0]) and np.array_equal(a[1].view(np.uint32), b[1].view(np.uint32))
+
+
+APPEND_CASES = [
+    (2, 256, 32, 8, 2, torch.float32, 40),
+    (2, 500, 64, 8, 3, torch.float32, 70),
+    (3, 1024, 128, 32, 3, torch.bfloat16, 100),
+    (1, 100, 128, 4, 3, torch.bfloat16, 60),
+]
+
+
+@pytest.mark.parametrize("h,n,d,bf,depth,dtype,m", APPEND_CASES)
+def test_append_matches_oracle(h, n, d, bf, depth, dtype, m):
+    st, ox, keys, vals = build_both(h, n, d, bf, depth, dtype, seed=31, spare=(m + 1) * bf)
+    new_k = make_keys(h, m, d, 77, dtype)
+    new_v = make_keys(h, m, d, 78, dtype, normalize=False)
+    # one key per call (the decode pattern), then a batch
+    half = m // 2
+    for i in range(half):
+        S.append(st, new_k[:, i:i + 1].contiguous(), new_v[:, i:i + 1].contiguous())
+        O.append(ox, new_k[:, i:i + 1].contiguous(), new_v[:, i:i + 1].contiguous())
+    S.append(st, new_k[:, half:].contiguous(), new_v[:, half:].contiguous())
+    O.append(ox, new_k[:, half:].contiguous(), new_v[:, half:].contiguous())
+    torch.cuda.synchronize()
+    assert int(st.status.item()) == 0 and int(ox.status[0]) == 0
+    assert_index_equal(st, ox, "append")
+    assert int((st.slot2token >= 0).sum()) == h * (n + m)
+    # incrementally widened radii bound the radii recomputed from the layout
+    r_inc = st.parent_radii.clone()
+    S.recompute_radii(st)
+    O.recompute_radii(ox)
+    torch.cuda.synchronize()
+    assert_index_equal(st, ox, "radii")
+    assert bool((r_inc >= st.parent_radii - 1e-6).all())
+    # search after append still equals the oracle
+    q = make_queries(h * 2, d, seed=4)
+    tau = torch.full((h * 2,), 0.1, device="cuda")
+    _run_search_case(st, ox, q, tau, L.HIRA_GATE_GE | L.HIRA_LEAF_GE)
+
+
+def test_append_capacity_status():
+    h, n, d, bf = 1, 64, 32, 8
+    st, ox, keys, vals = build_both(h, n, d, bf, 2, torch.float32, seed=5, spare=2)
+    new_k = make_keys(h, 8, d, 91) * 50.0  # far from everything: each becomes its own parent
+    new_v = make_keys(h, 8, d, 92)
+    S.append(st, new_k, new_v)
+    O.append(ox, new_k, new_v)
+    torch.cuda.synchronize()
+    assert int(st.status.item()) == int(ox.status[0]) != 0
+    assert_index_equal(st, ox, "append at capacity")
+
+
+ATTN_CASES = [
+    (2, 2048, 128, 32, 3, torch.float32, 4, 0, 1e-5),
+    (2, 2048, 128, 32, 3, torch.bfloat16, 4, 5, 2e-3),
+    (1, 4096, 64, 8, 2, torch.bfloat16, 2, 0, 2e-3),
+    (2, 600, 128, 16, 3, torch.float32, 1, 33, 1e-5),
+]
+
+
+@pytest.mark.parametrize("h,n,d,bf,depth,dtype,group,n_queued,tol", ATTN_CASES)
+@pytest.mark.parametrize("n_splits", [1, 3, None])
+def test_sparse_attention_matches_oracle(h, n, d, bf, depth, dtype, group, n_queued, tol, n_splits):
+    st, ox, keys, vals = build_both(h, n, d, bf, depth, dtype, seed=41)
+    hq = h * group
+    q = make_queries(hq, d, seed=6)
+    sc = torch.einsum("hnd,hgd->hgn", keys.float(), q.view(h, group, d)).reshape(hq, n).cpu().numpy()
+    tau = torch.from_numpy(exact_tau(sc, 0.05)).cuda()
+    scaling = torch.full((hq,), 8.0, device="cuda")
+    _, compact = S.search(st, q, tau, scaling=scaling, flags=L.HIRA_GATE_GE | L.HIRA_LEAF_GE, want_compact=True)
+    qk = make_keys(h, n_queued, d, 55, dtype) if n_queued else None
+    qv = make_keys(h, n_queued, d, 56, dtype, normalize=False) if n_queued else None
+    ml = torch.zeros((hq, 2), device="cuda")
+    out = S.sparse_attn(st, q, scaling, compact, queued_k=qk, queued_v=qv, n_splits=n_splits, out_ml=ml)
+    torch.cuda.synchronize()
+    o_dense, o_keep = O.search(ox, q, tau, scaling=scaling, flags=O.GATE_GE | O.LEAF_GE)
+    want, want_ml = O.attention(ox, q, scaling, o_dense, o_keep, queued_k=qk, queued_v=qv)
+    got = out.cpu().numpy()
+    denom = np.abs(want).max(axis=-1, keepdims=True) + 1e-6
+    assert np.max(np.abs(got - want) / denom) < tol
+    got_ml = ml.cpu().numpy()
+    np.testing.assert_allclose(got_ml[:, 0], want_ml[:, 0], rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(got_ml[:, 1], want_ml[:, 1], rtol=1e-4)
+
+
+def test_attention_with_nothing_selected_is_zero():
+    st, ox, keys, vals = build_both(1, 512, 128, 16, 3, torch.bfloat16, seed=1)
+    q = make_queries(2, 128, seed=2)
+    tau = torch.full((2,), 1e30, device="cuda")
+    _, compact = S.search(st, q, tau, flags=L.HIRA_GATE_GE | L.HIRA_LEAF_GE, want_compact=True)
+    out = S.sparse_attn(st, q, None, compact)
+    torch.cuda.synchronize()
+    assert float(out.abs().max()) == 0.0
+
+
+def test_merge_partials_matches_oracle():
+    g = torch.Generator().manual_seed(0)
+    po = torch.randn((4, 6, 128), generator=g)
+    pml = torch.stack([torch.randn((4, 6), generator=g) * 5, torch.rand((4, 6), generator=g) * 100 + 1], dim=-1)
+    pml[1, 2, 0] = float("-inf")
+    pml[1, 2, 1] = 0.0
+    ml = torch.zeros((6, 2), device="cuda")
+    out = S.merge_partials(po.cuda().contiguous(), pml.cuda().contiguous(), out_ml=ml)
+    torch.cuda.synchronize()
+    want, want_ml = O.merge_partials(po, pml)
+    np.testing.assert_allclose(out.cpu().numpy(), want, rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(ml.cpu().numpy(), want_ml, rtol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("s,k", [(1000, 16), (64, 64), (4096, 1), (37, 5)])
+def test_threshold_matches_oracle(dtype, s, k):
+    h, d, group = 2, 128, 3
+    samples = make_keys(h, s, d, 13, dtype)
+    q = make_queries(h * group, d, seed=14)
+    for method in (L.HIRA_TAU_SAMPLE_MAX, L.HIRA_TAU_SAMPLE_MEAN_TOPK, L.HIRA_TAU_SAMPLE_KTH):
+        got = S.threshold(samples, q, method, k).cpu().numpy()
+        want = O.threshold(samples, q, method, k)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"method {method}"
+
+
+def test_kth_score_is_exact():
+    h, n, d, bf, group = 2, 3000, 128, 32, 2
+    st, ox, keys, _ = build_both(h, n, d, bf, 3, torch.bfloat16, seed=17)
+    hq = h * group
+    q = make_queries(hq, d, seed=18)
+    tau = torch.full((hq,), float("-inf"), device="cuda")
+    _, compact = S.search(st, q, tau, flags=L.HIRA_GATE_GT | L.HIRA_LEAF_CANDIDATES, want_compact=True)
+    k = torch.tensor([1, 60, 3000, 3001], dtype=torch.int32, device="cuda")
+    got = S.kth_score(st, compact, k).cpu().numpy()
+    o_dense, o_keep = O.search(ox, q, tau, flags=O.GATE_GT)
+    for qh in range(hq):
+        s = np.sort(o_dense[qh][o_keep[qh] > 0])[::-1]
+        kk = int(k[qh])
+        want = s[kk - 1] if kk <= len(s) else -np.inf
+        assert got[qh] == want
+
+
+def test_assign_matches_oracle():
+    for dtype in (torch.float32, torch.bfloat16):
+        pts = make_keys(2, 700, 128, 23, dtype)
+        cents = make_keys(2, 90, 128, 24, dtype)
+        idx, d2 = S.assign(pts, cents, use_tensor_cores=False)
+        torch.cuda.synchronize()
+        o_idx, o_d2 = O.assign(pts, cents)
+        assert np.array_equal(idx.cpu().numpy(), o_idx)
+        assert np.array_equal(d2.cpu().numpy().view(np.uint32), o_d2.view(np.uint32))
+
+
+def test_export_roundtrip():
+    st, ox, keys, vals = build_both(2, 500, 64, 8, 3, torch.bfloat16, seed=29)
+    k, v = S.export(st, 500)
+    torch.cuda.synchronize()
+    assert torch.equal(k, keys) and torch.equal(v, vals)
+
+
+def test_bad_arguments_raise():
+    st = new_state(1, 32, 8, 2, 4, torch.float32)
+    q = make_queries(2, 32, seed=1)
+    tau = torch.zeros((2,), device="cuda")
+    with pytest.raises(ValueError):
+        S.search(st, q, tau, flags=0x40, want_compact=True)
+    with pytest.raises(ValueError):
+        S.search(st, q, tau, flags=0)  # no output buffer
+    st2 = new_state(2, 32, 8, 2, 4, torch.float32)
+    with pytest.raises(ValueError):  # 3 query heads over 2 kv heads without a map
+        S.search(st2, make_queries(3, 32, seed=1), torch.zeros((3,), device="cuda"), want_compact=True)

@@ -144,7 +144,10 @@ assign_kernel(const T* __restrict__ points, long long p_head_stride, const T* __
 template <typename T>
 static int launch_assign_cc(const T* points, long long p_head_stride, const T* cents, const float* csq,
                             int n_heads, int n, int k, int dim, int32_t* out_idx, float* out_d2, cudaStream_t s) {
-    const size_t smem = (size_t)(AS_PTS + AS_CTS) * (dim + 1) * sizeof(float);
+    // points tile + the larger of (centre tile, the 2 x [AS_PTS][16] reduction arrays that reuse it)
+    const size_t cs_floats = (size_t)AS_CTS * (dim + 1) > (size_t)2 * AS_PTS * 16 ? (size_t)AS_CTS * (dim + 1)
+                                                                                  : (size_t)2 * AS_PTS * 16;
+    const size_t smem = ((size_t)AS_PTS * (dim + 1) + cs_floats) * sizeof(float);
     auto kern = assign_kernel<T>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

@@ -204,7 +204,9 @@ search_kernel(const SearchParams P) {
                 const uint32_t m = head_mask_from_ballot<GT>(b, tid);
                 if (lane == 0 && i < ng) {
                     s_gpmask[i] = (unsigned char)m;
-                    if (valid && P.stats) {
+                    // a grandparent whose parents span several tiles is gated by each of
+                    // them; only the tile holding its first parent books the visit
+                    if (valid && P.stats && (tile_p0 % bf) == 0) {
                         for (int jj = 0; jj < nq; ++jj) {
                             atomicAdd(&s_stat[jj][0], 1u);
                             if ((m >> jj) & 1u) atomicAdd(&s_stat[jj][1], 1u);

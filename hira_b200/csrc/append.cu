@@ -20,7 +20,7 @@
 namespace hira {
 
 constexpr int APPEND_THREADS = 512;
-constexpr int APPEND_HW = APPEND_THREADS / 16;
+constexpr int APPEND_HW = APPEND_THREADS / GROUP;  // 8-lane groups: one centre row per group per step
 constexpr int APPEND_UNROLL = 4;
 
 struct AppendParams {
@@ -43,7 +43,7 @@ __device__ __forceinline__ bool better(float s, int i, const Best& b) {
 template <typename T, int NCH, typename Valid>
 __device__ Best nearest_row(const T* rows, const float* sq, int n, const float (&x)[NCH][8], int dim,
                             Valid valid, Best* s_best) {
-    const int tid = threadIdx.x, lane = tid & 15, hw = tid >> 4;
+    const int tid = threadIdx.x, lane = tid & (GROUP - 1), hw = tid / GROUP;
     Best best{CUDART_INF_F, 0x7fffffff};
     for (int p0 = 0; p0 < n; p0 += APPEND_HW * APPEND_UNROLL) {  // uniform trip count
         RawChunk<T> raw[APPEND_UNROLL][NCH];
@@ -54,7 +54,7 @@ __device__ Best nearest_row(const T* rows, const float* sq, int n, const float (
             ok[u] = p < n && valid(p);
 #pragma unroll
             for (int i = 0; i < NCH; ++i) {
-                const int c = lane + 16 * i;
+                const int c = lane + GROUP * i;
                 if (ok[u] && c * 8 < dim) raw[u][i] = load_chunk_coherent<T>(rows + (size_t)p * dim, c);
                 else raw[u][i] = zero_chunk<T>();
             }
@@ -69,7 +69,7 @@ __device__ Best nearest_row(const T* rows, const float* sq, int n, const float (
                 to_float(raw[u][i], a);
                 chunk_fma(acc, a, x[i]);
             }
-            const float d = halfwarp_sum(__fadd_rn(acc.e, acc.o));
+            const float d = group_sum(__fadd_rn(acc.e, acc.o));
             if (ok[u]) {
                 const float s = __fsub_rn(sq[p], __fmul_rn(2.0f, d));
                 if (better(s, p, best)) best = Best{s, p};
@@ -92,7 +92,7 @@ append_kernel(const AppendParams P) {
     __shared__ Best s_best[APPEND_HW];
     const hira_index_t& ix = P.ix;
     const int h = blockIdx.x;
-    const int tid = threadIdx.x, lane = tid & 15, hw = tid >> 4;
+    const int tid = threadIdx.x, lane = tid & (GROUP - 1), hw = tid / GROUP;
     const int bf = ix.bf, dim = ix.dim, vdim = ix.vdim;
     const size_t capP = ix.cap_parents, capC = capP * bf, capG = ix.cap_gp;
     T* children = reinterpret_cast<T*>(ix.children) + (size_t)h * capC * dim;
@@ -170,13 +170,13 @@ append_kernel(const AppendParams P) {
                 if (hw == 0) {
 #pragma unroll
                     for (int i = 0; i < NCH; ++i) {
-                        const int c = lane + 16 * i;
+                        const int c = lane + GROUP * i;
                         if (c * 8 < dim) store_chunk(children + (size_t)slot * dim, c, x[i]);
                     }
                     if (values) {
 #pragma unroll
                         for (int i = 0; i < NVCH; ++i) {
-                            const int c = lane + 16 * i;
+                            const int c = lane + GROUP * i;
                             if (c * 8 < vdim) {
                                 float v[8];
                                 to_float(load_chunk<TV>(new_v + (size_t)key * vdim, c), v);
@@ -203,7 +203,7 @@ append_kernel(const AppendParams P) {
                 if (hw == 0) {
 #pragma unroll
                     for (int i = 0; i < NCH; ++i) {
-                        const int c = lane + 16 * i;
+                        const int c = lane + GROUP * i;
                         if (c * 8 < dim) {
                             store_chunk(children + (size_t)slot * dim, c, x[i]);
                             store_chunk(parents + (size_t)p_dst * dim, c, x[i]);
@@ -213,7 +213,7 @@ append_kernel(const AppendParams P) {
                     if (values) {
 #pragma unroll
                         for (int i = 0; i < NVCH; ++i) {
-                            const int c = lane + 16 * i;
+                            const int c = lane + GROUP * i;
                             if (c * 8 < vdim) {
                                 float v[8];
                                 to_float(load_chunk<TV>(new_v + (size_t)key * vdim, c), v);
@@ -249,12 +249,12 @@ append_kernel(const AppendParams P) {
 
 template <typename T, typename TV>
 static int launch_append(const AppendParams& P, cudaStream_t s) {
-    const bool k2 = P.ix.dim > 128, v2 = P.ix.vdim > 128;
+    const bool k2 = P.ix.dim > 128, v2 = P.ix.vdim > 128;   // chunks per lane: 2 up to 128 elements, else 4
     const int grid = P.ix.n_heads;
-    if (!k2 && !v2) append_kernel<T, TV, 1, 1><<<grid, APPEND_THREADS, 0, s>>>(P);
-    else if (k2 && !v2) append_kernel<T, TV, 2, 1><<<grid, APPEND_THREADS, 0, s>>>(P);
-    else if (!k2 && v2) append_kernel<T, TV, 1, 2><<<grid, APPEND_THREADS, 0, s>>>(P);
-    else append_kernel<T, TV, 2, 2><<<grid, APPEND_THREADS, 0, s>>>(P);
+    if (!k2 && !v2) append_kernel<T, TV, 2, 2><<<grid, APPEND_THREADS, 0, s>>>(P);
+    else if (k2 && !v2) append_kernel<T, TV, 4, 2><<<grid, APPEND_THREADS, 0, s>>>(P);
+    else if (!k2 && v2) append_kernel<T, TV, 2, 4><<<grid, APPEND_THREADS, 0, s>>>(P);
+    else append_kernel<T, TV, 4, 4><<<grid, APPEND_THREADS, 0, s>>>(P);
     HIRA_CHECK_LAUNCH("hira_append launch");
     return HIRA_OK;
 }

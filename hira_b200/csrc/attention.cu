@@ -7,8 +7,8 @@
 // sit in the same slots as the keys (indexer/cuda.py:397-423), and the keys not
 // yet indexed arrive as a dense queue (cache/hira_cache.py:121-140).
 //
-// One CTA per (query head, split of the tile range).  16-lane groups each
-// gather one value row (256 B for V=128 bf16) with a 128-bit load per lane,
+// One CTA per (query head, split of the tile range).  8-lane groups each
+// gather one value row (256 B for V=128 bf16) with two 128-bit loads per lane,
 // four rows in flight per thread; softmax is online in fp32.
 #include "common.cuh"
 #include <math_constants.h>
@@ -16,7 +16,7 @@
 namespace hira {
 
 constexpr int ATTN_THREADS = 256;
-constexpr int ATTN_HW = ATTN_THREADS / 16;
+constexpr int ATTN_HW = ATTN_THREADS / GROUP;  // 8-lane groups: one value row per group per step
 constexpr int ATTN_CHUNK = 2048;  // list entries staged in shared memory (>= rows of one search tile)
 constexpr int ATTN_UNROLL = 4;
 constexpr int QUEUE_FLAG = 0x40000000;
@@ -58,8 +58,8 @@ sparse_attn_kernel(const AttnParams P) {
     extern __shared__ __align__(16) float s_out[];  // [ATTN_HW][vdim]
 
     const int tid = threadIdx.x;
-    const int lane = tid & 15;
-    const int hw = tid >> 4;
+    const int lane = tid & (GROUP - 1);
+    const int hw = tid / GROUP;
     const int qh = blockIdx.y;
     const int split = blockIdx.x;
     const int h = P.q2kv ? P.q2kv[qh] : qh / P.group;
@@ -120,7 +120,7 @@ sparse_attn_kernel(const AttnParams P) {
                     }
 #pragma unroll
                     for (int i = 0; i < NVCH; ++i) {
-                        const int c = lane + 16 * i;
+                        const int c = lane + GROUP * i;
                         if (row != nullptr && c * 8 < P.vdim) raw[u][i] = load_chunk_stream<TV>(row, c);
                         else raw[u][i] = zero_chunk<TV>();
                     }
@@ -167,7 +167,7 @@ sparse_attn_kernel(const AttnParams P) {
                     if (j < n) {
 #pragma unroll
                         for (int i = 0; i < NCH; ++i) {
-                            const int c = lane + 16 * i;
+                            const int c = lane + GROUP * i;
                             if (c * 8 < P.dim) {
                                 float a[8];
                                 to_float(load_chunk<TK>(qk + (size_t)(j0 + j) * P.dim, c), a);
@@ -175,7 +175,7 @@ sparse_attn_kernel(const AttnParams P) {
                             }
                         }
                     }
-                    d = halfwarp_sum(__fadd_rn(a2.e, a2.o));
+                    d = group_sum(__fadd_rn(a2.e, a2.o));
                 }
                 if (lane == 0 && j < n) {
                     s_idx[fill + j] = QUEUE_FLAG | (j0 + j);
@@ -192,7 +192,7 @@ sparse_attn_kernel(const AttnParams P) {
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < NVCH; ++i) {
-        const int c = lane + 16 * i;
+        const int c = lane + GROUP * i;
         if (c * 8 < P.vdim) {
 #pragma unroll
             for (int e = 0; e < 8; ++e) s_out[(size_t)hw * P.vdim + c * 8 + e] = acc[i][e];
@@ -255,11 +255,11 @@ template <typename TK, typename TV>
 static int launch_attn(const AttnParams& P, cudaStream_t s) {
     dim3 grid((unsigned)P.n_splits, (unsigned)P.n_qheads);
     const size_t smem = (size_t)ATTN_HW * P.vdim * sizeof(float);
-    const bool k2 = P.dim > 128, v2 = P.vdim > 128;
-    if (!k2 && !v2) sparse_attn_kernel<TK, TV, 1, 1><<<grid, ATTN_THREADS, smem, s>>>(P);
-    else if (k2 && !v2) sparse_attn_kernel<TK, TV, 2, 1><<<grid, ATTN_THREADS, smem, s>>>(P);
-    else if (!k2 && v2) sparse_attn_kernel<TK, TV, 1, 2><<<grid, ATTN_THREADS, smem, s>>>(P);
-    else sparse_attn_kernel<TK, TV, 2, 2><<<grid, ATTN_THREADS, smem, s>>>(P);
+    const bool k2 = P.dim > 128, v2 = P.vdim > 128;   // chunks per lane: 2 up to 128 elements, else 4
+    if (!k2 && !v2) sparse_attn_kernel<TK, TV, 2, 2><<<grid, ATTN_THREADS, smem, s>>>(P);
+    else if (k2 && !v2) sparse_attn_kernel<TK, TV, 4, 2><<<grid, ATTN_THREADS, smem, s>>>(P);
+    else if (!k2 && v2) sparse_attn_kernel<TK, TV, 2, 4><<<grid, ATTN_THREADS, smem, s>>>(P);
+    else sparse_attn_kernel<TK, TV, 4, 4><<<grid, ATTN_THREADS, smem, s>>>(P);
     HIRA_CHECK_LAUNCH("hira_sparse_attn launch");
     return HIRA_OK;
 }

@@ -223,13 +223,13 @@ __global__ void segment_starts_kernel(const uint64_t* __restrict__ keys, long lo
     for (long long s = prev + 1; s <= cur; ++s) start[s] = (int32_t)i;
 }
 
-// Lloyd mean update: one half-warp per centre, members added in sorted order
+// Lloyd mean update: one 8-lane group per centre, members added in sorted order
 template <typename T, int NCH>
 __global__ void means_kernel(const T* __restrict__ points, long long p_head_stride, int n,
                              const uint32_t* __restrict__ sorted_ids, const int32_t* __restrict__ start, int k,
                              int dim, long long n_seg, T* __restrict__ cents) {
-    const int lane = threadIdx.x & 15;
-    const long long seg = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 4;
+    const int lane = threadIdx.x & (GROUP - 1);
+    const long long seg = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / GROUP;
     if (seg >= n_seg) return;
     const int h = (int)(seg / k);
     const int b = start[seg], e = start[seg + 1];
@@ -244,7 +244,7 @@ __global__ void means_kernel(const T* __restrict__ points, long long p_head_stri
         const uint32_t id = sorted_ids[m];
 #pragma unroll
         for (int i = 0; i < NCH; ++i) {
-            const int c = lane + 16 * i;
+            const int c = lane + GROUP * i;
             if (c * 8 < dim) {
                 float a[8];
                 to_float(load_chunk<T>(P + (size_t)id * dim, c), a);
@@ -256,7 +256,7 @@ __global__ void means_kernel(const T* __restrict__ points, long long p_head_stri
     const float cnt = (float)(e - b);
 #pragma unroll
     for (int i = 0; i < NCH; ++i) {
-        const int c = lane + 16 * i;
+        const int c = lane + GROUP * i;
         if (c * 8 < dim) {
             float o[8];
 #pragma unroll
@@ -407,8 +407,8 @@ __global__ void set_used_kernel(int32_t* used, int n_heads, int used_p, int used
 // ---------------------------------------------------------------------------
 template <typename T, int NCH>
 __global__ void parent_radii_kernel(const hira_index_t ix) {
-    const int lane = threadIdx.x & 15;
-    const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 4;  // (head, parent)
+    const int lane = threadIdx.x & (GROUP - 1);
+    const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / GROUP;  // (head, parent)
     if (w >= (long long)ix.n_heads * ix.cap_parents) return;
     const int h = (int)(w / ix.cap_parents), p = (int)(w % ix.cap_parents);
     const int bf = ix.bf, dim = ix.dim;
@@ -441,8 +441,8 @@ __global__ void parent_radii_kernel(const hira_index_t ix) {
 
 template <typename T, int NCH>
 __global__ void gp_radii_kernel(const hira_index_t ix) {
-    const int lane = threadIdx.x & 15;
-    const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 4;  // (head, gp)
+    const int lane = threadIdx.x & (GROUP - 1);
+    const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) / GROUP;  // (head, gp)
     if (w >= (long long)ix.n_heads * ix.cap_gp) return;
     const int h = (int)(w / ix.cap_gp), g = (int)(w % ix.cap_gp);
     const int bf = ix.bf, dim = ix.dim;
@@ -471,15 +471,15 @@ __global__ void gp_radii_kernel(const hira_index_t ix) {
 template <typename T>
 static int launch_radii(const hira_index_t* ix, cudaStream_t s) {
     const long long hw_p = (long long)ix->n_heads * ix->cap_parents;
-    const int blocks_p = (int)((hw_p * 16 + 255) / 256);
-    if (ix->dim > 128) parent_radii_kernel<T, 2><<<blocks_p, 256, 0, s>>>(*ix);
-    else parent_radii_kernel<T, 1><<<blocks_p, 256, 0, s>>>(*ix);
+    const int blocks_p = (int)((hw_p * GROUP + 255) / 256);
+    if (ix->dim > 128) parent_radii_kernel<T, 4><<<blocks_p, 256, 0, s>>>(*ix);
+    else parent_radii_kernel<T, 2><<<blocks_p, 256, 0, s>>>(*ix);
     HIRA_CHECK_LAUNCH("parent radii launch");
     if (ix->depth == 3) {
         const long long hw_g = (long long)ix->n_heads * ix->cap_gp;
-        const int blocks_g = (int)((hw_g * 16 + 255) / 256);
-        if (ix->dim > 128) gp_radii_kernel<T, 2><<<blocks_g, 256, 0, s>>>(*ix);
-        else gp_radii_kernel<T, 1><<<blocks_g, 256, 0, s>>>(*ix);
+        const int blocks_g = (int)((hw_g * GROUP + 255) / 256);
+        if (ix->dim > 128) gp_radii_kernel<T, 4><<<blocks_g, 256, 0, s>>>(*ix);
+        else gp_radii_kernel<T, 2><<<blocks_g, 256, 0, s>>>(*ix);
         HIRA_CHECK_LAUNCH("grandparent radii launch");
     }
     return HIRA_OK;
@@ -591,9 +591,9 @@ static int build_level(int dtype, const T* points, long long p_head_stride, int 
         segment_starts_kernel<<<blocks1, 256, 0, s>>>(keys_out, total, n_seg, start);
         HIRA_CHECK_LAUNCH("segment starts launch");
         if (it + 1 < iters) {
-            const int mblocks = (int)((n_seg * 16 + 255) / 256);
-            if (dim > 128) means_kernel<T, 2><<<mblocks, 256, 0, s>>>(points, p_head_stride, n, vals_out, start, k, dim, n_seg, cents);
-            else means_kernel<T, 1><<<mblocks, 256, 0, s>>>(points, p_head_stride, n, vals_out, start, k, dim, n_seg, cents);
+            const int mblocks = (int)((n_seg * GROUP + 255) / 256);
+            if (dim > 128) means_kernel<T, 4><<<mblocks, 256, 0, s>>>(points, p_head_stride, n, vals_out, start, k, dim, n_seg, cents);
+            else means_kernel<T, 2><<<mblocks, 256, 0, s>>>(points, p_head_stride, n, vals_out, start, k, dim, n_seg, cents);
             HIRA_CHECK_LAUNCH("means launch");
         }
     }

@@ -2,16 +2,20 @@
 // canonical fp32 dot product that defines the library's bit-exact results.
 //
 // Canonical dot product of two D-vectors (D a multiple of 8, D <= 256),
-// evaluated by a group of 16 lanes ("half-warp"):
-//   lane l owns the 8-element chunks c with c % 16 == l  (elements 8c .. 8c+7);
+// evaluated by a group of 8 lanes (a quarter of a warp):
+//   lane l owns the 8-element chunks c with c % 8 == l  (elements 8c .. 8c+7);
 //   inside a lane two accumulators run over its chunks in increasing order:
 //     e = fma(a[8c+2j],   b[8c+2j],   e)      j = 0..3   (even elements)
 //     o = fma(a[8c+2j+1], b[8c+2j+1], o)                 (odd elements)
 //   the lane partial is p_l = e + o (lanes owning no chunk contribute +0);
-//   the 16 partials are summed by a butterfly: for s in 8,4,2,1: p_l += p_{l^s}.
+//   the 8 partials are summed by a butterfly: for s in 4,2,1: p_l += p_{l^s}.
 // All adds are IEEE fp32 round-to-nearest; the butterfly is symmetric, so every
 // lane ends with the same bits.  The CPU oracle evaluates the identical tree,
 // which is what makes selected-key sets bit-exact at the threshold boundary.
+// Eight lanes per row keep the shuffle count per row low (the search kernel is
+// close to instruction-issue bound) while every 16-byte load still sits in a
+// fully used 128-byte line: lanes 0..7 read bytes [0,128) of a bf16 row with
+// their first chunk and [128,256) with their second.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -43,6 +47,9 @@ void set_error(const char* fmt, ...);
     } while (0)
 
 int validate_index(const hira_index_t* ix, bool need_values);
+
+// chunks (of 8 elements) each of the 8 lanes owns: 1 for D <= 64, 2 for D <= 128, 4 for D <= 256
+__host__ __device__ inline int chunks_per_lane(int dim) { return dim <= 64 ? 1 : (dim <= 128 ? 2 : 4); }
 
 __host__ __device__ inline size_t elem_size(int dtype) { return dtype == HIRA_BF16 ? 2 : 4; }
 
@@ -177,70 +184,80 @@ __device__ __forceinline__ void chunk_fma(Acc2& acc, const float (&a)[8], const 
 }
 
 // butterfly over the 16 lanes of a half-warp; every lane gets the sum
-// Shuffles name only the 16 lanes of the caller's own half-warp, so the two
-// halves of a warp may diverge (different trip counts, early exit).
-__device__ __forceinline__ unsigned half_mask() { return 0xffffu << (threadIdx.x & 16); }
+// Shuffles name only the 8 lanes of the caller's own group, so the groups of a
+// warp may diverge (different trip counts, early exit).
+constexpr int GROUP = 8;  // lanes per row
+__device__ __forceinline__ unsigned group_mask() { return 0xffu << (threadIdx.x & 24); }
 
-__device__ __forceinline__ float halfwarp_sum(float p) {
-    const unsigned hm = half_mask();
-    p = __fadd_rn(p, __shfl_xor_sync(hm, p, 8));
-    p = __fadd_rn(p, __shfl_xor_sync(hm, p, 4));
-    p = __fadd_rn(p, __shfl_xor_sync(hm, p, 2));
-    p = __fadd_rn(p, __shfl_xor_sync(hm, p, 1));
+__device__ __forceinline__ float group_sum(float p) {
+    const unsigned gm = group_mask();
+    p = __fadd_rn(p, __shfl_xor_sync(gm, p, 4));
+    p = __fadd_rn(p, __shfl_xor_sync(gm, p, 2));
+    p = __fadd_rn(p, __shfl_xor_sync(gm, p, 1));
     return p;
 }
 
 // Same butterfly for G values at once with fewer shuffles (a reduce-scatter:
 // at each step a lane keeps half of its values and sends the other half).
-// On return the canonical sum of head j is in r for the lanes whose index
-// selects j (see owner_of<G>); adds are commutative so the bits equal
-// halfwarp_sum() of each value.
+// On return the canonical sum of head head_of_lane(lane) is in the result; adds
+// are commutative so the bits equal group_sum() of each value.  `gm` is the
+// shuffle mask: group_mask() where the groups of a warp may have diverged, the
+// full mask where the whole warp is known to be converged (cheaper: a variable
+// mask makes the compiler emit a membership check).
 template <int G> struct HeadReduce;
 template <> struct HeadReduce<1> {
-    static __device__ __forceinline__ float run(const float (&v)[1], int /*lane*/) { return halfwarp_sum(v[0]); }
+    static __device__ __forceinline__ float run(const float (&v)[1], int /*lane*/, unsigned gm) {
+        float p = v[0];
+        p = __fadd_rn(p, __shfl_xor_sync(gm, p, 4));
+        p = __fadd_rn(p, __shfl_xor_sync(gm, p, 2));
+        p = __fadd_rn(p, __shfl_xor_sync(gm, p, 1));
+        return p;
+    }
     static __device__ __forceinline__ int head_of_lane(int /*lane*/) { return 0; }
+    static __device__ __forceinline__ bool is_writer(int lane) { return lane == 0; }
+    static __device__ __forceinline__ int first_lane(int /*j*/) { return 0; }
 };
 template <> struct HeadReduce<2> {
-    static __device__ __forceinline__ float run(const float (&v)[2], int lane) {
-        const bool hi = lane & 8;
-        float send = hi ? v[0] : v[1];
-        float keep = hi ? v[1] : v[0];
-        float r = __fadd_rn(keep, __shfl_xor_sync(half_mask(), send, 8));
-        r = __fadd_rn(r, __shfl_xor_sync(half_mask(), r, 4));
-        r = __fadd_rn(r, __shfl_xor_sync(half_mask(), r, 2));
-        r = __fadd_rn(r, __shfl_xor_sync(half_mask(), r, 1));
+    static __device__ __forceinline__ float run(const float (&v)[2], int lane, unsigned gm) {
+        const bool hi = lane & 4;
+        float r = __fadd_rn(hi ? v[1] : v[0], __shfl_xor_sync(gm, hi ? v[0] : v[1], 4));
+        r = __fadd_rn(r, __shfl_xor_sync(gm, r, 2));
+        r = __fadd_rn(r, __shfl_xor_sync(gm, r, 1));
         return r;
     }
-    static __device__ __forceinline__ int head_of_lane(int lane) { return (lane >> 3) & 1; }
+    static __device__ __forceinline__ int head_of_lane(int lane) { return (lane >> 2) & 1; }
+    static __device__ __forceinline__ bool is_writer(int lane) { return (lane & 3) == 0; }
+    static __device__ __forceinline__ int first_lane(int j) { return j * 4; }
 };
 template <> struct HeadReduce<4> {
-    static __device__ __forceinline__ float run(const float (&v)[4], int lane) {
-        const bool b3 = lane & 8, b2 = lane & 4;
-        float a = __fadd_rn(b3 ? v[2] : v[0], __shfl_xor_sync(half_mask(), b3 ? v[0] : v[2], 8));
-        float b = __fadd_rn(b3 ? v[3] : v[1], __shfl_xor_sync(half_mask(), b3 ? v[1] : v[3], 8));
-        float r = __fadd_rn(b2 ? b : a, __shfl_xor_sync(half_mask(), b2 ? a : b, 4));
-        r = __fadd_rn(r, __shfl_xor_sync(half_mask(), r, 2));
-        r = __fadd_rn(r, __shfl_xor_sync(half_mask(), r, 1));
+    static __device__ __forceinline__ float run(const float (&v)[4], int lane, unsigned gm) {
+        const bool b2 = lane & 4, b1 = lane & 2;
+        float a = __fadd_rn(b2 ? v[2] : v[0], __shfl_xor_sync(gm, b2 ? v[0] : v[2], 4));
+        float b = __fadd_rn(b2 ? v[3] : v[1], __shfl_xor_sync(gm, b2 ? v[1] : v[3], 4));
+        float r = __fadd_rn(b1 ? b : a, __shfl_xor_sync(gm, b1 ? a : b, 2));
+        r = __fadd_rn(r, __shfl_xor_sync(gm, r, 1));
         return r;
     }
-    static __device__ __forceinline__ int head_of_lane(int lane) { return (lane >> 2) & 3; }
+    static __device__ __forceinline__ int head_of_lane(int lane) { return (lane >> 1) & 3; }
+    static __device__ __forceinline__ bool is_writer(int lane) { return (lane & 1) == 0; }
+    static __device__ __forceinline__ int first_lane(int j) { return j * 2; }
 };
 template <> struct HeadReduce<8> {
-    static __device__ __forceinline__ float run(const float (&v)[8], int lane) {
-        const bool b3 = lane & 8, b2 = lane & 4, b1 = lane & 2;
+    static __device__ __forceinline__ float run(const float (&v)[8], int lane, unsigned gm) {
+        const bool b2 = lane & 4, b1 = lane & 2, b0 = lane & 1;
         float w[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-            w[j] = __fadd_rn(b3 ? v[4 + j] : v[j], __shfl_xor_sync(half_mask(), b3 ? v[j] : v[4 + j], 8));
+            w[j] = __fadd_rn(b2 ? v[4 + j] : v[j], __shfl_xor_sync(gm, b2 ? v[j] : v[4 + j], 4));
         float x[2];
 #pragma unroll
         for (int j = 0; j < 2; ++j)
-            x[j] = __fadd_rn(b2 ? w[2 + j] : w[j], __shfl_xor_sync(half_mask(), b2 ? w[j] : w[2 + j], 4));
-        float r = __fadd_rn(b1 ? x[1] : x[0], __shfl_xor_sync(half_mask(), b1 ? x[0] : x[1], 2));
-        r = __fadd_rn(r, __shfl_xor_sync(half_mask(), r, 1));
-        return r;
+            x[j] = __fadd_rn(b1 ? w[2 + j] : w[j], __shfl_xor_sync(gm, b1 ? w[j] : w[2 + j], 2));
+        return __fadd_rn(b0 ? x[1] : x[0], __shfl_xor_sync(gm, b0 ? x[0] : x[1], 1));
     }
-    static __device__ __forceinline__ int head_of_lane(int lane) { return (lane >> 1) & 7; }
+    static __device__ __forceinline__ int head_of_lane(int lane) { return lane & 7; }
+    static __device__ __forceinline__ bool is_writer(int /*lane*/) { return true; }
+    static __device__ __forceinline__ int first_lane(int j) { return j; }
 };
 
 // canonical dot of a global row with a per-lane register copy of the other
@@ -250,14 +267,14 @@ __device__ __forceinline__ float row_dot(const T* row, const float (&b)[NCH][8],
     Acc2 acc{0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < NCH; ++i) {
-        const int c = lane + 16 * i;
+        const int c = lane + 8 * i;
         if (c * 8 < dim) {
             float a[8];
             to_float(load_chunk<T>(row, c), a);
             chunk_fma(acc, a, b[i]);
         }
     }
-    return halfwarp_sum(__fadd_rn(acc.e, acc.o));
+    return group_sum(__fadd_rn(acc.e, acc.o));
 }
 
 // canonical ||a - b||^2 for two global rows (fp32 difference, then the tree)
@@ -266,7 +283,7 @@ __device__ __forceinline__ float row_dist2(const TA* ra, const TB* rb, int lane,
     Acc2 acc{0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < NCH; ++i) {
-        const int c = lane + 16 * i;
+        const int c = lane + 8 * i;
         if (c * 8 < dim) {
             float a[8], b[8], d[8];
             to_float(load_chunk<TA>(ra, c), a);
@@ -276,7 +293,7 @@ __device__ __forceinline__ float row_dist2(const TA* ra, const TB* rb, int lane,
             chunk_fma(acc, d, d);
         }
     }
-    return halfwarp_sum(__fadd_rn(acc.e, acc.o));
+    return group_sum(__fadd_rn(acc.e, acc.o));
 }
 
 // the same with coherent loads, and against a register copy of one operand
@@ -285,7 +302,7 @@ __device__ __forceinline__ float row_dist2_reg(const T* row, const float (&x)[NC
     Acc2 acc{0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < NCH; ++i) {
-        const int c = lane + 16 * i;
+        const int c = lane + 8 * i;
         if (c * 8 < dim) {
             float a[8], d[8];
             to_float(load_chunk_coherent<T>(row, c), a);
@@ -294,14 +311,14 @@ __device__ __forceinline__ float row_dist2_reg(const T* row, const float (&x)[NC
             chunk_fma(acc, d, d);
         }
     }
-    return halfwarp_sum(__fadd_rn(acc.e, acc.o));
+    return group_sum(__fadd_rn(acc.e, acc.o));
 }
 template <typename TA, typename TB, int NCH>
 __device__ __forceinline__ float row_dist2_coherent(const TA* ra, const TB* rb, int lane, int dim) {
     Acc2 acc{0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < NCH; ++i) {
-        const int c = lane + 16 * i;
+        const int c = lane + 8 * i;
         if (c * 8 < dim) {
             float a[8], b[8], d[8];
             to_float(load_chunk_coherent<TA>(ra, c), a);
@@ -311,7 +328,7 @@ __device__ __forceinline__ float row_dist2_coherent(const TA* ra, const TB* rb, 
             chunk_fma(acc, d, d);
         }
     }
-    return halfwarp_sum(__fadd_rn(acc.e, acc.o));
+    return group_sum(__fadd_rn(acc.e, acc.o));
 }
 // canonical ||x||^2 of a register vector
 template <int NCH>
@@ -319,7 +336,7 @@ __device__ __forceinline__ float reg_sqnorm(const float (&x)[NCH][8]) {
     Acc2 acc{0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < NCH; ++i) chunk_fma(acc, x[i], x[i]);
-    return halfwarp_sum(__fadd_rn(acc.e, acc.o));
+    return group_sum(__fadd_rn(acc.e, acc.o));
 }
 
 // load the lane's chunks of an fp32 vector (query) into registers
@@ -327,7 +344,7 @@ template <int NCH>
 __device__ __forceinline__ void load_vec_f32(const float* v, float (&b)[NCH][8], int lane, int dim) {
 #pragma unroll
     for (int i = 0; i < NCH; ++i) {
-        const int c = lane + 16 * i;
+        const int c = lane + 8 * i;
         if (c * 8 < dim) {
             to_float(load_chunk<float>(v, c), b[i]);
         } else {
@@ -340,7 +357,7 @@ template <typename T, int NCH>
 __device__ __forceinline__ void load_vec(const T* v, float (&b)[NCH][8], int lane, int dim) {
 #pragma unroll
     for (int i = 0; i < NCH; ++i) {
-        const int c = lane + 16 * i;
+        const int c = lane + 8 * i;
         if (c * 8 < dim) {
             to_float(load_chunk<T>(v, c), b[i]);
         } else {

@@ -8,17 +8,28 @@
 // Semantics follow kernels/triton_search_kernels.py:6-148 (gate `dot + r > tau`,
 // every child of a kept parent is emitted) or, by flags,
 // kernels/cpp/torch_ext_v3.cpp:177-241 (gate `>=`, leaf test `dot >= tau`).
-// The kernel is a streaming read: 16-lane groups each read one 256-byte row
-// with 128-bit loads, several rows in flight per thread; it is HBM-bound.
+// The kernel is a streaming read: 8-lane groups each read one row with 128-bit
+// asynchronous copies, several rows in flight per thread; it is HBM-bound.
 #include "common.cuh"
+#include <math_constants.h>
+#include <stdlib.h>
 
 namespace hira {
 
-constexpr int SEARCH_THREADS = 256;
-constexpr int SEARCH_HW = SEARCH_THREADS / 16;   // half-warps per CTA
-constexpr int SEARCH_WARPS = SEARCH_THREADS / 32;
 constexpr int MAX_TILE_ROWS = 1024;
-constexpr int SEARCH_UNROLL = 4;
+constexpr int SEARCH_RPI = 2;  // rows per 8-lane group per pipeline step
+constexpr uint32_t NOT_EMITTED = 0xffffffffu;  // score-buffer sentinel (a NaN no arithmetic produces)
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_16s(uint32_t smem_addr, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
 struct SearchParams {
     const void* children;
@@ -41,7 +52,8 @@ struct SearchParams {
     uint32_t* stats;
     int n_heads, n_qheads, group, depth, bf, dim;
     int cap_parents, cap_gp, tile_parents, n_tiles, flags;
-    uint32_t bf_magic;  // ceil(2^32 / bf): x / bf == __umulhi(x, bf_magic) for x < 2^20, bf <= 1024
+    uint32_t ring_offset;     // byte offset of the per-thread prefetch ring in dynamic shared memory
+    uint32_t bf_magic;        // ceil(2^32 / bf): x / bf == __umulhi(x, bf_magic) for x < 2^20, bf <= 1024
 };
 
 __device__ __forceinline__ int div_bf(int x, int bf, uint32_t magic) {
@@ -54,45 +66,95 @@ __device__ __forceinline__ bool gate_keep(float dot, float r, float qn, bool has
     return ge ? (s >= tau) : (s > tau);
 }
 
-// bit j of the result = predicate of the lane that owns head j in this half-warp
+// bit j of the result = predicate of the first lane that owns head j in this 8-lane group
 template <int GT>
 __device__ __forceinline__ uint32_t head_mask_from_ballot(uint32_t ballot, int tid) {
-    const int half_base = tid & 16;
+    const int base = tid & 24;
     uint32_t m = 0;
 #pragma unroll
-    for (int j = 0; j < GT; ++j) {
-        // first lane owning head j
-        int l = 0;
-        if (GT == 2) l = j * 8;
-        if (GT == 4) l = j * 4;
-        if (GT == 8) l = j * 2;
-        m |= ((ballot >> (half_base + l)) & 1u) << j;
-    }
+    for (int j = 0; j < GT; ++j) m |= ((ballot >> (base + HeadReduce<GT>::first_lane(j))) & 1u) << j;
     return m;
 }
 
+// canonical q.row for the GT heads held in qreg; result for head_of_lane(lane)
 template <typename T, int GT, int NCH>
-__global__ void __launch_bounds__(SEARCH_THREADS, (GT * NCH <= 4) ? 2 : 1)
+__device__ __forceinline__ float gate_dot(const T* row, const float (&qreg)[GT][NCH][8], int lane, int dim, bool load) {
+    float v[GT];
+#pragma unroll
+    for (int j = 0; j < GT; ++j) v[j] = 0.f;
+    if (load) {
+        Acc2 acc[GT];
+#pragma unroll
+        for (int j = 0; j < GT; ++j) acc[j] = Acc2{0.f, 0.f};
+#pragma unroll
+        for (int ci = 0; ci < NCH; ++ci) {
+            const int c = lane + GROUP * ci;
+            if (c * 8 < dim) {
+                float a[8];
+                to_float(load_chunk<T>(row, c), a);
+#pragma unroll
+                for (int j = 0; j < GT; ++j) chunk_fma(acc[j], a, qreg[j][ci]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < GT; ++j) v[j] = __fadd_rn(acc[j].e, acc[j].o);
+    }
+    return HeadReduce<GT>::run(v, lane, 0xffffffffu);  // callers keep the warp converged
+}
+
+// the same from chunks already loaded into registers
+template <typename T, int GT, int NCH>
+__device__ __forceinline__ float gate_dot_raw(const RawChunk<T> (&raw)[NCH], const float (&qreg)[GT][NCH][8], int lane) {
+    Acc2 acc[GT];
+#pragma unroll
+    for (int j = 0; j < GT; ++j) acc[j] = Acc2{0.f, 0.f};
+#pragma unroll
+    for (int ci = 0; ci < NCH; ++ci) {
+        float a[8];
+        to_float(raw[ci], a);
+#pragma unroll
+        for (int j = 0; j < GT; ++j) chunk_fma(acc[j], a, qreg[j][ci]);   // chunks outside the row were loaded as zeros
+    }
+    float v[GT];
+#pragma unroll
+    for (int j = 0; j < GT; ++j) v[j] = __fadd_rn(acc[j].e, acc[j].o);
+    return HeadReduce<GT>::run(v, lane, 0xffffffffu);  // callers keep the warp converged
+}
+
+template <typename T, int NCH>
+__device__ __forceinline__ void load_row_raw(RawChunk<T> (&raw)[NCH], const T* row, int lane, int dim, bool doit) {
+#pragma unroll
+    for (int ci = 0; ci < NCH; ++ci) {
+        const int c = lane + GROUP * ci;
+        if (doit && c * 8 < dim) raw[ci] = load_chunk<T>(row, c);
+        else raw[ci] = zero_chunk<T>();
+    }
+}
+
+template <typename T, int GT, int NCH, int STAGES, int MINB, bool FULLD, int TH>
+__global__ void __launch_bounds__(TH, MINB)
 search_kernel(const SearchParams P) {
+    constexpr int SEARCH_THREADS = TH;
+    constexpr int SEARCH_GROUPS = TH / GROUP;  // 8-lane groups per CTA
+    constexpr int PRE = 2;                      // parent-gate iterations whose loads are issued up front
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int TP = P.tile_parents;
     const int bf = P.bf;
     const int tile_rows = TP * bf;
-    float* s_score = reinterpret_cast<float*>(smem_raw);             // [tile_rows][GT]
-    int* s_pcount = reinterpret_cast<int*>(s_score + (size_t)tile_rows * GT);  // [TP]
+    float* s_score = reinterpret_cast<float*>(smem_raw);                         // [tile_rows][GT]
+    int* s_pcount = reinterpret_cast<int*>(s_score + (size_t)tile_rows * GT);    // [TP]
     unsigned short* s_plist = reinterpret_cast<unsigned short*>(s_pcount + TP);  // [TP]
     unsigned char* s_pmask = reinterpret_cast<unsigned char*>(s_plist + TP);     // [TP]
     unsigned char* s_gpmask = s_pmask + TP;                                      // [TP]
 
     __shared__ int s_qh[GT];
-    __shared__ float s_tau[GT], s_scale[GT], s_qn[GT];
+    __shared__ float s_scale[GT];
     __shared__ int s_nq, s_npass;
-    __shared__ int s_segcnt[SEARCH_WARPS];
     __shared__ uint32_t s_stat[GT][8];
 
     const int tid = threadIdx.x;
-    const int lane = tid & 15;     // lane inside the half-warp
-    const int hw = tid >> 4;       // half-warp id
+    const int lane = tid & (GROUP - 1);  // lane inside the 8-lane group
+    const int grp = tid / GROUP;         // group id: one row per group per step
     const int warp = tid >> 5;
     const int wl = tid & 31;
     const int tile = blockIdx.x % P.n_tiles;
@@ -107,53 +169,59 @@ search_kernel(const SearchParams P) {
 
     // ---- 1. query heads of this kv head handled by this CTA ------------------
     if (tid < GT * 8) (&s_stat[0][0])[tid] = 0;
+    int nq;
+    int qh_of[GT];
     if (P.q2kv == nullptr) {
-        if (tid == 0) {
-            int n = P.group - chunk * GT;
-            n = n < 0 ? 0 : (n > GT ? GT : n);
-            s_nq = n;
-            for (int j = 0; j < n; ++j) s_qh[j] = h * P.group + chunk * GT + j;
+        nq = P.group - chunk * GT;
+        nq = nq < 0 ? 0 : (nq > GT ? GT : nq);
+#pragma unroll
+        for (int j = 0; j < GT; ++j) qh_of[j] = h * P.group + chunk * GT + (j < nq ? j : 0);
+        if (tid < nq) s_qh[tid] = h * P.group + chunk * GT + tid;
+    } else {
+        if (warp == 0) {
+            // ordered scan of the explicit map; keep matches [chunk*GT, chunk*GT+GT)
+            int seen = 0;
+            for (int base = 0; base < P.n_qheads; base += 32) {
+                const int i = base + wl;
+                const bool m = (i < P.n_qheads) && (P.q2kv[i] == h);
+                const uint32_t b = __ballot_sync(0xffffffffu, m);
+                const int pos = seen + __popc(b & ((1u << wl) - 1u));
+                if (m && pos >= chunk * GT && pos < chunk * GT + GT) s_qh[pos - chunk * GT] = i;
+                seen += __popc(b);
+            }
+            if (wl == 0) {
+                int n = seen - chunk * GT;
+                s_nq = n < 0 ? 0 : (n > GT ? GT : n);
+            }
         }
-    } else if (warp == 0) {
-        // ordered scan of the explicit map; keep matches [chunk*GT, chunk*GT+GT)
-        int seen = 0;
-        for (int base = 0; base < P.n_qheads; base += 32) {
-            const int i = base + wl;
-            const bool m = (i < P.n_qheads) && (P.q2kv[i] == h);
-            const uint32_t b = __ballot_sync(0xffffffffu, m);
-            const int pos = seen + __popc(b & ((1u << wl) - 1u));
-            if (m && pos >= chunk * GT && pos < chunk * GT + GT) s_qh[pos - chunk * GT] = i;
-            seen += __popc(b);
-        }
-        if (wl == 0) {
-            int n = seen - chunk * GT;
-            s_nq = n < 0 ? 0 : (n > GT ? GT : n);
-        }
+        __syncthreads();
+        nq = s_nq;
+#pragma unroll
+        for (int j = 0; j < GT; ++j) qh_of[j] = s_qh[j < nq ? j : 0];
     }
-    __syncthreads();
-    const int nq = s_nq;
+    if (nq == 0) return;  // nothing mapped to this (kv head, chunk): no outputs owned (uniform over the CTA)
     const int tile_p0 = tile * TP;
     const size_t tile_c0 = (size_t)tile_p0 * bf;
-    if (nq == 0) return;  // nothing mapped to this (kv head, chunk): no outputs owned
-    if (tid < nq) {
-        const int qh = s_qh[tid];
-        s_tau[tid] = P.tau[qh];
-        s_scale[tid] = P.scaling ? P.scaling[qh] : 1.0f;
-        s_qn[tid] = has_qn ? P.qnorm[qh] : 1.0f;
-    }
+    const int my_head = HeadReduce<GT>::head_of_lane(lane);
+    const bool head_on = my_head < nq;
 
-    // tile beyond the slots in use: emit nothing
+    // ---- 2. every load the gates need, issued together (one memory latency, not five) ----
     const int used_parents = P.used[h * 4 + 0];
     const int used_gp = P.used[h * 4 + 1];
-    bool tile_empty;
-    if (P.depth == 3) tile_empty = (tile_p0 / bf) >= used_gp;
-    else tile_empty = tile_p0 >= used_parents;
-
+    const int g0 = tile_p0 / bf;
+    const int ng = (TP + bf - 1) / bf;  // grandparents touched by this tile (TP % bf == 0 or bf % TP == 0)
+    int my_qh = qh_of[0];
+#pragma unroll
+    for (int j = 1; j < GT; ++j)
+        if (my_head == j) my_qh = qh_of[j];
+    const float my_tau = head_on ? P.tau[my_qh] : 0.f;
+    const float my_qn = (head_on && has_qn) ? P.qnorm[my_qh] : 1.f;
+    if (tid < nq) s_scale[tid] = P.scaling ? P.scaling[s_qh[tid]] : 1.0f;  // s_qh[tid] was written by this thread or before the barrier above
     float qreg[GT][NCH][8];
 #pragma unroll
     for (int j = 0; j < GT; ++j) {
-        if (j < nq && !tile_empty) {
-            load_vec_f32<NCH>(P.q + (size_t)s_qh[j] * P.dim, qreg[j], lane, P.dim);
+        if (j < nq) {
+            load_vec_f32<NCH>(P.q + (size_t)qh_of[j] * P.dim, qreg[j], lane, P.dim);
         } else {
 #pragma unroll
             for (int i = 0; i < NCH; ++i)
@@ -161,45 +229,61 @@ search_kernel(const SearchParams P) {
                 for (int e = 0; e < 8; ++e) qreg[j][i][e] = 0.f;
         }
     }
-    __syncthreads();
+    // grandparent row of this group (first pass of the loop below) and its radius
+    RawChunk<T> graw[NCH];
+    float grad = 0.f;
+    const bool gp_mine = P.depth == 3 && grp < ng && (g0 + grp) < P.cap_gp;
+    {
+        const T* gps = reinterpret_cast<const T*>(P.gps) + (size_t)h * P.cap_gp * P.dim;
+        load_row_raw<T, NCH>(graw, gps + (size_t)(g0 + grp) * P.dim, lane, P.dim, gp_mine);
+        if (gp_mine) grad = P.gp_radii[(size_t)h * P.cap_gp + g0 + grp];
+    }
+    // parent rows of this group for the first PRE passes, with radius, child count and slot validity
+    RawChunk<T> praw[PRE][NCH];
+    float prad[PRE];
+    int pcnt[PRE], pgc[PRE];
+#pragma unroll
+    for (int u = 0; u < PRE; ++u) {
+        const int i = u * SEARCH_GROUPS + grp;
+        const int p = tile_p0 + i;
+        const bool in = (i < TP) && (p < P.cap_parents);
+        load_row_raw<T, NCH>(praw[u], parents + (size_t)p * P.dim, lane, P.dim, in);
+        prad[u] = in ? P.parent_radii[(size_t)h * P.cap_parents + p] : 0.f;
+        pcnt[u] = in ? P.child_counts[(size_t)h * P.cap_parents + p] : 0;
+        pgc[u] = (in && P.depth == 3) ? P.gp_counts[(size_t)h * P.cap_gp + p / bf] : 0;
+    }
+    // score buffer starts as "nothing emitted"
+    {
+        uint4* sc4 = reinterpret_cast<uint4*>(s_score);
+        const int n4 = tile_rows * GT / 4;
+        for (int i = tid; i < n4; i += SEARCH_THREADS) sc4[i] = make_uint4(NOT_EMITTED, NOT_EMITTED, NOT_EMITTED, NOT_EMITTED);
+        for (int i = n4 * 4 + tid; i < tile_rows * GT; i += SEARCH_THREADS)
+            reinterpret_cast<uint32_t*>(s_score)[i] = NOT_EMITTED;
+    }
 
-    int npass = 0;
+    // tile beyond the slots in use: emit nothing
+    bool tile_empty;
+    if (P.depth == 3) tile_empty = g0 >= used_gp;
+    else tile_empty = tile_p0 >= used_parents;
+
     if (!tile_empty) {
-        // ---- 2. grandparent gate ---------------------------------------------
+        // ---- 3a. grandparent gate --------------------------------------------
         const uint32_t allmask = (1u << nq) - 1u;
-        const int g0 = tile_p0 / bf;
-        const int ng = (TP + bf - 1) / bf;  // grandparents touched by this tile (TP % bf == 0 or bf % TP == 0)
         if (P.depth == 3) {
             const T* gps = reinterpret_cast<const T*>(P.gps) + (size_t)h * P.cap_gp * P.dim;
-            for (int i0 = 0; i0 < ng; i0 += SEARCH_HW) {  // trip count uniform over the CTA: shuffles inside
-                const int i = i0 + hw;
+            for (int i0 = 0; i0 < ng; i0 += SEARCH_GROUPS) {  // trip count uniform over the CTA: ballot inside
+                const int i = i0 + grp;
                 const int g = g0 + i;
-                const bool valid = (i < ng) && (g < used_gp);  // uniform inside the half-warp
-                float v[GT];
-#pragma unroll
-                for (int j = 0; j < GT; ++j) v[j] = 0.f;
-                if (valid) {
-                    Acc2 acc[GT];
-#pragma unroll
-                    for (int j = 0; j < GT; ++j) acc[j] = Acc2{0.f, 0.f};
-#pragma unroll
-                    for (int ci = 0; ci < NCH; ++ci) {
-                        const int c = lane + 16 * ci;
-                        if (c * 8 < P.dim) {
-                            float a[8];
-                            to_float(load_chunk<T>(gps + (size_t)g * P.dim, c), a);
-#pragma unroll
-                            for (int j = 0; j < GT; ++j) chunk_fma(acc[j], a, qreg[j][ci]);
-                        }
-                    }
-#pragma unroll
-                    for (int j = 0; j < GT; ++j) v[j] = __fadd_rn(acc[j].e, acc[j].o);
+                const bool valid = (i < ng) && (g < used_gp);  // uniform inside the group
+                float d, r;
+                if (i0 == 0) {
+                    d = gate_dot_raw<T, GT, NCH>(graw, qreg, lane);
+                    r = grad;
+                } else {
+                    d = gate_dot<T, GT, NCH>(gps + (size_t)g * P.dim, qreg, lane, P.dim, valid);
+                    r = valid ? P.gp_radii[(size_t)h * P.cap_gp + g] : 0.f;
                 }
-                const float d = HeadReduce<GT>::run(v, lane);
-                const int j = HeadReduce<GT>::head_of_lane(lane);
-                bool keep = false;
-                if (valid && j < nq)
-                    keep = gate_keep(d, P.gp_radii[(size_t)h * P.cap_gp + g], s_qn[j], has_qn, s_tau[j], ge);
+                const bool keep = valid && head_on && gate_keep(d, r, my_qn, has_qn, my_tau, ge);
                 const uint32_t b = __ballot_sync(0xffffffffu, keep);
                 const uint32_t m = head_mask_from_ballot<GT>(b, tid);
                 if (lane == 0 && i < ng) {
@@ -214,58 +298,31 @@ search_kernel(const SearchParams P) {
                     }
                 }
             }
-            __syncthreads();
         }
+        __syncthreads();  // s_gpmask, s_stat zeroing, score sentinel
 
-        // ---- 3. parent gate ---------------------------------------------------
-        for (int i0 = 0; i0 < TP; i0 += SEARCH_HW) {  // uniform trip count
-            const int i = i0 + hw;
+        // ---- 3b. parent gate --------------------------------------------------
+        auto gate_parent = [&](int i0, float d, float r, int cnt, int gc) {
+            const int i = i0 + grp;
             const int p = tile_p0 + i;
-            bool valid = (i < TP) && (p < P.cap_parents);
+            const bool in = (i < TP) && (p < P.cap_parents);
+            bool valid = in;
             uint32_t gm = allmask;
-            if (valid) {
+            if (in) {
                 if (P.depth == 3) {
                     const int g = p / bf;
-                    valid = (g < used_gp) && ((p - g * bf) < P.gp_counts[(size_t)h * P.cap_gp + g]);
+                    valid = (g < used_gp) && ((p - g * bf) < gc);
                     gm = s_gpmask[g - g0];
                 } else {
                     valid = p < used_parents;
                 }
             }
             const bool work = valid && gm != 0;
-            float v[GT];
-#pragma unroll
-            for (int j = 0; j < GT; ++j) v[j] = 0.f;
-            if (work) {
-                Acc2 acc[GT];
-#pragma unroll
-                for (int j = 0; j < GT; ++j) acc[j] = Acc2{0.f, 0.f};
-#pragma unroll
-                for (int ci = 0; ci < NCH; ++ci) {
-                    const int c = lane + 16 * ci;
-                    if (c * 8 < P.dim) {
-                        float a[8];
-                        to_float(load_chunk<T>(parents + (size_t)p * P.dim, c), a);
-#pragma unroll
-                        for (int j = 0; j < GT; ++j) chunk_fma(acc[j], a, qreg[j][ci]);
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < GT; ++j) v[j] = __fadd_rn(acc[j].e, acc[j].o);
-            }
-            const float d = HeadReduce<GT>::run(v, lane);
-            const int j = HeadReduce<GT>::head_of_lane(lane);
-            bool keep = false;
-            if (work && j < nq && ((gm >> j) & 1u))
-                keep = gate_keep(d, P.parent_radii[(size_t)h * P.cap_parents + p], s_qn[j], has_qn, s_tau[j], ge);
+            const bool keep = work && head_on && ((gm >> my_head) & 1u) && gate_keep(d, r, my_qn, has_qn, my_tau, ge);
             const uint32_t b = __ballot_sync(0xffffffffu, keep);
             const uint32_t m = head_mask_from_ballot<GT>(b, tid);
             if (lane == 0 && i < TP) {
-                int cnt = 0;
-                if (valid) {
-                    cnt = P.child_counts[(size_t)h * P.cap_parents + p];
-                    cnt = cnt > bf ? bf : cnt;
-                }
+                cnt = valid ? (cnt > bf ? bf : cnt) : 0;
                 s_pmask[i] = (unsigned char)m;
                 s_pcount[i] = cnt;
                 if (work && P.stats) {
@@ -280,156 +337,217 @@ search_kernel(const SearchParams P) {
                     }
                 }
             }
+        };
+#pragma unroll
+        for (int u = 0; u < PRE; ++u) {  // rows loaded in step 2; the trip test is uniform over the CTA
+            if (u * SEARCH_GROUPS < TP)
+                gate_parent(u * SEARCH_GROUPS, gate_dot_raw<T, GT, NCH>(praw[u], qreg, lane), prad[u], pcnt[u], pgc[u]);
+        }
+        for (int i0 = PRE * SEARCH_GROUPS; i0 < TP; i0 += SEARCH_GROUPS) {  // uniform trip count
+            const int p = tile_p0 + i0 + grp;
+            const bool in = (i0 + grp < TP) && (p < P.cap_parents);
+            const float d = gate_dot<T, GT, NCH>(parents + (size_t)p * P.dim, qreg, lane, P.dim, in);
+            const float r = in ? P.parent_radii[(size_t)h * P.cap_parents + p] : 0.f;
+            const int cnt = in ? P.child_counts[(size_t)h * P.cap_parents + p] : 0;
+            const int gc = (in && P.depth == 3) ? P.gp_counts[(size_t)h * P.cap_gp + p / bf] : 0;
+            gate_parent(i0, d, r, cnt, gc);
         }
         __syncthreads();
 
         // ---- 4. ordered list of parents kept for at least one head ------------
+        // one packed word per kept parent: local parent id << 19 | head mask << 11 | child count
+        uint32_t* s_pl = reinterpret_cast<uint32_t*>(s_pcount);  // reuses s_pcount after the pass below
         if (warp == 0) {
             int n = 0;
             for (int base = 0; base < TP; base += 32) {
                 const int i = base + wl;
-                const bool m = (i < TP) && s_pmask[i] != 0 && s_pcount[i] > 0;
+                uint32_t word = 0;
+                bool m = false;
+                if (i < TP) {
+                    const uint32_t cnt = (uint32_t)s_pcount[i], msk = s_pmask[i];
+                    m = msk != 0 && cnt > 0;
+                    word = ((uint32_t)i << 19) | (msk << 11) | cnt;
+                }
                 const uint32_t b = __ballot_sync(0xffffffffu, m);
-                if (m) s_plist[n + __popc(b & ((1u << wl) - 1u))] = (unsigned short)i;
+                __syncwarp();  // every lane has read s_pcount[base..base+31] before slots <= base+31 are overwritten
+                if (m) s_pl[n + __popc(b & ((1u << wl) - 1u))] = word;
                 n += __popc(b);
             }
             if (wl == 0) s_npass = n;
         }
         __syncthreads();
-        npass = s_npass;
+        const int npass = s_npass;
 
         // ---- 5. stream the children rows of kept parents ----------------------
+        // The kept parents form a flat list of npass*bf rows; 8-lane group g walks the R
+        // consecutive rows [g*R, (g+1)*R) of it, so its row pointer and score index just
+        // step forward and the parent word is reloaded once per bf rows.  Each thread owns
+        // a private ring of STAGES slots in shared memory and keeps STAGES-1 steps (of RPI
+        // rows) of asynchronous 16-byte copies (cp.async, L2 only) in flight ahead of the
+        // rows it is working on; only the issuing thread reads a slot, so no barrier is
+        // needed and the depth of the prefetch costs no registers.
+        constexpr int TPP = (int)(sizeof(T) / 2);   // 16-byte pieces per chunk
+        constexpr int PIECES = NCH * TPP;           // 16-byte pieces per thread per row
+        constexpr int PIECE_STRIDE = SEARCH_THREADS * 16;
+        constexpr int STAGE_STRIDE = SEARCH_RPI * PIECES * PIECE_STRIDE;
+        const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(smem_raw + P.ring_offset) + tid * 16;
+        const unsigned char* ring_g = smem_raw + P.ring_offset + tid * 16;
+        const int row_bytes = P.dim * (int)sizeof(T);
+        const char* gbase = reinterpret_cast<const char*>(children) + tile_c0 * (size_t)row_bytes + lane * 8 * sizeof(T);
         const int total = npass * bf;
-        for (int base = 0; base < total; base += SEARCH_HW * SEARCH_UNROLL) {
-            RawChunk<T> raw[SEARCH_UNROLL][NCH];
-            int sl[SEARCH_UNROLL];  // local slot (pl*bf + child) or -1
+        int R = (total + SEARCH_GROUPS - 1) / SEARCH_GROUPS;
+        R = (R + SEARCH_RPI - 1) / SEARCH_RPI * SEARCH_RPI;
+        const int n_it = R / SEARCH_RPI;
+
+        // cursor over the rows of this group: parent-list position k, child c, parent word w
+        struct Cursor { int k, c, cnt; uint32_t w; };
+        auto load_parent = [&](Cursor& cu) {
+            cu.w = cu.k < npass ? s_pl[cu.k] : 0u;
+            cu.cnt = (int)(cu.w & 0x7ffu);
+        };
+        Cursor ic, cc;
+        ic.k = div_bf(grp * R, bf, P.bf_magic);
+        ic.c = grp * R - ic.k * bf;
+        load_parent(ic);
+        cc = ic;
+        const char* isrc = gbase + (size_t)((ic.w >> 19) * bf + ic.c) * row_bytes;
+        float* cdst = s_score + (size_t)((cc.w >> 19) * bf + cc.c) * GT + my_head;
+        bool cgate = (cc.w >> (11 + my_head)) & 1u;
+        const bool writer = HeadReduce<GT>::is_writer(lane);
+        const bool emit_all = leaf_mode == HIRA_LEAF_CANDIDATES;
+        // d > tau  <=>  d >= nextafter(tau): one comparison serves both leaf rules
+        const float leaf_thr = (leaf_mode == HIRA_LEAF_GT) ? nextafterf(my_tau, CUDART_INF_F) : my_tau;
+
+        auto issue_rows = [&](uint32_t stage_off) {
 #pragma unroll
-            for (int u = 0; u < SEARCH_UNROLL; ++u) {
-                const int r = base + u * SEARCH_HW + hw;
-                sl[u] = -1;
-                if (r < total) {
-                    const int k = div_bf(r, bf, P.bf_magic);
-                    const int child = r - k * bf;
-                    const int pl = s_plist[k];
-                    if (child < s_pcount[pl]) sl[u] = pl * bf + child;
+            for (int u = 0; u < SEARCH_RPI; ++u) {
+                if (ic.c < ic.cnt) {
+#pragma unroll
+                    for (int pc = 0; pc < PIECES; ++pc) {
+                        const int coff = (pc / TPP) * GROUP * 8 * (int)sizeof(T) + (pc % TPP) * 16;
+                        if (FULLD || (lane + GROUP * (pc / TPP)) * 8 < P.dim)
+                            cp_async_16s(ring_s + stage_off + (u * PIECES + pc) * PIECE_STRIDE, isrc + coff);
+                    }
                 }
-#pragma unroll
-                for (int ci = 0; ci < NCH; ++ci) {
-                    const int c = lane + 16 * ci;
-                    if (sl[u] >= 0 && c * 8 < P.dim)
-                        raw[u][ci] = load_chunk_stream<T>(children + (tile_c0 + sl[u]) * P.dim, c);
-                    else
-                        raw[u][ci] = zero_chunk<T>();
+                ++ic.c;
+                isrc += row_bytes;
+                if (ic.c == bf) {
+                    ic.c = 0;
+                    ++ic.k;
+                    load_parent(ic);
+                    isrc = gbase + (size_t)((ic.w >> 19) * bf) * row_bytes;
                 }
             }
+        };
+        {
+            uint32_t so = 0;
 #pragma unroll
-            for (int u = 0; u < SEARCH_UNROLL; ++u) {
+            for (int it = 0; it < STAGES - 1; ++it) {
+                if (it < n_it) issue_rows(so);
+                cp_async_commit();
+                so += STAGE_STRIDE;
+            }
+        }
+        uint32_t issue_off = (STAGES - 1) * STAGE_STRIDE, cons_off = 0;
+        for (int it = 0; it < n_it; ++it) {
+            if (it + STAGES - 1 < n_it) issue_rows(issue_off);
+            cp_async_commit();
+            issue_off = (issue_off == (STAGES - 1) * STAGE_STRIDE) ? 0 : issue_off + STAGE_STRIDE;
+            cp_async_wait<STAGES - 1>();
+#pragma unroll
+            for (int u = 0; u < SEARCH_RPI; ++u) {
                 Acc2 acc[GT];
 #pragma unroll
                 for (int j = 0; j < GT; ++j) acc[j] = Acc2{0.f, 0.f};
 #pragma unroll
                 for (int ci = 0; ci < NCH; ++ci) {
+                    // a slot that was not filled this step holds stale bytes: harmless, nothing is stored for it
+                    const uint4* src = reinterpret_cast<const uint4*>(ring_g + cons_off + (u * PIECES + ci * TPP) * PIECE_STRIDE);
                     float a[8];
-                    to_float(raw[u][ci], a);
+                    if (TPP == 1) {
+                        unpack_bf16x8(src[0], a);
+                    } else {
+                        const uint4 lo = src[0], hi = src[SEARCH_THREADS];
+                        a[0] = __uint_as_float(lo.x); a[1] = __uint_as_float(lo.y);
+                        a[2] = __uint_as_float(lo.z); a[3] = __uint_as_float(lo.w);
+                        a[4] = __uint_as_float(hi.x); a[5] = __uint_as_float(hi.y);
+                        a[6] = __uint_as_float(hi.z); a[7] = __uint_as_float(hi.w);
+                    }
+                    if (FULLD || (lane + GROUP * ci) * 8 < P.dim) {
 #pragma unroll
-                    for (int j = 0; j < GT; ++j) chunk_fma(acc[j], a, qreg[j][ci]);
+                        for (int j = 0; j < GT; ++j) chunk_fma(acc[j], a, qreg[j][ci]);
+                    }
                 }
                 float v[GT];
 #pragma unroll
                 for (int j = 0; j < GT; ++j) v[j] = __fadd_rn(acc[j].e, acc[j].o);
-                const float d = HeadReduce<GT>::run(v, lane);
-                const int j = HeadReduce<GT>::head_of_lane(lane);
-                // the first lane owning head j writes
-                const bool writer = (GT == 1) ? (lane == 0)
-                                  : (GT == 2) ? ((lane & 7) == 0)
-                                  : (GT == 4) ? ((lane & 3) == 0)
-                                              : ((lane & 1) == 0);
-                if (writer && sl[u] >= 0) s_score[(size_t)sl[u] * GT + j] = d;
-            }
-        }
-        __syncthreads();
-    }
-
-    // ---- 6. ordered compaction per head + dense output ------------------------
-    constexpr int NSEG = SEARCH_WARPS / GT;  // warps per head
-    const int j = warp % GT;
-    const int seg = warp / GT;
-    const int seg_rows = (tile_rows + NSEG - 1) / NSEG;
-    const int r_begin = seg * seg_rows;
-    const int r_end = min(tile_rows, r_begin + seg_rows);
-    const bool active = j < nq;
-    const int qh = active ? s_qh[j] : 0;
-    const float tau = active ? s_tau[j] : 0.f;
-    const float scale = active ? s_scale[j] : 0.f;
-    const bool want_compact = P.out_idx != nullptr;
-
-    auto keep_of = [&](int i, float& sc) -> bool {
-        // i: local slot inside the tile
-        const int pl = div_bf(i, bf, P.bf_magic);
-        const int child = i - pl * bf;
-        bool k = (npass > 0) && ((s_pmask[pl] >> j) & 1u) && (child < s_pcount[pl]);
-        sc = 0.f;
-        if (k) {
-            sc = s_score[(size_t)i * GT + j];
-            if (leaf_mode == HIRA_LEAF_GE) k = sc >= tau;
-            else if (leaf_mode == HIRA_LEAF_GT) k = sc > tau;
-        }
-        return k;
-    };
-
-    int mycount = 0;
-    if (active && want_compact && npass > 0) {
-        for (int base = r_begin; base < r_end; base += 32) {
-            const int i = base + wl;
-            float sc;
-            const bool k = (i < r_end) && keep_of(i, sc);
-            mycount += __popc(__ballot_sync(0xffffffffu, k));
-        }
-    }
-    if (wl == 0) s_segcnt[warp] = mycount;
-    __syncthreads();
-    if (active) {
-        int offset = 0, total_cnt = 0;
-        for (int s = 0; s < NSEG; ++s) {
-            const int c = s_segcnt[s * GT + j];
-            if (s < seg) offset += c;
-            total_cnt += c;
-        }
-        const size_t out_base = (size_t)qh * cap_children + tile_c0;
-        if (want_compact || P.out_dense) {
-            for (int base = r_begin; base < r_end; base += 32) {
-                const int i = base + wl;
-                float sc = 0.f;
-                const bool k = (i < r_end) && (npass > 0) && keep_of(i, sc);
-                const float emitted = __fmul_rn(sc, scale);
-                if (want_compact) {
-                    const uint32_t b = __ballot_sync(0xffffffffu, k);
-                    if (k) {
-                        const int pos = offset + __popc(b & ((1u << wl) - 1u));
-                        P.out_idx[out_base + pos] = (int32_t)(tile_c0 + i);
-                        P.out_score[out_base + pos] = emitted;
-                    }
-                    offset += __popc(b);
+                const float d = HeadReduce<GT>::run(v, lane, 0xffffffffu);  // the whole warp runs every step
+                if (writer && cgate && cc.c < cc.cnt && (emit_all || d >= leaf_thr)) *cdst = d;
+                ++cc.c;
+                cdst += GT;
+                if (cc.c == bf) {
+                    cc.c = 0;
+                    ++cc.k;
+                    load_parent(cc);
+                    cdst = s_score + (size_t)((cc.w >> 19) * bf) * GT + my_head;
+                    cgate = (cc.w >> (11 + my_head)) & 1u;
                 }
-                if (P.out_dense && i < r_end && tile_c0 + i < cap_children)
-                    P.out_dense[out_base + i] = k ? emitted : 0.f;
             }
+            cons_off = (cons_off == (STAGES - 1) * STAGE_STRIDE) ? 0 : cons_off + STAGE_STRIDE;
         }
-        if (seg == 0 && wl == 0) {
-            if (want_compact) P.out_count[(size_t)qh * P.n_tiles + tile] = total_cnt;
+        cp_async_wait<0>();
+        __syncthreads();
+    } else {
+        __syncthreads();  // the score sentinel must be visible to the compaction warps
+    }
+
+    // ---- 6. ordered compaction (one warp per head) + dense output -------------
+    if (warp < nq) {
+        const int j = warp;
+        const int qh = s_qh[j];
+        const float scale = s_scale[j];
+        const bool want_compact = P.out_idx != nullptr;
+        const size_t out_base = (size_t)qh * cap_children + tile_c0;
+        const uint32_t* sc = reinterpret_cast<const uint32_t*>(s_score);
+        int offset = 0;
+        for (int base = 0; base < tile_rows; base += 32) {
+            const int i = base + wl;
+            const uint32_t bits = (i < tile_rows) ? sc[(size_t)i * GT + j] : NOT_EMITTED;
+            const bool k = bits != NOT_EMITTED;
+            const float emitted = __fmul_rn(__uint_as_float(bits), scale);
+            const uint32_t b = __ballot_sync(0xffffffffu, k);
+            if (want_compact && k) {
+                const int pos = offset + __popc(b & ((1u << wl) - 1u));
+                P.out_idx[out_base + pos] = (int32_t)(tile_c0 + i);
+                P.out_score[out_base + pos] = emitted;
+            }
+            offset += __popc(b);
+            if (P.out_dense && i < tile_rows && tile_c0 + i < cap_children)
+                P.out_dense[out_base + i] = k ? emitted : 0.f;
+        }
+        if (wl == 0) {
+            if (want_compact) P.out_count[(size_t)qh * P.n_tiles + tile] = offset;
             if (P.stats) {
                 uint32_t* st = P.stats + (size_t)qh * 8;
                 for (int k = 0; k < 8; ++k)
                     if (k != 5 && s_stat[j][k]) atomicAdd(st + k, s_stat[j][k]);
-                if (total_cnt) atomicAdd(st + 5, (uint32_t)total_cnt);
+                if (offset) atomicAdd(st + 5, (uint32_t)offset);
             }
         }
     }
 }
 
-template <typename T, int GT, int NCH>
-static int launch_search(const SearchParams& P, int chunks, size_t smem, cudaStream_t stream) {
-    auto kern = search_kernel<T, GT, NCH>;
+template <typename T, int GT, int NCH, int STAGES, int MINB, bool FULLD>
+static int launch_search_fd(SearchParams P, int chunks, cudaStream_t stream) {
+    constexpr int SEARCH_THREADS = GT == 8 ? 256 : 128;   // one compaction warp per head
+    constexpr int BLOCKS = GT == 8 ? MINB : 2 * MINB;     // MINB counts 256-thread blocks per SM
+    auto kern = search_kernel<T, GT, NCH, STAGES, BLOCKS, FULLD, SEARCH_THREADS>;
+    const size_t tile_rows = (size_t)P.tile_parents * P.bf;
+    size_t off = tile_rows * GT * sizeof(float) + (size_t)P.tile_parents * (4 + 2 + 1 + 1);
+    off = (off + 15) & ~(size_t)15;
+    P.ring_offset = (uint32_t)off;
+    const size_t pieces = (size_t)NCH * (sizeof(T) / 2);
+    const size_t smem = off + (size_t)STAGES * SEARCH_RPI * pieces * SEARCH_THREADS * 16;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
@@ -443,20 +561,51 @@ static int launch_search(const SearchParams& P, int chunks, size_t smem, cudaStr
     return HIRA_OK;
 }
 
+// FULLD: every lane's chunks lie inside the row (D == 64 * NCH), so the per-chunk bounds tests drop out
+template <typename T, int GT, int NCH, int STAGES, int MINB>
+static int launch_search(const SearchParams& P, int chunks, cudaStream_t stream) {
+    if (P.dim == 64 * NCH) return launch_search_fd<T, GT, NCH, STAGES, MINB, true>(P, chunks, stream);
+    return launch_search_fd<T, GT, NCH, STAGES, MINB, false>(P, chunks, stream);
+}
+
+static int tuning_variant() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("HIRA_SEARCH_VARIANT");
+        v = e ? atoi(e) : 0;
+    }
+    return v;
+}
+
 template <typename T, int NCH>
 static int dispatch_gt(const SearchParams& P, int max_group, cudaStream_t stream) {
     int gt = 1;
     while (gt < max_group && gt < 8) gt <<= 1;
-    if (NCH == 2 && gt > 4) gt = 4;  // keep the register budget
+    if (NCH == 4 && gt > 2) gt = 2;  // D > 128: keep the query registers within budget
     const int chunks = (max_group + gt - 1) / gt;
-    const size_t tile_rows = (size_t)P.tile_parents * P.bf;
-    const size_t smem = tile_rows * gt * sizeof(float) + (size_t)P.tile_parents * (4 + 2 + 1 + 1) + 16;
-    switch (gt) {
-        case 1: return launch_search<T, 1, NCH>(P, chunks, smem, stream);
-        case 2: return launch_search<T, 2, NCH>(P, chunks, smem, stream);
-        case 4: return launch_search<T, 4, NCH>(P, chunks, smem, stream);
-        default: return launch_search<T, 8, 1>(P, chunks, smem, stream);
+    constexpr bool BF = sizeof(T) == 2;
+    constexpr int ST = BF ? (NCH == 2 ? 4 : 2) : 2;  // ring = ST * SEARCH_RPI * pieces * 4 KB
+    if constexpr (BF && NCH == 2) {
+      if (gt == 4) {
+        switch (tuning_variant()) {  // prefetch depth / residency of the headline shape
+            case 1: return launch_search<T, 4, NCH, 8, 1>(P, chunks, stream);
+            case 2: return launch_search<T, 4, NCH, 2, 2>(P, chunks, stream);
+            case 3: return launch_search<T, 4, NCH, 3, 2>(P, chunks, stream);
+            default: return launch_search<T, 4, NCH, 4, 2>(P, chunks, stream);
+        }
+      }
     }
+    switch (gt) {
+        case 1: return launch_search<T, 1, NCH, ST, 2>(P, chunks, stream);
+        case 2: return launch_search<T, 2, NCH, ST, NCH == 4 ? 1 : 2>(P, chunks, stream);
+        default: break;
+    }
+    if constexpr (NCH < 4) {
+        if (gt == 4) return launch_search<T, 4, NCH, ST, 2>(P, chunks, stream);
+        return launch_search<T, 8, NCH, ST, 1>(P, chunks, stream);
+    }
+    set_error("hira_search: internal dispatch error");
+    return HIRA_ERR_ARG;
 }
 
 }  // namespace hira
@@ -527,9 +676,10 @@ extern "C" int hira_search(const hira_index_t* ix, const float* q, const float* 
     P.n_tiles = (ix->cap_parents + tile_parents - 1) / tile_parents;
     P.flags = flags;
     P.bf_magic = (uint32_t)((0x100000000ull + (uint64_t)bf - 1) / (uint64_t)bf);
+    P.ring_offset = 0;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    const bool two = ix->dim > 128;
+    const bool wide = ix->dim > 128;
     if (ix->dtype == HIRA_BF16)
-        return two ? dispatch_gt<__nv_bfloat16, 2>(P, max_group, s) : dispatch_gt<__nv_bfloat16, 1>(P, max_group, s);
-    return two ? dispatch_gt<float, 2>(P, max_group, s) : dispatch_gt<float, 1>(P, max_group, s);
+        return wide ? dispatch_gt<__nv_bfloat16, 4>(P, max_group, s) : dispatch_gt<__nv_bfloat16, 2>(P, max_group, s);
+    return wide ? dispatch_gt<float, 4>(P, max_group, s) : dispatch_gt<float, 2>(P, max_group, s);
 }

@@ -14,7 +14,7 @@
 namespace hira {
 
 constexpr int TAU_THREADS = 256;
-constexpr int TAU_HW = TAU_THREADS / 16;
+constexpr int TAU_HW = TAU_THREADS / GROUP;
 constexpr int TAU_MAX_SAMPLES = 4096;
 
 template <typename T, int NCH>
@@ -23,7 +23,7 @@ threshold_kernel(const T* __restrict__ samples, long long head_stride, int n_sam
                  const float* __restrict__ q, const int32_t* __restrict__ q2kv, int group, int method, int k,
                  float* __restrict__ tau_out) {
     __shared__ float s[TAU_MAX_SAMPLES];
-    const int tid = threadIdx.x, lane = tid & 15, hw = tid >> 4;
+    const int tid = threadIdx.x, lane = tid & (GROUP - 1), hw = tid / GROUP;
     const int qh = blockIdx.x;
     const int h = q2kv ? q2kv[qh] : qh / group;
     const T* rows = samples + (size_t)h * head_stride;
@@ -37,7 +37,7 @@ threshold_kernel(const T* __restrict__ samples, long long head_stride, int n_sam
         if (i < n_samples) {
 #pragma unroll
             for (int ci = 0; ci < NCH; ++ci) {
-                const int c = lane + 16 * ci;
+                const int c = lane + GROUP * ci;
                 if (c * 8 < dim) {
                     float a[8];
                     to_float(load_chunk<T>(rows + (size_t)i * dim, c), a);
@@ -45,7 +45,7 @@ threshold_kernel(const T* __restrict__ samples, long long head_stride, int n_sam
                 }
             }
         }
-        const float r = halfwarp_sum(__fadd_rn(acc.e, acc.o));
+        const float r = group_sum(__fadd_rn(acc.e, acc.o));
         const float d = (i < n_samples) ? r : -CUDART_INF_F;  // padding sorts last
         if (lane == 0 && i < n2) s[i] = d;
     }
@@ -157,15 +157,15 @@ extern "C" int hira_threshold(const void* samples, int32_t dtype, int32_t n_head
                    "hira_threshold: k=%d outside 1..n_samples=%d", k, n_samples);
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const int group = q2kv ? 1 : n_qheads / n_heads;
-    const bool two = dim > 128;
+    const bool wide = dim > 128;  // chunks per lane: 2 up to 128 elements, else 4
     if (dtype == HIRA_BF16) {
         auto* p = reinterpret_cast<const __nv_bfloat16*>(samples);
-        if (two) threshold_kernel<__nv_bfloat16, 2><<<n_qheads, TAU_THREADS, 0, s>>>(p, head_stride, n_samples, dim, q, q2kv, group, method, k, tau_out);
-        else threshold_kernel<__nv_bfloat16, 1><<<n_qheads, TAU_THREADS, 0, s>>>(p, head_stride, n_samples, dim, q, q2kv, group, method, k, tau_out);
+        if (wide) threshold_kernel<__nv_bfloat16, 4><<<n_qheads, TAU_THREADS, 0, s>>>(p, head_stride, n_samples, dim, q, q2kv, group, method, k, tau_out);
+        else threshold_kernel<__nv_bfloat16, 2><<<n_qheads, TAU_THREADS, 0, s>>>(p, head_stride, n_samples, dim, q, q2kv, group, method, k, tau_out);
     } else {
         auto* p = reinterpret_cast<const float*>(samples);
-        if (two) threshold_kernel<float, 2><<<n_qheads, TAU_THREADS, 0, s>>>(p, head_stride, n_samples, dim, q, q2kv, group, method, k, tau_out);
-        else threshold_kernel<float, 1><<<n_qheads, TAU_THREADS, 0, s>>>(p, head_stride, n_samples, dim, q, q2kv, group, method, k, tau_out);
+        if (wide) threshold_kernel<float, 4><<<n_qheads, TAU_THREADS, 0, s>>>(p, head_stride, n_samples, dim, q, q2kv, group, method, k, tau_out);
+        else threshold_kernel<float, 2><<<n_qheads, TAU_THREADS, 0, s>>>(p, head_stride, n_samples, dim, q, q2kv, group, method, k, tau_out);
     }
     HIRA_CHECK_LAUNCH("hira_threshold launch");
     return HIRA_OK;

@@ -61,14 +61,14 @@ static void load_row(const void* base, int dtype, size_t row, int dim, float* ou
 }
 
 /* ---- canonical dot product ---------------------------------------------------
- * 16 lanes; lane l owns the 8-element chunks c with c % 16 == l; per lane an
- * even and an odd FMA chain over its chunks in increasing order; lane partial
- * = even + odd; butterfly over the lanes with strides 8, 4, 2, 1. */
+ * 8 lanes; lane l owns the 8-element chunks c with c % 8 == l; per lane an even
+ * and an odd FMA chain over its chunks in increasing order; lane partial =
+ * even + odd; butterfly over the lanes with strides 4, 2, 1. */
 float oracle_dot(const float* a, const float* b, int dim) {
-    float p[16];
-    for (int l = 0; l < 16; ++l) {
+    float p[8];
+    for (int l = 0; l < 8; ++l) {
         float e = 0.0f, o = 0.0f;
-        for (int c = l; c * 8 < dim; c += 16) {
+        for (int c = l; c * 8 < dim; c += 8) {
             for (int j = 0; j < 4; ++j) {
                 e = fmaf(a[8 * c + 2 * j], b[8 * c + 2 * j], e);
                 o = fmaf(a[8 * c + 2 * j + 1], b[8 * c + 2 * j + 1], o);
@@ -76,9 +76,9 @@ float oracle_dot(const float* a, const float* b, int dim) {
         }
         p[l] = e + o;
     }
-    for (int s = 8; s >= 1; s >>= 1) {
-        float t[16];
-        for (int l = 0; l < 16; ++l) t[l] = p[l] + p[l ^ s];
+    for (int s = 4; s >= 1; s >>= 1) {
+        float t[8];
+        for (int l = 0; l < 8; ++l) t[l] = p[l] + p[l ^ s];
         memcpy(p, t, sizeof(p));
     }
     return p[0];

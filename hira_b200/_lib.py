@@ -24,8 +24,9 @@ EXPORTED_SYMBOLS = [
     "hira_last_error", "hira_version", "hira_search_tile_parents", "hira_search",
     "hira_attn_default_splits", "hira_sparse_attn", "hira_merge_partials", "hira_append",
     "hira_threshold", "hira_kth_score", "hira_build_workspace_bytes", "hira_build",
-    "hira_recompute_radii", "hira_export", "hira_assign",
+    "hira_recompute_radii", "hira_export", "hira_assign", "hira_sparse_attn_noalloc",
 ]
+NOALLOC_SCRATCH_FLOATS = 1 << 20
 
 
 class HiraIndexStruct(C.Structure):
@@ -59,6 +60,8 @@ def _declare(lib):
     lib.hira_attn_default_splits.argtypes = [I32, I32]
     lib.hira_sparse_attn.restype = C.c_int
     lib.hira_sparse_attn.argtypes = [IX, P, P, P, I32, I32, P, P, P, P, P, I32, I64, I32, P, P, P, P]
+    lib.hira_sparse_attn_noalloc.restype = C.c_int
+    lib.hira_sparse_attn_noalloc.argtypes = [IX, P, P, P, I32, I32, P, P, P, P, P, I32, I64, I32, P, P, P]
     lib.hira_merge_partials.restype = C.c_int
     lib.hira_merge_partials.argtypes = [P, P, I32, I32, I32, P, P, P]
     lib.hira_append.restype = C.c_int

@@ -334,3 +334,68 @@ extern "C" int hira_merge_partials(const float* part_o, const float* part_ml, in
     HIRA_CHECK_LAUNCH("hira_merge_partials launch");
     return HIRA_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Sparse attention for callers that must not allocate.
+//
+// Some hosts of this library cannot give hira_sparse_attn a workspace: a decode
+// loop that has promised "no cudaMalloc after warm-up" (an allocation can stall
+// every stream of the device), a plugin that only receives input and output
+// buffers from its framework, or a C caller without any device allocator of its
+// own.  For them the split-KV partials live in a fixed array inside the library
+// image.  Every GPU that loads the library carries the array until the process
+// exits, so it is kept modest: HIRA_NOALLOC_SCRATCH_FLOATS floats (4 MiB).
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) float g_attn_scratch[HIRA_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_scratch_ptr[kMaxDevices];  // device address of g_attn_scratch per device, 0 = not looked up yet
+
+// In host code `g_attn_scratch` names a host-side shadow of the symbol, not device
+// memory, so the address a kernel can use has to be asked for -- once per device,
+// with that device current.
+int scratch_for_current_device(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        hira::set_error("hira_sparse_attn_noalloc: cudaGetDevice failed or device index %d is out of range", dev);
+        return HIRA_ERR_CUDA;
+    }
+    if (g_scratch_ptr[dev] == nullptr) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_attn_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            hira::set_error("hira_sparse_attn_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+            return HIRA_ERR_CUDA;
+        }
+        g_scratch_ptr[dev] = p;
+    }
+    *out = g_scratch_ptr[dev];
+    return HIRA_OK;
+}
+}  // namespace
+
+extern "C" int hira_sparse_attn_noalloc(const hira_index_t* ix, const float* q, const float* scaling,
+                                        const int32_t* q2kv, int32_t n_qheads, int32_t tile_parents,
+                                        const int32_t* idx, const float* score, const int32_t* count,
+                                        const void* queued_k, const void* queued_v, int32_t n_queued,
+                                        int64_t queued_head_stride, int32_t n_splits, float* out, float* out_ml,
+                                        void* stream) {
+    HIRA_CHECK_ARG(ix != nullptr, HIRA_ERR_ARG, "hira_sparse_attn_noalloc: index is NULL");
+    HIRA_CHECK_ARG(n_qheads >= 1 && n_splits >= 1 && ix->vdim >= 1, HIRA_ERR_SHAPE,
+                   "hira_sparse_attn_noalloc: n_qheads=%d n_splits=%d vdim=%d", n_qheads, n_splits, ix->vdim);
+    const long long need = (long long)n_qheads * n_splits * (ix->vdim + 2);
+    HIRA_CHECK_ARG(need <= (long long)HIRA_NOALLOC_SCRATCH_FLOATS, HIRA_ERR_CAPACITY,
+                   "hira_sparse_attn_noalloc: n_qheads (%d) x n_splits (%d) x (vdim + 2) (%d) = %lld floats of "
+                   "partials exceed the built-in scratch of %d floats; lower n_splits or call hira_sparse_attn "
+                   "with a workspace of your own",
+                   n_qheads, n_splits, ix->vdim + 2, need, (int)HIRA_NOALLOC_SCRATCH_FLOATS);
+    float* scratch = nullptr;
+    const int rc = scratch_for_current_device(&scratch);
+    if (rc != HIRA_OK) return rc;
+    // every (query head, split) slot of the scratch that the merge reads is written by the
+    // attention kernel of this same call first, so nothing has to be cleared
+    return hira_sparse_attn(ix, q, scaling, q2kv, n_qheads, tile_parents, idx, score, count, queued_k, queued_v,
+                            n_queued, queued_head_stride, n_splits, scratch, out, out_ml, stream);
+}

@@ -158,6 +158,29 @@ int hira_sparse_attn(const hira_index_t* index, const float* q,
                      int64_t queued_head_stride, int32_t n_splits,
                      float* workspace, float* out, float* out_ml, void* stream);
 
+/* hira_sparse_attn without a caller workspace.  No counterpart in the reference: it
+ * exists for callers that cannot allocate device memory at this point -- a decode
+ * loop that must not call cudaMalloc after warm-up, a plugin that is handed only its
+ * inputs and outputs, a C host with no device allocator.  The split-KV partials go to
+ * an array built into the library (HIRA_NOALLOC_SCRATCH_FLOATS floats = 4 MiB, held on
+ * every GPU that loads the library until the process exits); the call fails with
+ * HIRA_ERR_CAPACITY when n_qheads * n_splits * (vdim + 2) is larger than that.
+ * Same arguments and results as hira_sparse_attn minus `workspace`.  It calls no
+ * cudaMalloc / cudaFree and no allocating library routine.  The first call on a device
+ * looks up the array's device address (with that device current): make that call
+ * before any stream capture begins.  All calls share the one array, which keeps the
+ * previous call's partials; nothing in it needs clearing, but two calls that overlap
+ * on the GPU (different streams, or different threads) race on it. */
+#define HIRA_NOALLOC_SCRATCH_FLOATS (1 << 20)
+int hira_sparse_attn_noalloc(const hira_index_t* index, const float* q,
+                             const float* scaling, const int32_t* q2kv,
+                             int32_t n_qheads, int32_t tile_parents,
+                             const int32_t* idx, const float* score,
+                             const int32_t* count, const void* queued_k,
+                             const void* queued_v, int32_t n_queued,
+                             int64_t queued_head_stride, int32_t n_splits,
+                             float* out, float* out_ml, void* stream);
+
 /* Log-sum-exp merge of partial softmax results (used across sequence shards
  * after an all-gather).  part_o [n_parts][n_qheads][vdim] holds NORMALISED
  * outputs, part_ml [n_parts][n_qheads][2] their (m, l).  Writes the normalised

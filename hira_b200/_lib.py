@@ -23,6 +23,7 @@ HIRA_TAU_SAMPLE_MAX, HIRA_TAU_SAMPLE_MEAN_TOPK, HIRA_TAU_SAMPLE_KTH = 0, 1, 2
 EXPORTED_SYMBOLS = [
     "hira_last_error", "hira_version", "hira_search_tile_parents", "hira_search",
     "hira_attn_default_splits", "hira_sparse_attn", "hira_merge_partials", "hira_append",
+    "hira_append_workspace_bytes",
     "hira_threshold", "hira_kth_score", "hira_build_workspace_bytes", "hira_build",
     "hira_recompute_radii", "hira_export", "hira_assign", "hira_sparse_attn_noalloc",
 ]
@@ -65,7 +66,9 @@ def _declare(lib):
     lib.hira_merge_partials.restype = C.c_int
     lib.hira_merge_partials.argtypes = [P, P, I32, I32, I32, P, P, P]
     lib.hira_append.restype = C.c_int
-    lib.hira_append.argtypes = [IX, P, P, I32, I64, I64, I32, P, P]
+    lib.hira_append.argtypes = [IX, P, P, I32, I64, I64, I32, P, P, SZ, P]
+    lib.hira_append_workspace_bytes.restype = SZ
+    lib.hira_append_workspace_bytes.argtypes = [IX, I32]
     lib.hira_threshold.restype = C.c_int
     lib.hira_threshold.argtypes = [P, I32, I32, I32, I32, I64, P, P, I32, I32, I32, P, P]
     lib.hira_kth_score.restype = C.c_int

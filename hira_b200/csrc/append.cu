@@ -23,6 +23,7 @@ constexpr int APPEND_THREADS = 512;
 constexpr int APPEND_HW = APPEND_THREADS / GROUP;  // 8-lane groups: one centre row per group per step
 constexpr int APPEND_UNROLL = 4;
 
+struct BestRec;
 struct AppendParams {
     hira_index_t ix;
     const void* new_k;
@@ -31,7 +32,13 @@ struct AppendParams {
     long long k_head_stride, v_head_stride;
     int token_base;
     int32_t* status;
+    // two-kernel path: partial arg-mins of the scan kernel, [head][key][part], or NULL
+    struct BestRec* partial;
+    int n_parts;
 };
+
+struct BestRec { float s; int i; };
+constexpr int APPEND_MAX_STAGED = 32;  // keys per call the two-kernel path handles
 
 struct Best { float s; int i; };
 
@@ -39,29 +46,35 @@ __device__ __forceinline__ bool better(float s, int i, const Best& b) {
     return s < b.s || (s == b.s && i < b.i);
 }
 
-// arg-min of sq[p] - 2 x.c_p over p in [0, n) with valid(p); all threads get it
-template <typename T, int NCH, typename Valid>
+// arg-min of sq[p] - 2 x.c_p over p in [0, n) with valid(p); all threads get it.
+// Rows, norms and validity are fetched side by side (an invalid slot inside the scanned
+// range is an all-zero row, so reading it is harmless); validity only masks the compare.
+template <typename T, int NCH, int TH, typename Valid>
 __device__ Best nearest_row(const T* rows, const float* sq, int n, const float (&x)[NCH][8], int dim,
                             Valid valid, Best* s_best) {
+    constexpr int NG = TH / GROUP;
     const int tid = threadIdx.x, lane = tid & (GROUP - 1), hw = tid / GROUP;
     Best best{CUDART_INF_F, 0x7fffffff};
-    for (int p0 = 0; p0 < n; p0 += APPEND_HW * APPEND_UNROLL) {  // uniform trip count
+    for (int p0 = 0; p0 < n; p0 += NG * APPEND_UNROLL) {  // uniform trip count
         RawChunk<T> raw[APPEND_UNROLL][NCH];
         bool ok[APPEND_UNROLL];
+        float sqv[APPEND_UNROLL];
 #pragma unroll
         for (int u = 0; u < APPEND_UNROLL; ++u) {
-            const int p = p0 + u * APPEND_HW + hw;
-            ok[u] = p < n && valid(p);
+            const int p = p0 + u * NG + hw;
+            const bool in = p < n;
 #pragma unroll
             for (int i = 0; i < NCH; ++i) {
                 const int c = lane + GROUP * i;
-                if (ok[u] && c * 8 < dim) raw[u][i] = load_chunk_coherent<T>(rows + (size_t)p * dim, c);
+                if (in && c * 8 < dim) raw[u][i] = load_chunk_coherent<T>(rows + (size_t)p * dim, c);
                 else raw[u][i] = zero_chunk<T>();
             }
+            sqv[u] = in ? sq[p] : 0.f;
+            ok[u] = in && valid(p);
         }
 #pragma unroll
         for (int u = 0; u < APPEND_UNROLL; ++u) {
-            const int p = p0 + u * APPEND_HW + hw;
+            const int p = p0 + u * NG + hw;
             Acc2 acc{0.f, 0.f};
 #pragma unroll
             for (int i = 0; i < NCH; ++i) {
@@ -70,26 +83,67 @@ __device__ Best nearest_row(const T* rows, const float* sq, int n, const float (
                 chunk_fma(acc, a, x[i]);
             }
             const float d = group_sum(__fadd_rn(acc.e, acc.o));
-            if (ok[u]) {
-                const float s = __fsub_rn(sq[p], __fmul_rn(2.0f, d));
-                if (better(s, p, best)) best = Best{s, p};
-            }
+            const float s = __fsub_rn(sqv[u], __fmul_rn(2.0f, d));
+            if (ok[u] && better(s, p, best)) best = Best{s, p};
         }
     }
     __syncthreads();
     if (lane == 0) s_best[hw] = best;
     __syncthreads();
     Best b = s_best[0];
-    for (int w = 1; w < APPEND_HW; ++w)
+    for (int w = 1; w < NG; ++w)
         if (better(s_best[w].s, s_best[w].i, b)) b = s_best[w];
     __syncthreads();
     return b;
+}
+
+// Stage 1 of the two-kernel path: CTA (part, head) scans its slice of the parents that are
+// valid when the call starts, for every new key, and writes one partial arg-min each.  The
+// parents a call creates itself are not in this scan; stage 2 adds them from its own list.
+constexpr int SCAN_THREADS = 256;
+
+template <typename T, int NCH>
+__global__ void __launch_bounds__(SCAN_THREADS, NCH == 2 ? 3 : 1)
+append_scan_kernel(const AppendParams P) {
+    __shared__ Best s_best[SCAN_THREADS / GROUP];
+    const hira_index_t& ix = P.ix;
+    const int h = blockIdx.y, part = blockIdx.x;
+    const int lane = threadIdx.x & (GROUP - 1);
+    const int bf = ix.bf, dim = ix.dim;
+    const size_t capP = ix.cap_parents, capG = ix.cap_gp;
+    const T* parents = reinterpret_cast<const T*>(ix.parents) + (size_t)h * capP * dim;
+    const float* psq = ix.parent_sqnorm + (size_t)h * capP;
+    const int32_t* gc = ix.depth == 3 ? ix.gp_counts + (size_t)h * capG : nullptr;
+    const int32_t* used = ix.used + (size_t)h * 4;
+    const int n_scan = ix.depth == 3 ? used[1] * bf : used[0];
+    const int per = (n_scan + P.n_parts - 1) / P.n_parts;
+    const int lo = min(n_scan, part * per), hi = min(n_scan, lo + per);
+    const T* new_k = reinterpret_cast<const T*>(P.new_k) + (size_t)h * P.k_head_stride;
+    for (int key = 0; key < P.n_new; ++key) {
+        float x[NCH][8];
+        load_vec<T, NCH>(new_k + (size_t)key * dim, x, lane, dim);
+        Best b;
+        if (ix.depth == 3)
+            b = nearest_row<T, NCH, SCAN_THREADS>(parents + (size_t)lo * dim, psq + lo, hi - lo, x, dim,
+                                                  [&](int p) { return ((p + lo) % bf) < gc[(p + lo) / bf]; }, s_best);
+        else
+            b = nearest_row<T, NCH, SCAN_THREADS>(parents + (size_t)lo * dim, psq + lo, hi - lo, x, dim,
+                                                  [&](int) { return true; }, s_best);
+        if (threadIdx.x == 0) {
+            BestRec r;
+            r.s = b.s;
+            r.i = b.i == 0x7fffffff ? b.i : b.i + lo;
+            P.partial[((size_t)h * P.n_new + key) * P.n_parts + part] = r;
+        }
+    }
 }
 
 template <typename T, typename TV, int NCH, int NVCH>
 __global__ void __launch_bounds__(APPEND_THREADS)
 append_kernel(const AppendParams P) {
     __shared__ Best s_best[APPEND_HW];
+    __shared__ int s_newp[APPEND_MAX_STAGED];  // parents created earlier in this call (two-kernel path)
+    int n_newp = 0;
     const hira_index_t& ix = P.ix;
     const int h = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & (GROUP - 1), hw = tid / GROUP;
@@ -120,12 +174,36 @@ append_kernel(const AppendParams P) {
 
         // ---- nearest valid parent ---------------------------------------------
         Best bp;
-        if (ix.depth == 3) {
+        if (P.partial != nullptr) {
+            // arg-min over the scanned slices, then over the parents this call created itself
+            bp = Best{CUDART_INF_F, 0x7fffffff};
+            const BestRec* pr_ = P.partial + ((size_t)h * P.n_new + key) * P.n_parts;
+            for (int s2 = 0; s2 < P.n_parts; ++s2) {
+                const BestRec r = pr_[s2];
+                if (better(r.s, r.i, bp)) bp = Best{r.s, r.i};
+            }
+            for (int e = 0; e < n_newp; ++e) {  // uniform trip count; every group computes the same row
+                const int p = s_newp[e];
+                Acc2 acc{0.f, 0.f};
+#pragma unroll
+                for (int i = 0; i < NCH; ++i) {
+                    const int c = lane + GROUP * i;
+                    if (c * 8 < dim) {
+                        float a[8];
+                        to_float(load_chunk_coherent<T>(parents + (size_t)p * dim, c), a);
+                        chunk_fma(acc, a, x[i]);
+                    }
+                }
+                const float d = group_sum(__fadd_rn(acc.e, acc.o));
+                const float sc = __fsub_rn(psq[p], __fmul_rn(2.0f, d));
+                if (better(sc, p, bp)) bp = Best{sc, p};
+            }
+        } else if (ix.depth == 3) {
             const int n_scan = used_g * bf;
-            bp = nearest_row<T, NCH>(parents, psq, n_scan, x, dim,
+            bp = nearest_row<T, NCH, APPEND_THREADS>(parents, psq, n_scan, x, dim,
                                      [&](int p) { return (p % bf) < gc[p / bf]; }, s_best);
         } else {
-            bp = nearest_row<T, NCH>(parents, psq, used_p, x, dim, [&](int) { return true; }, s_best);
+            bp = nearest_row<T, NCH, APPEND_THREADS>(parents, psq, used_p, x, dim, [&](int) { return true; }, s_best);
         }
         const bool have_parent = bp.i != 0x7fffffff;
         const bool placed = have_parent && cc[bp.i] < bf;
@@ -135,7 +213,7 @@ append_kernel(const AppendParams P) {
         if (!placed) {
             if (ix.depth == 3) {
                 // nearest grandparent among those in use (no validity mask: indexer/cuda.py:918-920)
-                const Best bg = nearest_row<T, NCH>(gps, gsq, used_g, x, dim, [&](int) { return true; }, s_best);
+                const Best bg = nearest_row<T, NCH, APPEND_THREADS>(gps, gsq, used_g, x, dim, [&](int) { return true; }, s_best);
                 if (bg.i != 0x7fffffff && gc[bg.i] < bf) {
                     g_dst = bg.i;
                     p_dst = g_dst * bf + gc[g_dst];
@@ -243,6 +321,10 @@ append_kernel(const AppendParams P) {
                 }
             }
         }
+        if (!placed && p_dst >= 0 && P.partial != nullptr && n_newp < APPEND_MAX_STAGED) {
+            if (tid == 0) s_newp[n_newp] = p_dst;
+            ++n_newp;
+        }
         __syncthreads();  // make the insertion visible to the next key's scan
     }
 }
@@ -251,6 +333,12 @@ template <typename T, typename TV>
 static int launch_append(const AppendParams& P, cudaStream_t s) {
     const bool k2 = P.ix.dim > 128, v2 = P.ix.vdim > 128;   // chunks per lane: 2 up to 128 elements, else 4
     const int grid = P.ix.n_heads;
+    if (P.partial != nullptr) {
+        dim3 g1((unsigned)P.n_parts, (unsigned)P.ix.n_heads);
+        if (k2) append_scan_kernel<T, 4><<<g1, SCAN_THREADS, 0, s>>>(P);
+        else append_scan_kernel<T, 2><<<g1, SCAN_THREADS, 0, s>>>(P);
+        HIRA_CHECK_LAUNCH("hira_append scan launch");
+    }
     if (!k2 && !v2) append_kernel<T, TV, 2, 2><<<grid, APPEND_THREADS, 0, s>>>(P);
     else if (k2 && !v2) append_kernel<T, TV, 4, 2><<<grid, APPEND_THREADS, 0, s>>>(P);
     else if (!k2 && v2) append_kernel<T, TV, 2, 4><<<grid, APPEND_THREADS, 0, s>>>(P);
@@ -263,9 +351,23 @@ static int launch_append(const AppendParams& P, cudaStream_t s) {
 
 using namespace hira;
 
+static int append_parts(const hira_index_t* ix) {
+    // enough CTAs to fill the GPU, slices of at least 128 parents
+    int parts = (8 * 148 + ix->n_heads - 1) / ix->n_heads;
+    const int max_parts = ix->cap_parents / 128;
+    if (parts > max_parts) parts = max_parts;
+    if (parts > 64) parts = 64;
+    return parts < 1 ? 1 : parts;
+}
+
+extern "C" size_t hira_append_workspace_bytes(const hira_index_t* ix, int32_t n_new) {
+    if (!ix || n_new < 1 || n_new > APPEND_MAX_STAGED || ix->n_heads < 1 || ix->cap_parents < 1) return 0;
+    return (size_t)ix->n_heads * n_new * append_parts(ix) * sizeof(BestRec);
+}
+
 extern "C" int hira_append(const hira_index_t* ix, const void* new_k, const void* new_v, int32_t n_new,
                            int64_t k_head_stride, int64_t v_head_stride, int32_t token_base,
-                           int32_t* status, void* stream) {
+                           int32_t* status, void* workspace, size_t workspace_bytes, void* stream) {
     int rc = validate_index(ix, false);
     if (rc != HIRA_OK) return rc;
     HIRA_CHECK_ARG(new_k && status, HIRA_ERR_ARG, "hira_append: new_k and status must not be NULL");
@@ -279,6 +381,12 @@ extern "C" int hira_append(const hira_index_t* ix, const void* new_k, const void
     P.ix = *ix; P.new_k = new_k; P.new_v = new_v; P.n_new = n_new;
     P.k_head_stride = k_head_stride; P.v_head_stride = v_head_stride;
     P.token_base = token_base; P.status = status;
+    P.partial = nullptr; P.n_parts = 0;
+    const size_t need = hira_append_workspace_bytes(ix, n_new);
+    if (workspace != nullptr && need > 0 && workspace_bytes >= need && append_parts(ix) > 1) {
+        P.partial = reinterpret_cast<BestRec*>(workspace);
+        P.n_parts = append_parts(ix);
+    }
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const bool kb = ix->dtype == HIRA_BF16, vb = ix->vdtype == HIRA_BF16 || !ix->values;
     if (kb && vb) return launch_append<__nv_bfloat16, __nv_bfloat16>(P, s);

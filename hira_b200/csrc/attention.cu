@@ -53,13 +53,17 @@ __global__ void __launch_bounds__(ATTN_THREADS)
 sparse_attn_kernel(const AttnParams P) {
     __shared__ int s_idx[ATTN_CHUNK];
     __shared__ float s_logit[ATTN_CHUNK];
+    __shared__ int s_cnt[ATTN_THREADS];
+    __shared__ int s_off[ATTN_THREADS + 1];
     __shared__ float s_red[ATTN_HW];
     __shared__ float s_bcast;
+    __shared__ int s_end;
     extern __shared__ __align__(16) float s_out[];  // [ATTN_HW][vdim]
 
     const int tid = threadIdx.x;
     const int lane = tid & (GROUP - 1);
     const int hw = tid / GROUP;
+    const int warp = tid >> 5, wl = tid & 31;
     const int qh = blockIdx.y;
     const int split = blockIdx.x;
     const int h = P.q2kv ? P.q2kv[qh] : qh / P.group;
@@ -68,7 +72,7 @@ sparse_attn_kernel(const AttnParams P) {
     const int t1 = (int)(((long long)(split + 1) * P.n_tiles) / P.n_splits);
 
     float m = -CUDART_INF_F;
-    float l = 0.f;  // this half-warp's share of the denominator
+    float l = 0.f;  // this group's share of the denominator
     float acc[NVCH][8];
 #pragma unroll
     for (int i = 0; i < NVCH; ++i)
@@ -84,7 +88,7 @@ sparse_attn_kernel(const AttnParams P) {
         for (int i = tid; i < fill; i += ATTN_THREADS) mx = fmaxf(mx, s_logit[i]);
 #pragma unroll
         for (int s = 16; s >= 1; s >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, s));
-        if ((tid & 31) == 0) s_red[tid >> 5] = mx;
+        if (wl == 0) s_red[warp] = mx;
         __syncthreads();
         if (tid == 0) {
             float v = s_red[0];
@@ -137,16 +141,57 @@ sparse_attn_kernel(const AttnParams P) {
     };
 
     // ---- emitted children of this split's tiles -------------------------------
-    for (int t = t0; t < t1; ++t) {
-        const int c = P.count[(size_t)qh * P.n_tiles + t];
-        if (c == 0) continue;
-        if (fill + c > ATTN_CHUNK) flush();
-        const size_t base = (size_t)qh * P.cap_children + (size_t)t * P.tile_rows;
-        for (int i = tid; i < c; i += ATTN_THREADS) {
-            s_idx[fill + i] = P.idx[base + i];
-            s_logit[fill + i] = P.score[base + i];
+    // The per-tile counts of a batch of tiles are fetched together and prefix-summed, then
+    // the warps copy the tiles' (slot, logit) segments into the staging list side by side:
+    // two memory latencies per batch instead of two per tile.
+    for (int tb = t0; tb < t1; tb += ATTN_THREADS) {
+        const int nb = min(ATTN_THREADS, t1 - tb);
+        const int my_cnt = tid < nb ? P.count[(size_t)qh * P.n_tiles + tb + tid] : 0;
+        __syncthreads();
+        s_cnt[tid] = my_cnt;
+        // inclusive scan over the warp, then over the warp totals
+        int v = my_cnt;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int o = __shfl_up_sync(0xffffffffu, v, d);
+            if (wl >= d) v += o;
         }
-        fill += c;
+        if (wl == 31) s_off[ATTN_THREADS - 8 + warp] = v;   // parked in the tail of s_off until combined
+        __syncthreads();
+        int wbase = 0;
+        for (int w = 0; w < warp; ++w) wbase += s_off[ATTN_THREADS - 8 + w];
+        __syncthreads();
+        s_off[tid + 1] = wbase + v;
+        if (tid == 0) s_off[0] = 0;
+        __syncthreads();
+        int b0 = 0;
+        while (b0 < nb) {
+            // largest e with s_off[e] - s_off[b0] <= room left in the staging list
+            if (tid == 0) {
+                int e = b0;
+                const int room = ATTN_CHUNK - fill;
+                while (e < nb && s_off[e + 1] - s_off[b0] <= room) ++e;
+                s_end = e;
+            }
+            __syncthreads();
+            const int e = s_end;
+            if (e == b0) {  // the next tile does not fit: drain the list first (a tile never exceeds the list)
+                flush();
+                continue;
+            }
+            for (int t = b0 + warp; t < e; t += ATTN_THREADS / 32) {
+                const int c = s_cnt[t];
+                const int o = fill + s_off[t] - s_off[b0];
+                const size_t base = (size_t)qh * P.cap_children + (size_t)(tb + t) * P.tile_rows;
+                for (int i = wl; i < c; i += 32) {
+                    s_idx[o + i] = P.idx[base + i];
+                    s_logit[o + i] = P.score[base + i];
+                }
+            }
+            fill += s_off[e] - s_off[b0];
+            b0 = e;
+            __syncthreads();
+        }
     }
 
     // ---- queued (not yet indexed) keys: split 0 only ---------------------------
@@ -159,24 +204,21 @@ sparse_attn_kernel(const AttnParams P) {
         while (j0 < P.n_queued) {
             if (fill == ATTN_CHUNK) flush();
             const int n = min(P.n_queued - j0, ATTN_CHUNK - fill);
-            for (int b = 0; b < n; b += ATTN_HW) {  // uniform trip count: shuffles inside
+            for (int b = 0; b < n; b += ATTN_HW) {  // uniform trip count
                 const int j = b + hw;
-                float d = 0.f;
-                {
-                    Acc2 a2{0.f, 0.f};
-                    if (j < n) {
+                Acc2 a2{0.f, 0.f};
+                if (j < n) {
 #pragma unroll
-                        for (int i = 0; i < NCH; ++i) {
-                            const int c = lane + GROUP * i;
-                            if (c * 8 < P.dim) {
-                                float a[8];
-                                to_float(load_chunk<TK>(qk + (size_t)(j0 + j) * P.dim, c), a);
-                                chunk_fma(a2, a, qreg[i]);
-                            }
+                    for (int i = 0; i < NCH; ++i) {
+                        const int c = lane + GROUP * i;
+                        if (c * 8 < P.dim) {
+                            float a[8];
+                            to_float(load_chunk<TK>(qk + (size_t)(j0 + j) * P.dim, c), a);
+                            chunk_fma(a2, a, qreg[i]);
                         }
                     }
-                    d = group_sum(__fadd_rn(a2.e, a2.o));
                 }
+                const float d = group_sum(__fadd_rn(a2.e, a2.o));
                 if (lane == 0 && j < n) {
                     s_idx[fill + j] = QUEUE_FLAG | (j0 + j);
                     s_logit[fill + j] = __fmul_rn(d, scale);
@@ -188,7 +230,7 @@ sparse_attn_kernel(const AttnParams P) {
     }
     if (fill > 0) flush();
 
-    // ---- combine the half-warps ------------------------------------------------
+    // ---- combine the groups ----------------------------------------------------
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < NVCH; ++i) {

@@ -218,16 +218,24 @@ def merge_partials(part_o, part_ml, out=None, out_ml=None):
     return out
 
 
-def append(st: IndexState, new_k: torch.Tensor, new_v: Optional[torch.Tensor], token_base: int = -1):
+def append(st: IndexState, new_k: torch.Tensor, new_v: Optional[torch.Tensor], token_base: int = -1,
+           use_workspace: bool = True):
     """new_k (n_heads, M, D), new_v (n_heads, M, V) contiguous, index dtypes."""
     lib = L.load()
     assert new_k.is_contiguous() and new_k.dtype == st.dtype
     m = new_k.shape[1]
     if new_v is not None:
         assert new_v.is_contiguous() and new_v.dtype == st.vdtype
+    ws, nbytes = None, 0
+    if use_workspace:
+        nbytes = int(lib.hira_append_workspace_bytes(st.struct, m))
+        if nbytes:
+            ws = getattr(st, "_append_ws", None)
+            if ws is None or ws.numel() < nbytes:
+                ws = st._append_ws = torch.empty((nbytes,), dtype=torch.uint8, device=st.device)
     rc = lib.hira_append(st.struct, L.ptr(new_k), L.ptr(new_v), m, m * st.dim,
                          m * st.vdim if new_v is not None else 0, token_base, L.ptr(st.status),
-                         L.current_stream(st.device))
+                         L.ptr(ws), nbytes, L.current_stream(st.device))
     L.check(rc, "hira_append")
 
 

@@ -206,10 +206,17 @@ int hira_merge_partials(const float* part_o, const float* part_ml,
  *   token_base: token position of new key 0 is token_base + used[h][2]
  *          when token_base < 0, else token_base + i
  *   status: device int32, OR-ed with HIRA_STATUS_* on capacity exhaustion
+ *   workspace: optional scratch of hira_append_workspace_bytes(index, n_new)
+ *          bytes (0 = not applicable, for n_new > 32).  With it the parent scan is
+ *          spread over the whole GPU (one kernel scans slices, a second one picks
+ *          the arg-min and inserts); without it (NULL) one CTA per head does
+ *          everything.  The result is identical either way.
  */
+size_t hira_append_workspace_bytes(const hira_index_t* index, int32_t n_new);
 int hira_append(const hira_index_t* index, const void* new_k, const void* new_v,
                 int32_t n_new, int64_t k_head_stride, int64_t v_head_stride,
-                int32_t token_base, int32_t* status, void* stream);
+                int32_t token_base, int32_t* status, void* workspace,
+                size_t workspace_bytes, void* stream);
 
 /* ------------------------------------------------------------------------- */
 /* Threshold finder (the reference names sample_max / sample_mean_topk but

@@ -165,6 +165,23 @@ def test_append_matches_oracle(h, n, d, bf, depth, dtype, m):
     _run_search_case(st, ox, q, tau, L.HIRA_GATE_GE | L.HIRA_LEAF_GE)
 
 
+def test_append_with_and_without_workspace_agree():
+    # the scan spread over the GPU (two kernels, scratch) and the one-CTA-per-head path give the same index
+    h, n, d, bf = 2, 8192, 128, 32
+    a, ox, keys, vals = build_both(h, n, d, bf, 3, torch.bfloat16, seed=61, spare=40 * bf)
+    b, _, _, _ = build_both(h, n, d, bf, 3, torch.bfloat16, seed=61, spare=40 * bf)
+    new_k = make_keys(h, 24, d, 62, torch.bfloat16)
+    new_v = make_keys(h, 24, d, 63, torch.bfloat16, normalize=False)
+    for lo, hi in ((0, 1), (1, 2), (2, 10), (10, 24)):
+        S.append(a, new_k[:, lo:hi].contiguous(), new_v[:, lo:hi].contiguous(), use_workspace=True)
+        S.append(b, new_k[:, lo:hi].contiguous(), new_v[:, lo:hi].contiguous(), use_workspace=False)
+        O.append(ox, new_k[:, lo:hi].contiguous(), new_v[:, lo:hi].contiguous())
+    torch.cuda.synchronize()
+    assert int(L.load().hira_append_workspace_bytes(a.struct, 1)) > 0
+    assert_index_equal(a, ox, "append with workspace")
+    assert_index_equal(b, ox, "append without workspace")
+
+
 def test_append_capacity_status():
     h, n, d, bf = 1, 64, 32, 8
     st, ox, keys, vals = build_both(h, n, d, bf, 2, torch.float32, seed=5, spare=2)

@@ -40,6 +40,10 @@ KEEP_FRAC = 0.02
 ROPE_BASE = 500000.0
 OUTLIER_CHANNELS = (7, 42, 71, 110)
 N_QUERY_SETS = 4
+# DRAM bytes (read + write) of one search_kernel launch per (batch, kv head) group of 131,072 keys, from
+# the ncu capture summarised in profiles/search_kernel_bf16_g4_batch2_ctx131072.md (16 groups:
+# 559.04 MB read + 6.08 MB written); traffic grows in proportion to the groups a launch covers.
+SEARCH_DRAM_BYTES_PER_GROUP_AT_CTX = (559.043840e6 + 6.076416e6) / 16
 
 
 def peaks():
@@ -308,7 +312,8 @@ def run_ours(args):
         "e2e": {"value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]},
         "gpu_launches": args.steps * 4,
         "roofline": {"bound": "hbm", "kernel": "search_kernel", "achieved": achieved, "peak": peak,
-                     "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                     "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": (SEARCH_DRAM_BYTES_PER_GROUP_AT_CTX * n_groups if ctx == CTX else None),
                      "algorithmic_bytes_per_launch": search_bytes},
         "breakdown_us": {"search": search_ms * 1e3, "sparse_attn": attn_ms * 1e3, "append": append_ms * 1e3},
         "step_hbm": {"bytes": step_bytes, "achieved_gbs": step_bytes / (ms_per_step * 1e-3) / 1e9,

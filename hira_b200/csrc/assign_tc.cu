@@ -1,17 +1,293 @@
-// Tensor-core (tcgen05 / TMEM) nearest-centroid assignment for bf16 points.
+// Tensor-core nearest-centroid assignment (the dense contraction of the index build,
+// torch.cdist + argmin at indexer/cuda.py:244-245) for bf16 points with D = 128.
+//
+// Per CTA: one tile of 128 points (A, 32 KB, loaded once by TMA) against all centroids of
+// the head in tiles of 128 (B, 32 KB per tile, double-buffered TMA).  One elected thread
+// issues tcgen05.mma (M=128, N=128, K=16, bf16 in, fp32 accumulate in TMEM: 128 lanes x 128
+// columns), tcgen05.commit signals an mbarrier, then each of the 128 threads reads its own
+// point's row of the accumulator with tcgen05.ld and folds score = ||c||^2 - 2 x.c into a
+// running arg-min, so the (points x centroids) matrix never leaves the SM.  Two CTAs are
+// resident per SM, so one CTA's arg-min epilogue overlaps the other's MMAs.
+//
+// Every wait on an mbarrier is bounded; on a timeout the CTA writes index -1 for its points
+// and leaves in an orderly way (TMEM freed).  No TMA multicast is used.
 #include "common.cuh"
+
+#include <cuda.h>
+#include <math_constants.h>
 
 namespace hira {
 
-bool assign_tc_supported(int dtype, int n, int k, int dim) {
-    (void)dtype; (void)n; (void)k; (void)dim;
-    return false;
+constexpr int TC_BM = 128;       // points per CTA
+constexpr int TC_BN = 128;       // centroids per tile
+constexpr int TC_K = 128;        // D
+constexpr int TC_BOX_K = 64;     // elements per 128-byte swizzle row
+constexpr int TC_BOX_BYTES = TC_BM * TC_BOX_K * 2;   // 16 KB
+constexpr int TC_THREADS = 128;
+constexpr unsigned long long TC_WAIT_CYCLES = 400ull * 1000 * 1000;  // ~0.2 s
+
+struct TcSmem {
+    // offsets in the 1024-byte aligned dynamic shared memory
+    static constexpr int A = 0;                          // 2 boxes
+    static constexpr int B = 2 * TC_BOX_BYTES;           // 2 stages x 2 boxes
+    static constexpr int CSQ = B + 4 * TC_BOX_BYTES;     // 128 floats
+    static constexpr int BAR = CSQ + TC_BN * 4;          // bar_a, bar_b[2], bar_mma
+    static constexpr int TMEM_SLOT = BAR + 4 * 8;
+    static constexpr int TOTAL = TMEM_SLOT + 16;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait: false on timeout
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if ((unsigned long long)(clock64() - t0) > TC_WAIT_CYCLES) return false;
+    }
+    return true;
 }
 
-int launch_assign_tc(const void*, long long, const void*, const float*, int, int, int, int, int32_t*, float*,
-                     cudaStream_t) {
-    set_error("tensor-core assignment is not available for this shape");
-    return HIRA_ERR_ARG;
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
+
+// K-major operand tile, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3ffff) >> 4);        // start address
+    d |= (uint64_t)1 << 16;                          // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                          // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
+    return d;
+}
+
+// kind::f16, D = fp32, A = B = bf16, both K-major, M = 128, N = 128
+constexpr uint32_t TC_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 2)
+assign_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 const __nv_bfloat16* __restrict__ points, long long p_head_stride,
+                 const float* __restrict__ csq, int n, int k, int32_t* __restrict__ out_idx,
+                 float* __restrict__ out_d2) {
+    extern __shared__ unsigned char tc_smem_raw[];
+    unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t s_base = smem_u32(sm);
+    float* s_csq = reinterpret_cast<float*>(sm + TcSmem::CSQ);
+    volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(sm + TcSmem::TMEM_SLOT);
+    const uint32_t bar_a = s_base + TcSmem::BAR, bar_b0 = bar_a + 8, bar_mma = bar_a + 24;
+    __shared__ int s_fail;
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int h = blockIdx.y;
+    const int m0 = blockIdx.x * TC_BM;
+    const int nt = (k + TC_BN - 1) / TC_BN;
+
+    if (tid == 0) {
+        s_fail = 0;
+        mbar_init(bar_a, 1);
+        mbar_init(bar_b0, 1);
+        mbar_init(bar_b0 + 8, 1);
+        mbar_init(bar_mma, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();   // thread 0 took the branch above: reconverge before the warp-wide allocation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(s_base + TcSmem::TMEM_SLOT), "r"(TC_BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *s_tmem;
+
+    if (tid == 0) {
+        mbar_expect_tx(bar_a, 2 * TC_BOX_BYTES);
+        tma_load_3d(s_base + TcSmem::A, &map_a, 0, m0, h, bar_a);
+        tma_load_3d(s_base + TcSmem::A + TC_BOX_BYTES, &map_a, TC_BOX_K, m0, h, bar_a);
+        mbar_expect_tx(bar_b0, 2 * TC_BOX_BYTES);
+        tma_load_3d(s_base + TcSmem::B, &map_b, 0, 0, h, bar_b0);
+        tma_load_3d(s_base + TcSmem::B + TC_BOX_BYTES, &map_b, TC_BOX_K, 0, h, bar_b0);
+    }
+
+    float best = CUDART_INF_F;
+    int best_i = 0x7fffffff;
+    bool failed = false;
+    for (int j = 0; j < nt; ++j) {
+        const int st = j & 1;
+        // centroid norms of this tile (+inf past the last centroid: never the arg-min)
+        {
+            const int c = j * TC_BN + tid;
+            s_csq[tid] = c < k ? csq[(size_t)h * k + c] : CUDART_INF_F;
+        }
+        if (tid == 0) {
+            if (j + 1 < nt) {   // prefetch the next centroid tile; its stage was released by the MMAs of tile j-1
+                const uint32_t bar = bar_b0 + 8 * ((j + 1) & 1);
+                const uint32_t dst = s_base + TcSmem::B + ((j + 1) & 1) * 2 * TC_BOX_BYTES;
+                mbar_expect_tx(bar, 2 * TC_BOX_BYTES);
+                tma_load_3d(dst, &map_b, 0, (j + 1) * TC_BN, h, bar);
+                tma_load_3d(dst + TC_BOX_BYTES, &map_b, TC_BOX_K, (j + 1) * TC_BN, h, bar);
+            }
+            bool ok = true;
+            if (j == 0) ok = mbar_wait(bar_a, 0);
+            ok = ok && mbar_wait(bar_b0 + 8 * st, (j >> 1) & 1);
+            if (!ok) s_fail = 1;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (ok) {
+                const uint32_t a0 = s_base + TcSmem::A, b0 = s_base + TcSmem::B + st * 2 * TC_BOX_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < TC_K / 16; ++ks) {
+                    const uint32_t off = (ks >> 2) * TC_BOX_BYTES + (ks & 3) * 32;
+                    umma_f16(tmem, umma_desc(a0 + off), umma_desc(b0 + off), TC_IDESC, ks > 0 ? 1u : 0u);
+                }
+            }
+            umma_commit(bar_mma);   // arrives when the MMAs above (if any) are complete
+        }
+        __syncthreads();            // s_csq written, s_fail visible
+        if (!mbar_wait(bar_mma, j & 1)) failed = true;
+        if (s_fail) failed = true;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (!failed) {
+#pragma unroll 1
+            for (int cb = 0; cb < TC_BN; cb += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + cb, r);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float s = __fmaf_rn(-2.0f, __uint_as_float(r[i]), s_csq[cb + i]);  // 2*x.c is exact: same bits as csq - 2*dot
+                    if (s < best) { best = s; best_i = j * TC_BN + cb + i; }   // ascending centroid id: ties keep the lowest
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        failed = __syncthreads_or(failed);   // accumulator and s_csq may be overwritten; one verdict for the CTA
+        if (failed) break;
+    }
+
+    const int p = m0 + tid;
+    if (p < n) {
+        if (failed) {
+            out_idx[(size_t)h * n + p] = -1;
+            out_d2[(size_t)h * n + p] = 0.f;
+        } else {
+            const __nv_bfloat16* row = points + (size_t)h * p_head_stride + (size_t)p * TC_K;
+            float xsq = 0.f;
+#pragma unroll 4
+            for (int c = 0; c < TC_K / 8; ++c) {
+                float f[8];
+                unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(row) + c), f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) xsq = __fmaf_rn(f[e], f[e], xsq);
+            }
+            out_idx[(size_t)h * n + p] = best_i;
+            out_d2[(size_t)h * n + p] = fmaxf(__fadd_rn(xsq, best), 0.f);
+        }
+    }
+    if (failed && tid == 0 && nt > 0) {
+        // let copies that may still be in flight land before the shared memory is given back (bounded)
+        mbar_wait(bar_b0, 0);
+        mbar_wait(bar_b0 + 8, 0);
+    }
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_BN) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// rows x 128 bf16 per head, head stride in elements; box = 64 elements x 128 rows, 128-byte swizzle
+static bool make_map(CUtensorMap* map, const void* base, long long rows, long long head_stride, int n_heads) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[3] = {(cuuint64_t)TC_K, (cuuint64_t)rows, (cuuint64_t)n_heads};
+    const cuuint64_t strides[2] = {(cuuint64_t)TC_K * 2, (cuuint64_t)head_stride * 2};
+    const cuuint32_t box[3] = {(cuuint32_t)TC_BOX_K, (cuuint32_t)TC_BM, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool assign_tc_supported(int dtype, int n, int k, int dim) {
+    return dtype == HIRA_BF16 && dim == TC_K && n >= 1 && k >= 1;
+}
+
+int launch_assign_tc(const void* points, long long p_head_stride, const void* cents, const float* csq,
+                     int n_heads, int n, int k, int dim, int32_t* out_idx, float* out_d2, cudaStream_t s) {
+    HIRA_CHECK_ARG(dim == TC_K, HIRA_ERR_SHAPE, "tensor-core assignment needs dim == %d", TC_K);
+    HIRA_CHECK_ARG(((uintptr_t)points & 15) == 0 && ((uintptr_t)cents & 15) == 0 && (p_head_stride % 8) == 0,
+                   HIRA_ERR_ARG, "tensor-core assignment needs 16-byte aligned rows");
+    CUtensorMap map_a, map_b;
+    if (!make_map(&map_a, points, n, p_head_stride, n_heads) || !make_map(&map_b, cents, k, (long long)k * TC_K, n_heads)) {
+        set_error("tensor-core assignment: cuTensorMapEncodeTiled failed or is unavailable");
+        return HIRA_ERR_CUDA;
+    }
+    const size_t smem = TcSmem::TOTAL + 1024;
+    cudaError_t e = cudaFuncSetAttribute(assign_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { set_error("assign_tc: cudaFuncSetAttribute: %s", cudaGetErrorString(e)); return HIRA_ERR_CUDA; }
+    dim3 grid((unsigned)((n + TC_BM - 1) / TC_BM), (unsigned)n_heads);
+    assign_tc_kernel<<<grid, TC_THREADS, smem, s>>>(map_a, map_b, reinterpret_cast<const __nv_bfloat16*>(points),
+                                                    p_head_stride, csq, n, k, out_idx, out_d2);
+    HIRA_CHECK_LAUNCH("assign_tc launch");
+    return HIRA_OK;
 }
 
 }  // namespace hira

@@ -291,6 +291,55 @@ def test_assign_matches_oracle():
         assert np.array_equal(d2.cpu().numpy().view(np.uint32), o_d2.view(np.uint32))
 
 
+@pytest.mark.parametrize("h,n,k", [(1, 128, 128), (3, 1000, 300), (2, 4096, 128), (1, 50, 7)])
+def test_assign_tensor_cores(h, n, k):
+    # tcgen05 accumulates in hardware order, so a near-tie may resolve differently from the
+    # fp32 FMA chain: the chosen centroid must be (numerically) a nearest one
+    torch.backends.cuda.matmul.allow_tf32 = False
+    pts = make_keys(h, n, 128, 71, torch.bfloat16, normalize=False)
+    cents = make_keys(h, k, 128, 72, torch.bfloat16, normalize=False)
+    idx, d2 = S.assign(pts, cents, use_tensor_cores=True)
+    torch.cuda.synchronize()
+    assert int(idx.min()) >= 0 and int(idx.max()) < k, "the kernel reported a timeout (-1) or an out-of-range centroid"
+    full = torch.cdist(pts.float(), cents.float()) ** 2                     # (h, n, k)
+    best = full.min(dim=2).values
+    chosen = full.gather(2, idx.long().unsqueeze(-1)).squeeze(-1)
+    assert float((chosen - best).max()) <= 1e-3 * float(best.max())
+    torch.testing.assert_close(d2, best, atol=2e-2, rtol=1e-4)
+    cc_idx, _ = S.assign(pts, cents, use_tensor_cores=False)
+    assert float((idx == cc_idx).float().mean()) > 0.999
+
+
+def test_build_with_tensor_cores_gives_a_valid_index():
+    h, n, d, bf = 2, 4096, 128, 32
+    keys = make_keys(h, n, d, 81, torch.bfloat16)
+    vals = make_keys(h, n, d, 82, torch.bfloat16, normalize=False)
+    st = new_state(h, d, bf, 3, (n // bf // bf) * bf, torch.bfloat16)
+    S.build(st, keys, vals, n_iters=2, use_tensor_cores=True)
+    torch.cuda.synchronize()
+    assert int((st.slot2token >= 0).sum()) == h * n and int(st.child_counts.sum()) == h * n
+    tok = st.slot2token.clamp_min(0).long()
+    ok = st.slot2token >= 0
+    assert torch.equal(st.children[ok], keys.gather(1, tok.unsqueeze(-1).expand(-1, -1, d))[ok])
+    # radii really bound their children
+    pc = st.children.float().view(h, -1, bf, d)
+    dist = (pc - st.parents.float()[:, :, None, :]).norm(dim=-1)
+    slot_ok = torch.arange(bf, device="cuda")[None, None, :] < st.child_counts[:, :, None]
+    assert bool((dist[slot_ok] <= st.parent_radii[:, :, None].expand_as(dist)[slot_ok] + 1e-4).all())
+    # and the search over it still equals brute force
+    q = make_queries(h * 4, d, seed=83)
+    sc = torch.einsum("hnd,hgd->hgn", keys.float(), q.view(h, 4, d)).reshape(h * 4, n)
+    tau = torch.sort(sc, dim=-1).values[:, int(n * 0.95)].contiguous()
+    _, c = S.search(st, q, tau, flags=L.HIRA_GATE_GE | L.HIRA_LEAF_GE, want_compact=True)
+    sets = compact_sets(c)
+    s2t = st.slot2token.cpu().numpy()
+    for qh in range(h * 4):
+        got = set(s2t[qh // 4, sets[qh][0]].tolist())
+        must = set(torch.nonzero(sc[qh] > tau[qh] + 1e-4).flatten().tolist())
+        never = set(torch.nonzero(sc[qh] < tau[qh] - 1e-4).flatten().tolist())
+        assert must <= got and not (got & never)
+
+
 def test_export_roundtrip():
     st, ox, keys, vals = build_both(2, 500, 64, 8, 3, torch.bfloat16, seed=29)
     k, v = S.export(st, 500)

@@ -24,7 +24,7 @@ EXPORTED_SYMBOLS = [
     "hira_last_error", "hira_version", "hira_search_tile_parents", "hira_search",
     "hira_attn_default_splits", "hira_sparse_attn", "hira_merge_partials", "hira_append",
     "hira_append_workspace_bytes",
-    "hira_threshold", "hira_kth_score", "hira_build_workspace_bytes", "hira_build",
+    "hira_threshold", "hira_kth_score", "hira_prepare_query", "hira_build_workspace_bytes", "hira_build",
     "hira_recompute_radii", "hira_export", "hira_assign", "hira_sparse_attn_noalloc",
 ]
 NOALLOC_SCRATCH_FLOATS = 1 << 20
@@ -71,6 +71,8 @@ def _declare(lib):
     lib.hira_append_workspace_bytes.argtypes = [IX, I32]
     lib.hira_threshold.restype = C.c_int
     lib.hira_threshold.argtypes = [P, I32, I32, I32, I32, I64, P, P, I32, I32, I32, P, P]
+    lib.hira_prepare_query.restype = C.c_int
+    lib.hira_prepare_query.argtypes = [P, I32, I32, I32, C.c_float, P, P, P]
     lib.hira_kth_score.restype = C.c_int
     lib.hira_kth_score.argtypes = [IX, I32, I32, P, P, P, P, P]
     lib.hira_build_workspace_bytes.restype = SZ

@@ -66,11 +66,19 @@ def hira_decode_attention(query: torch.Tensor, cache_output, *, scaling: Optiona
     b, hq, lq, d = query.shape
     if lq != 1:
         raise NotImplementedError("hira_decode_attention handles one query token per step")
-    q = query.reshape(b * hq, d).to(device=st.device, dtype=torch.float32)
-    qn = q.norm(dim=-1).clamp_min(1e-20)
-    q_hat = (q / qn[:, None]).contiguous()
+    q = query.reshape(b * hq, d)
+    if q.device != st.device or q.dtype not in (torch.float32, torch.bfloat16):
+        q = q.to(device=st.device, dtype=torch.float32)
     sm_scale = float(scaling) if scaling is not None else d ** -0.5
-    logit_scale = (qn * sm_scale).contiguous()
+    bufs = getattr(searcher, "_decode_bufs", None)
+    if bufs is None or bufs[0].shape != (b * hq, d) or bufs[0].device != st.device:
+        bufs = (torch.empty((b * hq, d), dtype=torch.float32, device=st.device),
+                torch.empty((b * hq,), dtype=torch.float32, device=st.device))
+        try:
+            searcher._decode_bufs = bufs
+        except AttributeError:
+            pass
+    q_hat, logit_scale = S.prepare_query(q.contiguous(), sm_scale, bufs[0], bufs[1])
     if threshold is None:
         samples = _samples_for(indexer, sample_size)
         fn = THRESHOLD_METHODS[threshold_method]
@@ -87,7 +95,13 @@ def hira_decode_attention(query: torch.Tensor, cache_output, *, scaling: Optiona
         qv = cache_output.queued_values
         queued_v = qv.reshape(-1, qv.shape[-2], qv.shape[-1]).to(st.vdtype).contiguous()
     q2kv, _ = srch._coerce_q2kv(q_head_to_kv, b * hq, st.n_heads, st.device)
-    out = S.sparse_attn(st, q_hat, logit_scale, compact, q2kv=q2kv, queued_k=queued_k, queued_v=queued_v)
+    n_splits = S.attn_splits(st, b * hq, compact.tile_parents)
+    ws = getattr(srch, "_attn_ws", None)
+    need = b * hq * n_splits * (st.vdim + 2)
+    if ws is None or ws.numel() < need or ws.device != st.device:
+        ws = srch._attn_ws = torch.empty((need,), dtype=torch.float32, device=st.device)
+    out = S.sparse_attn(st, q_hat, logit_scale, compact, q2kv=q2kv, queued_k=queued_k, queued_v=queued_v,
+                        n_splits=n_splits, workspace=ws)
     out = out.reshape(b, hq, 1, st.vdim)
     return (out, compact) if return_compact else out
 

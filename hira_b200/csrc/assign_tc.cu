@@ -6,8 +6,9 @@
 // issues tcgen05.mma (M=128, N=128, K=16, bf16 in, fp32 accumulate in TMEM: 128 lanes x 128
 // columns), tcgen05.commit signals an mbarrier, then each of the 128 threads reads its own
 // point's row of the accumulator with tcgen05.ld and folds score = ||c||^2 - 2 x.c into a
-// running arg-min, so the (points x centroids) matrix never leaves the SM.  Two CTAs are
-// resident per SM, so one CTA's arg-min epilogue overlaps the other's MMAs.
+// running arg-min, so the (points x centroids) matrix never leaves the SM.  Two TMEM
+// accumulators alternate (the MMAs of the next centroid tile run while the previous one is
+// read out) and two CTAs are resident per SM.
 //
 // Every wait on an mbarrier is bounded; on a timeout the CTA writes index -1 for its points
 // and leaves in an orderly way (TMEM freed).  No TMA multicast is used.
@@ -23,16 +24,15 @@ constexpr int TC_BN = 128;       // centroids per tile
 constexpr int TC_K = 128;        // D
 constexpr int TC_BOX_K = 64;     // elements per 128-byte swizzle row
 constexpr int TC_BOX_BYTES = TC_BM * TC_BOX_K * 2;   // 16 KB
-constexpr int TC_THREADS = 128;
+constexpr int TC_THREADS = 160;      // 4 epilogue warps + 1 producer/MMA warp
 constexpr unsigned long long TC_WAIT_CYCLES = 400ull * 1000 * 1000;  // ~0.2 s
 
 struct TcSmem {
     // offsets in the 1024-byte aligned dynamic shared memory
     static constexpr int A = 0;                          // 2 boxes
     static constexpr int B = 2 * TC_BOX_BYTES;           // 2 stages x 2 boxes
-    static constexpr int CSQ = B + 4 * TC_BOX_BYTES;     // 128 floats
-    static constexpr int BAR = CSQ + TC_BN * 4;          // bar_a, bar_b[2], bar_mma
-    static constexpr int TMEM_SLOT = BAR + 4 * 8;
+    static constexpr int BAR = B + 4 * TC_BOX_BYTES;     // bar_a, bar_b[2], bar_bfree[2], bar_full[2], bar_empty[2]
+    static constexpr int TMEM_SLOT = BAR + 9 * 8;
     static constexpr int TOTAL = TMEM_SLOT + 16;
 };
 
@@ -105,6 +105,14 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Warps 0-3 (128 threads) own the 128 TMEM lanes = the 128 points and run the arg-min
+// epilogue; lane 0 of warp 4 issues the TMA loads and the MMAs.  Two accumulators (2 x 128
+// TMEM columns) alternate, so the MMAs of centroid tile j+1 run while tile j is being read
+// out.  All hand-offs are mbarriers with bounded waits.
 __global__ void __launch_bounds__(TC_THREADS, 2)
 assign_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __nv_bfloat16* __restrict__ points, long long p_head_stride,
@@ -113,9 +121,12 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     extern __shared__ unsigned char tc_smem_raw[];
     unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(tc_smem_raw) + 1023) & ~(uintptr_t)1023);
     const uint32_t s_base = smem_u32(sm);
-    float* s_csq = reinterpret_cast<float*>(sm + TcSmem::CSQ);
     volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(sm + TcSmem::TMEM_SLOT);
-    const uint32_t bar_a = s_base + TcSmem::BAR, bar_b0 = bar_a + 8, bar_mma = bar_a + 24;
+    const uint32_t bar_a = s_base + TcSmem::BAR;
+    const uint32_t bar_b = bar_a + 8;        // [2] centroid tile landed
+    const uint32_t bar_bfree = bar_a + 24;   // [2] MMAs that read the stage are complete
+    const uint32_t bar_full = bar_a + 40;    // [2] accumulator written
+    const uint32_t bar_empty = bar_a + 56;   // [2] accumulator read out by all 128 epilogue threads
     __shared__ int s_fail;
 
     const int tid = threadIdx.x, warp = tid >> 5;
@@ -126,114 +137,151 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (tid == 0) {
         s_fail = 0;
         mbar_init(bar_a, 1);
-        mbar_init(bar_b0, 1);
-        mbar_init(bar_b0 + 8, 1);
-        mbar_init(bar_mma, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_b + 8 * i, 1);
+            mbar_init(bar_bfree + 8 * i, 1);
+            mbar_init(bar_full + 8 * i, 1);
+            mbar_init(bar_empty + 8 * i, TC_BM);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 0) {
-        __syncwarp();   // thread 0 took the branch above: reconverge before the warp-wide allocation
+    if (warp == 4) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(s_base + TcSmem::TMEM_SLOT), "r"(TC_BN) : "memory");
+                     ::"r"(s_base + TcSmem::TMEM_SLOT), "r"(2 * TC_BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *s_tmem;
-
-    if (tid == 0) {
-        mbar_expect_tx(bar_a, 2 * TC_BOX_BYTES);
-        tma_load_3d(s_base + TcSmem::A, &map_a, 0, m0, h, bar_a);
-        tma_load_3d(s_base + TcSmem::A + TC_BOX_BYTES, &map_a, TC_BOX_K, m0, h, bar_a);
-        mbar_expect_tx(bar_b0, 2 * TC_BOX_BYTES);
-        tma_load_3d(s_base + TcSmem::B, &map_b, 0, 0, h, bar_b0);
-        tma_load_3d(s_base + TcSmem::B + TC_BOX_BYTES, &map_b, TC_BOX_K, 0, h, bar_b0);
-    }
-
-    float best = CUDART_INF_F;
-    int best_i = 0x7fffffff;
     bool failed = false;
-    for (int j = 0; j < nt; ++j) {
-        const int st = j & 1;
-        // centroid norms of this tile (+inf past the last centroid: never the arg-min)
-        {
-            const int c = j * TC_BN + tid;
-            s_csq[tid] = c < k ? csq[(size_t)h * k + c] : CUDART_INF_F;
-        }
-        if (tid == 0) {
-            if (j + 1 < nt) {   // prefetch the next centroid tile; its stage was released by the MMAs of tile j-1
-                const uint32_t bar = bar_b0 + 8 * ((j + 1) & 1);
-                const uint32_t dst = s_base + TcSmem::B + ((j + 1) & 1) * 2 * TC_BOX_BYTES;
-                mbar_expect_tx(bar, 2 * TC_BOX_BYTES);
-                tma_load_3d(dst, &map_b, 0, (j + 1) * TC_BN, h, bar);
-                tma_load_3d(dst + TC_BOX_BYTES, &map_b, TC_BOX_K, (j + 1) * TC_BN, h, bar);
-            }
-            bool ok = true;
-            if (j == 0) ok = mbar_wait(bar_a, 0);
-            ok = ok && mbar_wait(bar_b0 + 8 * st, (j >> 1) & 1);
-            if (!ok) s_fail = 1;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (ok) {
+
+    if (warp == 4) {
+        if (tid == 4 * 32) {
+            // ---- producer + MMA issuer -------------------------------------------------------
+            mbar_expect_tx(bar_a, 2 * TC_BOX_BYTES);
+            tma_load_3d(s_base + TcSmem::A, &map_a, 0, m0, h, bar_a);
+            tma_load_3d(s_base + TcSmem::A + TC_BOX_BYTES, &map_a, TC_BOX_K, m0, h, bar_a);
+            mbar_expect_tx(bar_b, 2 * TC_BOX_BYTES);
+            tma_load_3d(s_base + TcSmem::B, &map_b, 0, 0, h, bar_b);
+            tma_load_3d(s_base + TcSmem::B + TC_BOX_BYTES, &map_b, TC_BOX_K, 0, h, bar_b);
+            for (int j = 0; j < nt && !failed; ++j) {
+                const int st = j & 1;
+                if (j + 1 < nt) {
+                    // the other stage held tile j-1: refill it once those MMAs are complete
+                    const int s2 = (j + 1) & 1;
+                    if (j >= 1 && !mbar_wait(bar_bfree + 8 * s2, ((j - 1) >> 1) & 1)) { failed = true; break; }
+                    const uint32_t dst = s_base + TcSmem::B + s2 * 2 * TC_BOX_BYTES;
+                    mbar_expect_tx(bar_b + 8 * s2, 2 * TC_BOX_BYTES);
+                    tma_load_3d(dst, &map_b, 0, (j + 1) * TC_BN, h, bar_b + 8 * s2);
+                    tma_load_3d(dst + TC_BOX_BYTES, &map_b, TC_BOX_K, (j + 1) * TC_BN, h, bar_b + 8 * s2);
+                }
+                bool ok = true;
+                if (j == 0) ok = mbar_wait(bar_a, 0);
+                ok = ok && mbar_wait(bar_b + 8 * st, (j >> 1) & 1);
+                if (ok && j >= 2) ok = mbar_wait(bar_empty + 8 * st, ((j - 2) >> 1) & 1);   // accumulator drained
+                if (!ok) { failed = true; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t a0 = s_base + TcSmem::A, b0 = s_base + TcSmem::B + st * 2 * TC_BOX_BYTES;
 #pragma unroll
                 for (int ks = 0; ks < TC_K / 16; ++ks) {
                     const uint32_t off = (ks >> 2) * TC_BOX_BYTES + (ks & 3) * 32;
-                    umma_f16(tmem, umma_desc(a0 + off), umma_desc(b0 + off), TC_IDESC, ks > 0 ? 1u : 0u);
+                    umma_f16(tmem + st * TC_BN, umma_desc(a0 + off), umma_desc(b0 + off), TC_IDESC, ks > 0 ? 1u : 0u);
                 }
+                umma_commit(bar_bfree + 8 * st);
+                umma_commit(bar_full + 8 * st);
             }
-            umma_commit(bar_mma);   // arrives when the MMAs above (if any) are complete
+            if (failed) s_fail = 1;
         }
-        __syncthreads();            // s_csq written, s_fail visible
-        if (!mbar_wait(bar_mma, j & 1)) failed = true;
-        if (s_fail) failed = true;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (!failed) {
+    } else {
+        // ---- arg-min epilogue: thread t owns point m0 + t = TMEM lane t ------------------------
+        float best = CUDART_INF_F;
+        int best_i = 0x7fffffff;
+        const float* cs = csq + (size_t)h * k;
+        const bool cs_aligned = (reinterpret_cast<uintptr_t>(cs) & 15) == 0;
+        for (int j = 0; j < nt; ++j) {
+            const int st = j & 1;
+            if (!mbar_wait(bar_full + 8 * st, (j >> 1) & 1) || *reinterpret_cast<volatile int*>(&s_fail)) { failed = true; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const bool full_tile = (j + 1) * TC_BN <= k;
 #pragma unroll 1
             for (int cb = 0; cb < TC_BN; cb += 32) {
                 uint32_t r[32];
-                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + cb, r);
+                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + st * TC_BN + cb, r);
+                // scores of 32 centroids and their minimum; the index is looked up only when the
+                // running minimum improves (rare after the first tiles), which keeps the common
+                // path at one load, one FMA and one min per element
+                const int c0 = j * TC_BN + cb;
+                const float* cp = cs + c0;
+                float cq[32];
+                if (full_tile && cs_aligned) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float s = __fmaf_rn(-2.0f, __uint_as_float(r[i]), s_csq[cb + i]);  // 2*x.c is exact: same bits as csq - 2*dot
-                    if (s < best) { best = s; best_i = j * TC_BN + cb + i; }   // ascending centroid id: ties keep the lowest
+                    for (int i = 0; i < 8; ++i) {
+                        const float4 v = __ldg(reinterpret_cast<const float4*>(cp) + i);
+                        cq[4 * i] = v.x; cq[4 * i + 1] = v.y; cq[4 * i + 2] = v.z; cq[4 * i + 3] = v.w;
+                    }
+                } else if (full_tile) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) cq[i] = __ldg(cp + i);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) cq[i] = (c0 + i < k) ? __ldg(cp + i) : CUDART_INF_F;  // past the last centroid
+                }
+                float sc[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    sc[i] = __fmaf_rn(-2.0f, __uint_as_float(r[i]), cq[i]);  // 2*x.c is exact: same bits as csq - 2*dot
+                float m01[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) m01[i] = fminf(sc[2 * i], sc[2 * i + 1]);
+#pragma unroll
+                for (int w = 8; w >= 1; w >>= 1)
+#pragma unroll
+                    for (int i = 0; i < w; ++i) m01[i] = fminf(m01[i], m01[i + w]);
+                const float cmin = m01[0];
+                if (cmin < best) {   // strict: an equal score later in the scan never replaces an earlier centroid
+                    best = cmin;
+                    int first = 31;
+#pragma unroll
+                    for (int i = 30; i >= 0; --i)
+                        if (sc[i] == cmin) first = i;
+                    best_i = c0 + first;
                 }
             }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(bar_empty + 8 * st);
         }
-        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-        failed = __syncthreads_or(failed);   // accumulator and s_csq may be overwritten; one verdict for the CTA
-        if (failed) break;
-    }
-
-    const int p = m0 + tid;
-    if (p < n) {
-        if (failed) {
-            out_idx[(size_t)h * n + p] = -1;
-            out_d2[(size_t)h * n + p] = 0.f;
-        } else {
-            const __nv_bfloat16* row = points + (size_t)h * p_head_stride + (size_t)p * TC_K;
-            float xsq = 0.f;
+        const int p = m0 + tid;
+        if (p < n) {
+            if (failed) {
+                out_idx[(size_t)h * n + p] = -1;
+                out_d2[(size_t)h * n + p] = 0.f;
+            } else {
+                const __nv_bfloat16* row = points + (size_t)h * p_head_stride + (size_t)p * TC_K;
+                float xsq = 0.f;
 #pragma unroll 4
-            for (int c = 0; c < TC_K / 8; ++c) {
-                float f[8];
-                unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(row) + c), f);
+                for (int c = 0; c < TC_K / 8; ++c) {
+                    float f[8];
+                    unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(row) + c), f);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) xsq = __fmaf_rn(f[e], f[e], xsq);
+                    for (int e = 0; e < 8; ++e) xsq = __fmaf_rn(f[e], f[e], xsq);
+                }
+                out_idx[(size_t)h * n + p] = best_i;
+                out_d2[(size_t)h * n + p] = fmaxf(__fadd_rn(xsq, best), 0.f);
             }
-            out_idx[(size_t)h * n + p] = best_i;
-            out_d2[(size_t)h * n + p] = fmaxf(__fadd_rn(xsq, best), 0.f);
         }
     }
-    if (failed && tid == 0 && nt > 0) {
+    if (tid == 4 * 32 && failed) {
         // let copies that may still be in flight land before the shared memory is given back (bounded)
-        mbar_wait(bar_b0, 0);
-        mbar_wait(bar_b0 + 8, 0);
+        mbar_wait(bar_b, 0);
+        mbar_wait(bar_b + 8, 0);
     }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 0) {
+    if (warp == 4) {
         __syncwarp();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * TC_BN) : "memory");
     }
 }
 

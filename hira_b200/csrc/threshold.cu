@@ -138,9 +138,47 @@ kth_kernel(const float* __restrict__ score, const int32_t* __restrict__ count, l
     if (tid == 0) tau_out[qh] = fail ? -CUDART_INF_F : key_to_float(prefix);
 }
 
+// q_hat = q / ||q|| (fp32) and the per-head logit scale ||q|| * softmax_scale: the unit query
+// and `scaling` the reference's searchers expect (searcher/cpu.py:58-63), in one launch.
+template <typename T>
+__global__ void __launch_bounds__(128)
+prepare_query_kernel(const T* __restrict__ q, int dim, float sm_scale, float* __restrict__ q_hat,
+                     float* __restrict__ logit_scale) {
+    __shared__ float s_part[4];
+    const int qh = blockIdx.x, tid = threadIdx.x;
+    const T* row = q + (size_t)qh * dim;
+    float acc = 0.f;
+    for (int d = tid; d < dim; d += 128) {
+        const float v = (float)row[d];
+        acc = __fmaf_rn(v, v, acc);
+    }
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if ((tid & 31) == 0) s_part[tid >> 5] = acc;
+    __syncthreads();
+    const float nrm = fmaxf(__fsqrt_rn(s_part[0] + s_part[1] + s_part[2] + s_part[3]), 1e-20f);
+    for (int d = tid; d < dim; d += 128) q_hat[(size_t)qh * dim + d] = __fdiv_rn((float)row[d], nrm);
+    if (tid == 0) logit_scale[qh] = nrm * sm_scale;
+}
+
 }  // namespace hira
 
 using namespace hira;
+
+extern "C" int hira_prepare_query(const void* q, int32_t dtype, int32_t n_qheads, int32_t dim, float sm_scale,
+                                  float* q_hat, float* logit_scale, void* stream) {
+    HIRA_CHECK_ARG(q && q_hat && logit_scale, HIRA_ERR_ARG, "hira_prepare_query: NULL argument");
+    HIRA_CHECK_ARG(dtype == HIRA_F32 || dtype == HIRA_BF16, HIRA_ERR_DTYPE, "hira_prepare_query: dtype %d", dtype);
+    HIRA_CHECK_ARG(n_qheads >= 1 && dim >= 1, HIRA_ERR_SHAPE, "hira_prepare_query: n_qheads=%d dim=%d", n_qheads, dim);
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    if (dtype == HIRA_BF16)
+        prepare_query_kernel<<<n_qheads, 128, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(q), dim, sm_scale, q_hat, logit_scale);
+    else
+        prepare_query_kernel<<<n_qheads, 128, 0, s>>>(reinterpret_cast<const float*>(q), dim, sm_scale, q_hat, logit_scale);
+    HIRA_CHECK_LAUNCH("hira_prepare_query launch");
+    return HIRA_OK;
+}
+
 
 extern "C" int hira_threshold(const void* samples, int32_t dtype, int32_t n_heads, int32_t n_samples,
                               int32_t dim, int64_t head_stride, const float* q, const int32_t* q2kv,

@@ -252,6 +252,20 @@ def threshold(samples: torch.Tensor, q: torch.Tensor, method: int, k: int = 1, q
     return out
 
 
+def prepare_query(q: torch.Tensor, sm_scale: float, q_hat=None, logit_scale=None):
+    """q (H_q, D) fp32/bf16 contiguous -> (q_hat (H_q, D) fp32, logit_scale (H_q,) fp32)."""
+    lib = L.load()
+    hq, d = q.shape
+    if q_hat is None:
+        q_hat = torch.empty((hq, d), dtype=torch.float32, device=q.device)
+    if logit_scale is None:
+        logit_scale = torch.empty((hq,), dtype=torch.float32, device=q.device)
+    rc = lib.hira_prepare_query(L.ptr(q), L.dtype_code(q.dtype), hq, d, float(sm_scale), L.ptr(q_hat),
+                                L.ptr(logit_scale), L.current_stream(q.device))
+    L.check(rc, "hira_prepare_query")
+    return q_hat, logit_scale
+
+
 def kth_score(st: IndexState, compact: CompactResult, k: torch.Tensor, out=None):
     lib = L.load()
     hq = compact.idx.shape[0]

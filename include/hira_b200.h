@@ -229,6 +229,13 @@ int hira_threshold(const void* samples, int32_t dtype, int32_t n_heads,
                    const float* q, const int32_t* q2kv, int32_t n_qheads,
                    int32_t method, int32_t k, float* tau_out, void* stream);
 
+/* Query preparation for a decode step: q_hat[qh] = q[qh] / ||q[qh]|| in fp32 and
+ * logit_scale[qh] = ||q[qh]|| * sm_scale, i.e. the unit query the tree bound assumes and the
+ * `scaling` that turns emitted scores into attention logits (searcher/cpu.py:58-63).
+ *   q [n_qheads][dim] in `dtype` (dense). */
+int hira_prepare_query(const void* q, int32_t dtype, int32_t n_qheads, int32_t dim,
+                       float sm_scale, float* q_hat, float* logit_scale, void* stream);
+
 /* Exact k-th largest of the scores in a compacted search output (run
  * hira_search with HIRA_LEAF_CANDIDATES, tau = -inf and scaling = NULL first).
  * k [n_qheads] int32 per-head ranks (1 = largest).  tau_out[qh] = that score,

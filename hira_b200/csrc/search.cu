@@ -51,7 +51,7 @@ struct SearchParams {
     int32_t* out_count;
     uint32_t* stats;
     int n_heads, n_qheads, group, depth, bf, dim;
-    int cap_parents, cap_gp, tile_parents, n_tiles, flags;
+    int cap_parents, cap_gp, tile_parents, n_tiles, n_chunks, flags;
     uint32_t ring_offset;     // byte offset of the per-thread prefetch ring in dynamic shared memory
     uint32_t bf_magic;        // ceil(2^32 / bf): x / bf == __umulhi(x, bf_magic) for x < 2^20, bf <= 1024
 };
@@ -157,9 +157,11 @@ search_kernel(const SearchParams P) {
     const int grp = tid / GROUP;         // group id: one row per group per step
     const int warp = tid >> 5;
     const int wl = tid & 31;
-    const int tile = blockIdx.x % P.n_tiles;
-    const int h = blockIdx.x / P.n_tiles;
-    const int chunk = blockIdx.y;
+    // chunks of one tile are neighbours in the grid: they run at the same time and the later
+    // ones find the tile's rows in L2
+    const int chunk = blockIdx.x % P.n_chunks;
+    const int tile = (blockIdx.x / P.n_chunks) % P.n_tiles;
+    const int h = blockIdx.x / (P.n_chunks * P.n_tiles);
     const bool ge = P.flags & HIRA_GATE_GE;
     const int leaf_mode = P.flags & (HIRA_LEAF_GE | HIRA_LEAF_GT);
     const bool has_qn = P.qnorm != nullptr;
@@ -539,8 +541,8 @@ search_kernel(const SearchParams P) {
 
 template <typename T, int GT, int NCH, int STAGES, int MINB, bool FULLD>
 static int launch_search_fd(SearchParams P, int chunks, cudaStream_t stream) {
-    constexpr int SEARCH_THREADS = GT == 8 ? 256 : 128;   // one compaction warp per head
-    constexpr int BLOCKS = GT == 8 ? MINB : 2 * MINB;     // MINB counts 256-thread blocks per SM
+    constexpr int SEARCH_THREADS = 128;    // 4 warps: one compaction warp per head
+    constexpr int BLOCKS = 2 * MINB;       // MINB counts 256-thread blocks per SM
     auto kern = search_kernel<T, GT, NCH, STAGES, BLOCKS, FULLD, SEARCH_THREADS>;
     const size_t tile_rows = (size_t)P.tile_parents * P.bf;
     size_t off = tile_rows * GT * sizeof(float) + (size_t)P.tile_parents * (4 + 2 + 1 + 1);
@@ -555,7 +557,8 @@ static int launch_search_fd(SearchParams P, int chunks, cudaStream_t stream) {
             return HIRA_ERR_CUDA;
         }
     }
-    dim3 grid((unsigned)(P.n_heads * P.n_tiles), (unsigned)chunks);
+    P.n_chunks = chunks;
+    dim3 grid((unsigned)((size_t)P.n_heads * P.n_tiles * chunks));
     kern<<<grid, SEARCH_THREADS, smem, stream>>>(P);
     HIRA_CHECK_LAUNCH("hira_search launch");
     return HIRA_OK;
@@ -580,7 +583,7 @@ static int tuning_variant() {
 template <typename T, int NCH>
 static int dispatch_gt(const SearchParams& P, int max_group, cudaStream_t stream) {
     int gt = 1;
-    while (gt < max_group && gt < 8) gt <<= 1;
+    while (gt < max_group && gt < 4) gt <<= 1;   // larger groups run as several 4-head chunks sharing L2
     if (NCH == 4 && gt > 2) gt = 2;  // D > 128: keep the query registers within budget
     const int chunks = (max_group + gt - 1) / gt;
     constexpr bool BF = sizeof(T) == 2;
@@ -602,7 +605,6 @@ static int dispatch_gt(const SearchParams& P, int max_group, cudaStream_t stream
     }
     if constexpr (NCH < 4) {
         if (gt == 4) return launch_search<T, 4, NCH, ST, 2>(P, chunks, stream);
-        return launch_search<T, 8, NCH, ST, 1>(P, chunks, stream);
     }
     set_error("hira_search: internal dispatch error");
     return HIRA_ERR_ARG;

@@ -115,12 +115,16 @@ class CUDAIndexer(BaseIndexer):
 
     def _capacity_parents(self, n_keys: int) -> int:
         bf = self.branching_factor
+        k1 = max(1, -(-n_keys // bf))
         if self.max_context is None:
-            return max(1, -(-n_keys // bf))
-        # room for max_context keys: full parents for the built prefix plus, in the
-        # worst case, one new parent per appended key
-        n_ctx = max(self.max_context, n_keys)
-        return max(1, -(-n_keys // bf)) + (n_ctx - n_keys)
+            return k1
+        # room for max_context keys.  Worst case of the append rule: every appended key finds
+        # its nearest parent full and opens a new parent -- and, with three levels, finds its
+        # nearest grandparent full too and opens a whole new grandparent block.
+        extra = max(self.max_context, n_keys) - n_keys
+        if self.depth == CUDAIndexer.DEPTH.THREE_LEVELS:
+            return (-(-k1 // bf) + extra) * bf
+        return k1 + extra
 
     @torch.no_grad()
     def build(self, keys: torch.Tensor, values: Optional[torch.Tensor] = None):
@@ -136,8 +140,6 @@ class CUDAIndexer(BaseIndexer):
         self.num_heads, self.dim = h, d
         bf = self.branching_factor
         cap_p = self._capacity_parents(n)
-        if self.depth == CUDAIndexer.DEPTH.THREE_LEVELS and self.max_context is not None:
-            cap_p = cap_p + bf  # whole spare grandparent blocks
         st = S.IndexState(n_heads=h, dim=d, vdim=values.shape[-1] if values is not None else 0, bf=bf,
                           depth=self.depth.value, cap_parents=cap_p, dtype=keys.dtype,
                           vdtype=values.dtype if values is not None else None, device=keys.device,

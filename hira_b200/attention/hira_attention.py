@@ -79,6 +79,8 @@ def hira_decode_attention(query: torch.Tensor, cache_output, *, scaling: Optiona
         except AttributeError:
             pass
     q_hat, logit_scale = S.prepare_query(q.contiguous(), sm_scale, bufs[0], bufs[1])
+    if threshold is None and threshold_method == "none":
+        threshold = torch.full((b * hq,), float("-inf"), device=st.device)      # keep every key: dense-equivalent
     if threshold is None:
         samples = _samples_for(indexer, sample_size)
         fn = THRESHOLD_METHODS[threshold_method]
@@ -126,3 +128,29 @@ def hira_attention(module, query: torch.Tensor, key, value=None, attention_mask:
                     topk=getattr(cfg, "topk", 16), gate=getattr(cfg, "gate", "ge"))
     out = hira_decode_attention(query, key, scaling=scaling, threshold=kwargs.get("threshold"), **opts)
     return out.to(query.dtype).transpose(1, 2).contiguous(), None
+
+
+def make_hira_attention(hira_config=None, threshold: Optional[torch.Tensor] = None):
+    """An attention function bound to a HiraConfig, for `AttentionInterface.register`."""
+    def fn(module, query, key, value=None, attention_mask=None, dropout: float = 0.0, scaling=None, **kwargs):
+        kwargs.setdefault("hira_config", hira_config)
+        if threshold is not None:
+            kwargs.setdefault("threshold", threshold)
+        return hira_attention(module, query, key, value, attention_mask, dropout=dropout, scaling=scaling, **kwargs)
+    return fn
+
+
+def register_hira_attention(hira_config=None, name: str = "hira"):
+    """Registers `name` as an attention implementation of Hugging Face models, so that
+    `model.config._attn_implementation = name` (or `attn_implementation=name` at load time)
+    routes every attention layer through the index when `past_key_values` is a HiraCache
+    (the patching the reference sketches in examples/patch_llama.py:22-100).  Masks are built
+    as for SDPA; decode steps ignore them (one sequence, no padding)."""
+    from transformers import AttentionInterface
+    AttentionInterface.register(name, make_hira_attention(hira_config))
+    try:
+        from transformers.masking_utils import AttentionMaskInterface, sdpa_mask
+        AttentionMaskInterface.register(name, sdpa_mask)
+    except Exception:  # older transformers: no separate mask registry
+        pass
+    return name

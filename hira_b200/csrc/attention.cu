@@ -12,10 +12,11 @@
 // four rows in flight per thread; softmax is online in fp32.
 #include "common.cuh"
 #include <math_constants.h>
+#include <stdlib.h>
 
 namespace hira {
 
-constexpr int ATTN_THREADS = 256;
+constexpr int ATTN_THREADS = 128;
 constexpr int ATTN_HW = ATTN_THREADS / GROUP;  // 8-lane groups: one value row per group per step
 constexpr int ATTN_CHUNK = 2048;  // list entries staged in shared memory (>= rows of one search tile)
 constexpr int ATTN_UNROLL = 4;
@@ -312,7 +313,13 @@ using namespace hira;
 
 extern "C" int hira_attn_default_splits(int32_t n_qheads, int32_t n_tiles) {
     if (n_qheads < 1 || n_tiles < 1) return 1;
-    int s = (8 * 148 + n_qheads - 1) / n_qheads;
+    static int factor = 0;   // CTAs per SM aimed for (HIRA_ATTN_SPLIT_FACTOR overrides, for tuning)
+    if (factor == 0) {
+        const char* e = getenv("HIRA_ATTN_SPLIT_FACTOR");
+        factor = e ? atoi(e) : 16;
+        if (factor < 1) factor = 16;
+    }
+    int s = (factor * 148 + n_qheads - 1) / n_qheads;
     if (s > n_tiles) s = n_tiles;
     if (s > 64) s = 64;
     return s < 1 ? 1 : s;

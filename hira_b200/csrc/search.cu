@@ -542,7 +542,7 @@ search_kernel(const SearchParams P) {
 template <typename T, int GT, int NCH, int STAGES, int MINB, bool FULLD>
 static int launch_search_fd(SearchParams P, int chunks, cudaStream_t stream) {
     constexpr int SEARCH_THREADS = 128;    // 4 warps: one compaction warp per head
-    constexpr int BLOCKS = 2 * MINB;       // MINB counts 256-thread blocks per SM
+    constexpr int BLOCKS = MINB;           // 128-thread CTAs resident per SM
     auto kern = search_kernel<T, GT, NCH, STAGES, BLOCKS, FULLD, SEARCH_THREADS>;
     const size_t tile_rows = (size_t)P.tile_parents * P.bf;
     size_t off = tile_rows * GT * sizeof(float) + (size_t)P.tile_parents * (4 + 2 + 1 + 1);
@@ -591,20 +591,20 @@ static int dispatch_gt(const SearchParams& P, int max_group, cudaStream_t stream
     if constexpr (BF && NCH == 2) {
       if (gt == 4) {
         switch (tuning_variant()) {  // prefetch depth / residency of the headline shape
-            case 1: return launch_search<T, 4, NCH, 8, 1>(P, chunks, stream);
-            case 2: return launch_search<T, 4, NCH, 2, 2>(P, chunks, stream);
-            case 3: return launch_search<T, 4, NCH, 3, 2>(P, chunks, stream);
-            default: return launch_search<T, 4, NCH, 4, 2>(P, chunks, stream);
+            case 1: return launch_search<T, 4, NCH, 3, 5>(P, chunks, stream);
+            case 2: return launch_search<T, 4, NCH, 2, 5>(P, chunks, stream);
+            case 3: return launch_search<T, 4, NCH, 2, 6>(P, chunks, stream);
+            default: return launch_search<T, 4, NCH, 4, 4>(P, chunks, stream);
         }
       }
     }
     switch (gt) {
-        case 1: return launch_search<T, 1, NCH, ST, 2>(P, chunks, stream);
-        case 2: return launch_search<T, 2, NCH, ST, NCH == 4 ? 1 : 2>(P, chunks, stream);
+        case 1: return launch_search<T, 1, NCH, ST, 4>(P, chunks, stream);
+        case 2: return launch_search<T, 2, NCH, ST, NCH == 4 ? 2 : 4>(P, chunks, stream);
         default: break;
     }
     if constexpr (NCH < 4) {
-        if (gt == 4) return launch_search<T, 4, NCH, ST, 2>(P, chunks, stream);
+        if (gt == 4) return launch_search<T, 4, NCH, ST, 4>(P, chunks, stream);
     }
     set_error("hira_search: internal dispatch error");
     return HIRA_ERR_ARG;

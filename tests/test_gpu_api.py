@@ -225,3 +225,37 @@ def test_cache_and_attention_end_to_end(dtype, tol):
         torch.testing.assert_close(got2.reshape(b * hq, d)[qh], w @ vv, atol=tol, rtol=tol)
     a, _ = hira_attention(None, q, out, None, None, scaling=d ** -0.5, hira_config=cfg)
     assert tuple(a.shape) == (b, 1, hq, d) and a.dtype == dtype
+
+
+def test_patched_llama_generates_like_dense_attention():
+    """A (tiny, random) Hugging Face Llama with `hira` registered as its attention and a
+    HiraCache as `past_key_values`: with the threshold switched off the index must reproduce
+    dense attention, token for token, through prefill, queued keys and index appends."""
+    from transformers import DynamicCache, LlamaConfig, LlamaForCausalLM
+    from hira_b200 import register_hira_attention
+    torch.manual_seed(0)
+    cfg = LlamaConfig(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=64, max_position_embeddings=2048)
+    model = LlamaForCausalLM(cfg).cuda().eval()
+    ids = torch.randint(0, 512, (1, 300), device="cuda")
+    hcfg = HiraConfig(device_mode="cuda_only", update_every=3, num_levels=3, branching_factor=8, max_context=400,
+                      threshold_method="none")
+    name = register_hira_attention(hcfg)
+    with torch.no_grad():
+        model.config._attn_implementation = "sdpa"
+        ref_cache = DynamicCache(config=cfg)
+        ref = [model(ids, past_key_values=ref_cache, use_cache=True).logits[:, -1]]
+        model.config._attn_implementation = name
+        cache = HiraCache(cfg, hcfg)
+        got = [model(ids, past_key_values=cache, use_cache=True).logits[:, -1]]
+        tok = ref[0].argmax(-1, keepdim=True)
+        for _ in range(7):
+            model.config._attn_implementation = "sdpa"
+            ref.append(model(tok, past_key_values=ref_cache, use_cache=True).logits[:, -1])
+            model.config._attn_implementation = name
+            got.append(model(tok, past_key_values=cache, use_cache=True).logits[:, -1])
+            tok = ref[-1].argmax(-1, keepdim=True)
+    assert cache.get_seq_length(0) == 307
+    for a, b in zip(got, ref):
+        torch.testing.assert_close(a, b, atol=2e-3, rtol=2e-3)
+        assert torch.equal(a.argmax(-1), b.argmax(-1))

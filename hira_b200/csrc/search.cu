@@ -149,7 +149,7 @@ search_kernel(const SearchParams P) {
 
     __shared__ int s_qh[GT];
     __shared__ float s_scale[GT];
-    __shared__ int s_nq, s_npass;
+    __shared__ int s_nq, s_npass, s_dense;
     __shared__ uint32_t s_stat[GT][8];
 
     const int tid = threadIdx.x;
@@ -361,6 +361,7 @@ search_kernel(const SearchParams P) {
         uint32_t* s_pl = reinterpret_cast<uint32_t*>(s_pcount);  // reuses s_pcount after the pass below
         if (warp == 0) {
             int n = 0;
+            bool dense = true;  // every parent slot of the tile is full and kept for every head
             for (int base = 0; base < TP; base += 32) {
                 const int i = base + wl;
                 uint32_t word = 0;
@@ -369,13 +370,18 @@ search_kernel(const SearchParams P) {
                     const uint32_t cnt = (uint32_t)s_pcount[i], msk = s_pmask[i];
                     m = msk != 0 && cnt > 0;
                     word = ((uint32_t)i << 19) | (msk << 11) | cnt;
+                    dense = dense && msk == allmask && cnt == (uint32_t)bf;
                 }
                 const uint32_t b = __ballot_sync(0xffffffffu, m);
                 __syncwarp();  // every lane has read s_pcount[base..base+31] before slots <= base+31 are overwritten
                 if (m) s_pl[n + __popc(b & ((1u << wl) - 1u))] = word;
                 n += __popc(b);
             }
-            if (wl == 0) s_npass = n;
+            dense = __all_sync(0xffffffffu, dense);
+            if (wl == 0) {
+                s_npass = n;
+                s_dense = dense;
+            }
         }
         __syncthreads();
         const int npass = s_npass;
@@ -396,106 +402,160 @@ search_kernel(const SearchParams P) {
         const unsigned char* ring_g = smem_raw + P.ring_offset + tid * 16;
         const int row_bytes = P.dim * (int)sizeof(T);
         const char* gbase = reinterpret_cast<const char*>(children) + tile_c0 * (size_t)row_bytes + lane * 8 * sizeof(T);
-        const int total = npass * bf;
-        int R = (total + SEARCH_GROUPS - 1) / SEARCH_GROUPS;
-        R = (R + SEARCH_RPI - 1) / SEARCH_RPI * SEARCH_RPI;
-        const int n_it = R / SEARCH_RPI;
-
-        // cursor over the rows of this group: parent-list position k, child c, parent word w
-        struct Cursor { int k, c, cnt; uint32_t w; };
-        auto load_parent = [&](Cursor& cu) {
-            cu.w = cu.k < npass ? s_pl[cu.k] : 0u;
-            cu.cnt = (int)(cu.w & 0x7ffu);
-        };
-        Cursor ic, cc;
-        ic.k = div_bf(grp * R, bf, P.bf_magic);
-        ic.c = grp * R - ic.k * bf;
-        load_parent(ic);
-        cc = ic;
-        const char* isrc = gbase + (size_t)((ic.w >> 19) * bf + ic.c) * row_bytes;
-        float* cdst = s_score + (size_t)((cc.w >> 19) * bf + cc.c) * GT + my_head;
-        bool cgate = (cc.w >> (11 + my_head)) & 1u;
         const bool writer = HeadReduce<GT>::is_writer(lane);
         const bool emit_all = leaf_mode == HIRA_LEAF_CANDIDATES;
         // d > tau  <=>  d >= nextafter(tau): one comparison serves both leaf rules
         const float leaf_thr = (leaf_mode == HIRA_LEAF_GT) ? nextafterf(my_tau, CUDART_INF_F) : my_tau;
-
-        auto issue_rows = [&](uint32_t stage_off) {
+        // dot products of the row in ring slot (cons_off, u) with the CTA's heads; the lane
+        // returns the one of its own head
+        auto row_score = [&](uint32_t cons_off, int u) -> float {
+            Acc2 acc[GT];
 #pragma unroll
-            for (int u = 0; u < SEARCH_RPI; ++u) {
-                if (ic.c < ic.cnt) {
+            for (int j = 0; j < GT; ++j) acc[j] = Acc2{0.f, 0.f};
+#pragma unroll
+            for (int ci = 0; ci < NCH; ++ci) {
+                // a slot that was not filled this step holds stale bytes: harmless, nothing is stored for it
+                const uint4* src = reinterpret_cast<const uint4*>(ring_g + cons_off + (u * PIECES + ci * TPP) * PIECE_STRIDE);
+                float a[8];
+                if (TPP == 1) {
+                    unpack_bf16x8(src[0], a);
+                } else {
+                    const uint4 lo = src[0], hi = src[SEARCH_THREADS];
+                    a[0] = __uint_as_float(lo.x); a[1] = __uint_as_float(lo.y);
+                    a[2] = __uint_as_float(lo.z); a[3] = __uint_as_float(lo.w);
+                    a[4] = __uint_as_float(hi.x); a[5] = __uint_as_float(hi.y);
+                    a[6] = __uint_as_float(hi.z); a[7] = __uint_as_float(hi.w);
+                }
+                if (FULLD || (lane + GROUP * ci) * 8 < P.dim) {
+#pragma unroll
+                    for (int j = 0; j < GT; ++j) chunk_fma(acc[j], a, qreg[j][ci]);
+                }
+            }
+            float v[GT];
+#pragma unroll
+            for (int j = 0; j < GT; ++j) v[j] = __fadd_rn(acc[j].e, acc[j].o);
+            return HeadReduce<GT>::run(v, lane, 0xffffffffu);  // the whole warp runs every step
+        };
+        if (s_dense && tile_rows % (SEARCH_GROUPS * SEARCH_RPI) == 0) {
+            // Every parent slot of the tile is full and kept for every head (the usual case:
+            // the gates prune little): group g owns the rows [g*R, (g+1)*R) of the tile itself,
+            // so the source pointer and the score index only step forward and nothing per row
+            // needs testing.
+            // The CTA's 16 groups take 16 consecutive rows per sub-step, so one step of the CTA
+            // reads SEARCH_GROUPS * SEARCH_RPI consecutive rows (8 KB of bf16 at D=128).
+            constexpr int STEP_ROWS = SEARCH_GROUPS * SEARCH_RPI;
+            const int n_it = tile_rows / STEP_ROWS;
+            const char* isrc = gbase + (size_t)grp * row_bytes;
+            float* cdst = s_score + (size_t)grp * GT + my_head;
+            const size_t sub_bytes = (size_t)SEARCH_GROUPS * row_bytes;
+            auto issue_dense = [&](uint32_t stage_off) {
+#pragma unroll
+                for (int u = 0; u < SEARCH_RPI; ++u) {
 #pragma unroll
                     for (int pc = 0; pc < PIECES; ++pc) {
                         const int coff = (pc / TPP) * GROUP * 8 * (int)sizeof(T) + (pc % TPP) * 16;
                         if (FULLD || (lane + GROUP * (pc / TPP)) * 8 < P.dim)
-                            cp_async_16s(ring_s + stage_off + (u * PIECES + pc) * PIECE_STRIDE, isrc + coff);
+                            cp_async_16s(ring_s + stage_off + (u * PIECES + pc) * PIECE_STRIDE, isrc + u * sub_bytes + coff);
                     }
                 }
-                ++ic.c;
-                isrc += row_bytes;
-                if (ic.c == bf) {
-                    ic.c = 0;
-                    ++ic.k;
-                    load_parent(ic);
-                    isrc = gbase + (size_t)((ic.w >> 19) * bf) * row_bytes;
+                isrc += SEARCH_RPI * sub_bytes;
+            };
+            {
+                uint32_t so = 0;
+#pragma unroll
+                for (int it = 0; it < STAGES - 1; ++it) {
+                    if (it < n_it) issue_dense(so);
+                    cp_async_commit();
+                    so += STAGE_STRIDE;
                 }
             }
-        };
-        {
-            uint32_t so = 0;
-#pragma unroll
-            for (int it = 0; it < STAGES - 1; ++it) {
-                if (it < n_it) issue_rows(so);
+            uint32_t issue_off = (STAGES - 1) * STAGE_STRIDE, cons_off = 0;
+            for (int it = 0; it < n_it; ++it) {
+                if (it + STAGES - 1 < n_it) issue_dense(issue_off);
                 cp_async_commit();
-                so += STAGE_STRIDE;
+                issue_off = (issue_off == (STAGES - 1) * STAGE_STRIDE) ? 0 : issue_off + STAGE_STRIDE;
+                cp_async_wait<STAGES - 1>();
+#pragma unroll
+                for (int u = 0; u < SEARCH_RPI; ++u) {
+                    const float d = row_score(cons_off, u);
+                    if (writer && (emit_all || d >= leaf_thr)) cdst[u * SEARCH_GROUPS * GT] = d;
+                }
+                cdst += STEP_ROWS * GT;
+                cons_off = (cons_off == (STAGES - 1) * STAGE_STRIDE) ? 0 : cons_off + STAGE_STRIDE;
             }
-        }
-        uint32_t issue_off = (STAGES - 1) * STAGE_STRIDE, cons_off = 0;
-        for (int it = 0; it < n_it; ++it) {
-            if (it + STAGES - 1 < n_it) issue_rows(issue_off);
-            cp_async_commit();
-            issue_off = (issue_off == (STAGES - 1) * STAGE_STRIDE) ? 0 : issue_off + STAGE_STRIDE;
-            cp_async_wait<STAGES - 1>();
-#pragma unroll
-            for (int u = 0; u < SEARCH_RPI; ++u) {
-                Acc2 acc[GT];
-#pragma unroll
-                for (int j = 0; j < GT; ++j) acc[j] = Acc2{0.f, 0.f};
-#pragma unroll
-                for (int ci = 0; ci < NCH; ++ci) {
-                    // a slot that was not filled this step holds stale bytes: harmless, nothing is stored for it
-                    const uint4* src = reinterpret_cast<const uint4*>(ring_g + cons_off + (u * PIECES + ci * TPP) * PIECE_STRIDE);
-                    float a[8];
-                    if (TPP == 1) {
-                        unpack_bf16x8(src[0], a);
-                    } else {
-                        const uint4 lo = src[0], hi = src[SEARCH_THREADS];
-                        a[0] = __uint_as_float(lo.x); a[1] = __uint_as_float(lo.y);
-                        a[2] = __uint_as_float(lo.z); a[3] = __uint_as_float(lo.w);
-                        a[4] = __uint_as_float(hi.x); a[5] = __uint_as_float(hi.y);
-                        a[6] = __uint_as_float(hi.z); a[7] = __uint_as_float(hi.w);
+        } else {
+            const int total = npass * bf;
+            int R = (total + SEARCH_GROUPS - 1) / SEARCH_GROUPS;
+            R = (R + SEARCH_RPI - 1) / SEARCH_RPI * SEARCH_RPI;
+            const int n_it = R / SEARCH_RPI;
+
+            // cursor over the rows of this group: parent-list position k, child c, parent word w
+            struct Cursor { int k, c, cnt; uint32_t w; };
+            auto load_parent = [&](Cursor& cu) {
+                cu.w = cu.k < npass ? s_pl[cu.k] : 0u;
+                cu.cnt = (int)(cu.w & 0x7ffu);
+            };
+            Cursor ic, cc;
+            ic.k = div_bf(grp * R, bf, P.bf_magic);
+            ic.c = grp * R - ic.k * bf;
+            load_parent(ic);
+            cc = ic;
+            const char* isrc = gbase + (size_t)((ic.w >> 19) * bf + ic.c) * row_bytes;
+            float* cdst = s_score + (size_t)((cc.w >> 19) * bf + cc.c) * GT + my_head;
+            bool cgate = (cc.w >> (11 + my_head)) & 1u;
+
+            auto issue_rows = [&](uint32_t stage_off) {
+    #pragma unroll
+                for (int u = 0; u < SEARCH_RPI; ++u) {
+                    if (ic.c < ic.cnt) {
+    #pragma unroll
+                        for (int pc = 0; pc < PIECES; ++pc) {
+                            const int coff = (pc / TPP) * GROUP * 8 * (int)sizeof(T) + (pc % TPP) * 16;
+                            if (FULLD || (lane + GROUP * (pc / TPP)) * 8 < P.dim)
+                                cp_async_16s(ring_s + stage_off + (u * PIECES + pc) * PIECE_STRIDE, isrc + coff);
+                        }
                     }
-                    if (FULLD || (lane + GROUP * ci) * 8 < P.dim) {
-#pragma unroll
-                        for (int j = 0; j < GT; ++j) chunk_fma(acc[j], a, qreg[j][ci]);
+                    ++ic.c;
+                    isrc += row_bytes;
+                    if (ic.c == bf) {
+                        ic.c = 0;
+                        ++ic.k;
+                        load_parent(ic);
+                        isrc = gbase + (size_t)((ic.w >> 19) * bf) * row_bytes;
                     }
                 }
-                float v[GT];
-#pragma unroll
-                for (int j = 0; j < GT; ++j) v[j] = __fadd_rn(acc[j].e, acc[j].o);
-                const float d = HeadReduce<GT>::run(v, lane, 0xffffffffu);  // the whole warp runs every step
-                if (writer && cgate && cc.c < cc.cnt && (emit_all || d >= leaf_thr)) *cdst = d;
-                ++cc.c;
-                cdst += GT;
-                if (cc.c == bf) {
-                    cc.c = 0;
-                    ++cc.k;
-                    load_parent(cc);
-                    cdst = s_score + (size_t)((cc.w >> 19) * bf) * GT + my_head;
-                    cgate = (cc.w >> (11 + my_head)) & 1u;
+            };
+            {
+                uint32_t so = 0;
+    #pragma unroll
+                for (int it = 0; it < STAGES - 1; ++it) {
+                    if (it < n_it) issue_rows(so);
+                    cp_async_commit();
+                    so += STAGE_STRIDE;
                 }
             }
-            cons_off = (cons_off == (STAGES - 1) * STAGE_STRIDE) ? 0 : cons_off + STAGE_STRIDE;
+            uint32_t issue_off = (STAGES - 1) * STAGE_STRIDE, cons_off = 0;
+            for (int it = 0; it < n_it; ++it) {
+                if (it + STAGES - 1 < n_it) issue_rows(issue_off);
+                cp_async_commit();
+                issue_off = (issue_off == (STAGES - 1) * STAGE_STRIDE) ? 0 : issue_off + STAGE_STRIDE;
+                cp_async_wait<STAGES - 1>();
+    #pragma unroll
+                for (int u = 0; u < SEARCH_RPI; ++u) {
+                    const float d = row_score(cons_off, u);
+                    if (writer && cgate && cc.c < cc.cnt && (emit_all || d >= leaf_thr)) *cdst = d;
+                    ++cc.c;
+                    cdst += GT;
+                    if (cc.c == bf) {
+                        cc.c = 0;
+                        ++cc.k;
+                        load_parent(cc);
+                        cdst = s_score + (size_t)((cc.w >> 19) * bf) * GT + my_head;
+                        cgate = (cc.w >> (11 + my_head)) & 1u;
+                    }
+                }
+                cons_off = (cons_off == (STAGES - 1) * STAGE_STRIDE) ? 0 : cons_off + STAGE_STRIDE;
+            }
         }
         cp_async_wait<0>();
         __syncthreads();
@@ -512,20 +572,69 @@ search_kernel(const SearchParams P) {
         const size_t out_base = (size_t)qh * cap_children + tile_c0;
         const uint32_t* sc = reinterpret_cast<const uint32_t*>(s_score);
         int offset = 0;
-        for (int base = 0; base < tile_rows; base += 32) {
-            const int i = base + wl;
-            const uint32_t bits = (i < tile_rows) ? sc[(size_t)i * GT + j] : NOT_EMITTED;
-            const bool k = bits != NOT_EMITTED;
-            const float emitted = __fmul_rn(__uint_as_float(bits), scale);
-            const uint32_t b = __ballot_sync(0xffffffffu, k);
-            if (want_compact && k) {
-                const int pos = offset + __popc(b & ((1u << wl) - 1u));
-                P.out_idx[out_base + pos] = (int32_t)(tile_c0 + i);
-                P.out_score[out_base + pos] = emitted;
+        if (P.out_dense) {
+            for (int base = 0; base < tile_rows; base += 32) {
+                const int i = base + wl;
+                const uint32_t bits = (i < tile_rows) ? sc[(size_t)i * GT + j] : NOT_EMITTED;
+                const bool k = bits != NOT_EMITTED;
+                const float emitted = __fmul_rn(__uint_as_float(bits), scale);
+                const uint32_t b = __ballot_sync(0xffffffffu, k);
+                if (want_compact && k) {
+                    const int pos = offset + __popc(b & ((1u << wl) - 1u));
+                    P.out_idx[out_base + pos] = (int32_t)(tile_c0 + i);
+                    P.out_score[out_base + pos] = emitted;
+                }
+                offset += __popc(b);
+                if (i < tile_rows && tile_c0 + i < cap_children) P.out_dense[out_base + i] = k ? emitted : 0.f;
             }
-            offset += __popc(b);
-            if (P.out_dense && i < tile_rows && tile_c0 + i < cap_children)
-                P.out_dense[out_base + i] = k ? emitted : 0.f;
+        } else {
+            // Pass 1: one ballot per 32 rows, all loads independent; lane i keeps the bitmap of
+            // rows [32 i, 32 i + 32) (a tile has at most 32 such words).
+            static_assert(MAX_TILE_ROWS <= 1024, "one bitmap word per lane");
+            uint32_t mybits = 0;
+#pragma unroll 8
+            for (int it = 0; it < 32; ++it) {
+                const int i = it * 32 + wl;
+                const uint32_t bits = (i < tile_rows) ? sc[(size_t)i * GT + j] : NOT_EMITTED;
+                const uint32_t b = __ballot_sync(0xffffffffu, bits != NOT_EMITTED);
+                if (wl == it) mybits = b;
+            }
+            const int cnt = __popc(mybits);
+            int incl = cnt;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, incl, d);
+                if (wl >= d) incl += t;
+            }
+            const int total = __shfl_sync(0xffffffffu, incl, 31);
+            if (!want_compact) {
+                // only the count is wanted
+            } else if (total <= 4 * 32) {
+                // few rows emitted: every lane writes out the rows of its own word
+                int pos = incl - cnt;
+                uint32_t m = mybits;
+                while (m) {
+                    const int i = wl * 32 + (__ffs((int)m) - 1);
+                    m &= m - 1;
+                    P.out_idx[out_base + pos] = (int32_t)(tile_c0 + i);
+                    P.out_score[out_base + pos] = __fmul_rn(__uint_as_float(sc[(size_t)i * GT + j]), scale);
+                    ++pos;
+                }
+            } else {
+                // many rows emitted: word by word, so that the stores of a warp are contiguous
+                for (int it = 0; it < 32; ++it) {
+                    const uint32_t b = __shfl_sync(0xffffffffu, mybits, it);
+                    if (b == 0) continue;
+                    if ((b >> wl) & 1u) {
+                        const int i = it * 32 + wl;
+                        const int pos = offset + __popc(b & ((1u << wl) - 1u));
+                        P.out_idx[out_base + pos] = (int32_t)(tile_c0 + i);
+                        P.out_score[out_base + pos] = __fmul_rn(__uint_as_float(sc[(size_t)i * GT + j]), scale);
+                    }
+                    offset += __popc(b);
+                }
+            }
+            offset = total;
         }
         if (wl == 0) {
             if (want_compact) P.out_count[(size_t)qh * P.n_tiles + tile] = offset;

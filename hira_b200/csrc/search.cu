@@ -53,6 +53,8 @@ struct SearchParams {
     int n_heads, n_qheads, group, depth, bf, dim;
     int cap_parents, cap_gp, tile_parents, n_tiles, n_chunks, flags;
     uint32_t ring_offset;     // byte offset of the per-thread prefetch ring in dynamic shared memory
+    int ng;                   // grandparents touched by one tile
+    int tile_gp_shift;        // first grandparent of tile t: t >> shift (TP * 2^shift == bf), t * ng (-1: TP % bf == 0), t * TP / bf (-2)
     uint32_t bf_magic;        // ceil(2^32 / bf): x / bf == __umulhi(x, bf_magic) for x < 2^20, bf <= 1024
 };
 
@@ -159,9 +161,9 @@ search_kernel(const SearchParams P) {
     const int wl = tid & 31;
     // chunks of one tile are neighbours in the grid: they run at the same time and the later
     // ones find the tile's rows in L2
-    const int chunk = blockIdx.x % P.n_chunks;
-    const int tile = (blockIdx.x / P.n_chunks) % P.n_tiles;
-    const int h = blockIdx.x / (P.n_chunks * P.n_tiles);
+    const int chunk = blockIdx.x;
+    const int tile = blockIdx.y;
+    const int h = blockIdx.z;
     const bool ge = P.flags & HIRA_GATE_GE;
     const int leaf_mode = P.flags & (HIRA_LEAF_GE | HIRA_LEAF_GT);
     const bool has_qn = P.qnorm != nullptr;
@@ -210,8 +212,11 @@ search_kernel(const SearchParams P) {
     // ---- 2. every load the gates need, issued together (one memory latency, not five) ----
     const int used_parents = P.used[h * 4 + 0];
     const int used_gp = P.used[h * 4 + 1];
-    const int g0 = tile_p0 / bf;
-    const int ng = (TP + bf - 1) / bf;  // grandparents touched by this tile (TP % bf == 0 or bf % TP == 0)
+    // tiles align with grandparent blocks (TP % bf == 0 or bf % TP == 0): the tile's first
+    // grandparent and the number it touches come from the host, divisions by bf use its magic
+    const int g0 = P.tile_gp_shift >= 0 ? (tile >> P.tile_gp_shift)
+                                        : (P.tile_gp_shift == -1 ? tile * P.ng : div_bf(tile * TP, bf, P.bf_magic));
+    const int ng = P.ng;
     int my_qh = qh_of[0];
 #pragma unroll
     for (int j = 1; j < GT; ++j)
@@ -252,7 +257,7 @@ search_kernel(const SearchParams P) {
         load_row_raw<T, NCH>(praw[u], parents + (size_t)p * P.dim, lane, P.dim, in);
         prad[u] = in ? P.parent_radii[(size_t)h * P.cap_parents + p] : 0.f;
         pcnt[u] = in ? P.child_counts[(size_t)h * P.cap_parents + p] : 0;
-        pgc[u] = (in && P.depth == 3) ? P.gp_counts[(size_t)h * P.cap_gp + p / bf] : 0;
+        pgc[u] = (in && P.depth == 3) ? P.gp_counts[(size_t)h * P.cap_gp + g0 + div_bf(p - g0 * bf, bf, P.bf_magic)] : 0;
     }
     // score buffer starts as "nothing emitted"
     {
@@ -292,7 +297,7 @@ search_kernel(const SearchParams P) {
                     s_gpmask[i] = (unsigned char)m;
                     // a grandparent whose parents span several tiles is gated by each of
                     // them; only the tile holding its first parent books the visit
-                    if (valid && P.stats && (tile_p0 % bf) == 0) {
+                    if (valid && P.stats && tile_p0 == g0 * bf) {
                         for (int jj = 0; jj < nq; ++jj) {
                             atomicAdd(&s_stat[jj][0], 1u);
                             if ((m >> jj) & 1u) atomicAdd(&s_stat[jj][1], 1u);
@@ -312,7 +317,7 @@ search_kernel(const SearchParams P) {
             uint32_t gm = allmask;
             if (in) {
                 if (P.depth == 3) {
-                    const int g = p / bf;
+                    const int g = g0 + div_bf(p - g0 * bf, bf, P.bf_magic);
                     valid = (g < used_gp) && ((p - g * bf) < gc);
                     gm = s_gpmask[g - g0];
                 } else {
@@ -351,7 +356,7 @@ search_kernel(const SearchParams P) {
             const float d = gate_dot<T, GT, NCH>(parents + (size_t)p * P.dim, qreg, lane, P.dim, in);
             const float r = in ? P.parent_radii[(size_t)h * P.cap_parents + p] : 0.f;
             const int cnt = in ? P.child_counts[(size_t)h * P.cap_parents + p] : 0;
-            const int gc = (in && P.depth == 3) ? P.gp_counts[(size_t)h * P.cap_gp + p / bf] : 0;
+            const int gc = (in && P.depth == 3) ? P.gp_counts[(size_t)h * P.cap_gp + g0 + div_bf(p - g0 * bf, bf, P.bf_magic)] : 0;
             gate_parent(i0, d, r, cnt, gc);
         }
         __syncthreads();
@@ -469,19 +474,55 @@ search_kernel(const SearchParams P) {
                     so += STAGE_STRIDE;
                 }
             }
-            uint32_t issue_off = (STAGES - 1) * STAGE_STRIDE, cons_off = 0;
-            for (int it = 0; it < n_it; ++it) {
-                if (it + STAGES - 1 < n_it) issue_dense(issue_off);
-                cp_async_commit();
-                issue_off = (issue_off == (STAGES - 1) * STAGE_STRIDE) ? 0 : issue_off + STAGE_STRIDE;
-                cp_async_wait<STAGES - 1>();
+            if (FULLD && n_it >= STAGES && n_it % STAGES == 0) {
+                // Whole rounds of the ring, unrolled: slots, source offsets and score offsets are
+                // constants of the instruction stream.  Step k of a round works on slot k and
+                // refills slot k-1 with the step STAGES-1 ahead.
+                constexpr int RB = 64 * NCH * (int)sizeof(T);          // bytes per row (FULLD)
+                constexpr int SUB = SEARCH_GROUPS * RB;                 // bytes per sub-step of the CTA
+                auto round = [&](bool last) {
 #pragma unroll
-                for (int u = 0; u < SEARCH_RPI; ++u) {
-                    const float d = row_score(cons_off, u);
-                    if (writer && (emit_all || d >= leaf_thr)) cdst[u * SEARCH_GROUPS * GT] = d;
+                    for (int k = 0; k < STAGES; ++k) {
+                        if (!last || k == 0) {
+                            const uint32_t slot = (uint32_t)((k + STAGES - 1) % STAGES) * STAGE_STRIDE;
+#pragma unroll
+                            for (int u = 0; u < SEARCH_RPI; ++u)
+#pragma unroll
+                                for (int pc = 0; pc < PIECES; ++pc) {
+                                    const int coff = (pc / TPP) * GROUP * 8 * (int)sizeof(T) + (pc % TPP) * 16;
+                                    cp_async_16s(ring_s + slot + (u * PIECES + pc) * PIECE_STRIDE,
+                                                 isrc + (k * SEARCH_RPI + u) * SUB + coff);
+                                }
+                        }
+                        cp_async_commit();
+                        cp_async_wait<STAGES - 1>();
+#pragma unroll
+                        for (int u = 0; u < SEARCH_RPI; ++u) {
+                            const float d = row_score((uint32_t)k * STAGE_STRIDE, u);
+                            if (writer && (emit_all || d >= leaf_thr)) cdst[(k * SEARCH_RPI + u) * SEARCH_GROUPS * GT] = d;
+                        }
+                    }
+                    isrc += STAGES * SEARCH_RPI * SUB;
+                    cdst += STAGES * STEP_ROWS * GT;
+                };
+                const int n_rounds = n_it / STAGES;
+                for (int r = 0; r < n_rounds - 1; ++r) round(false);
+                round(true);
+            } else {
+                uint32_t issue_off = (STAGES - 1) * STAGE_STRIDE, cons_off = 0;
+                for (int it = 0; it < n_it; ++it) {
+                    if (it + STAGES - 1 < n_it) issue_dense(issue_off);
+                    cp_async_commit();
+                    issue_off = (issue_off == (STAGES - 1) * STAGE_STRIDE) ? 0 : issue_off + STAGE_STRIDE;
+                    cp_async_wait<STAGES - 1>();
+#pragma unroll
+                    for (int u = 0; u < SEARCH_RPI; ++u) {
+                        const float d = row_score(cons_off, u);
+                        if (writer && (emit_all || d >= leaf_thr)) cdst[u * SEARCH_GROUPS * GT] = d;
+                    }
+                    cdst += STEP_ROWS * GT;
+                    cons_off = (cons_off == (STAGES - 1) * STAGE_STRIDE) ? 0 : cons_off + STAGE_STRIDE;
                 }
-                cdst += STEP_ROWS * GT;
-                cons_off = (cons_off == (STAGES - 1) * STAGE_STRIDE) ? 0 : cons_off + STAGE_STRIDE;
             }
         } else {
             const int total = npass * bf;
@@ -667,7 +708,9 @@ static int launch_search_fd(SearchParams P, int chunks, cudaStream_t stream) {
         }
     }
     P.n_chunks = chunks;
-    dim3 grid((unsigned)((size_t)P.n_heads * P.n_tiles * chunks));
+    HIRA_CHECK_ARG(P.n_tiles <= 65535 && P.n_heads <= 65535, HIRA_ERR_SHAPE,
+                   "hira_search: %d tiles x %d heads exceed the grid limits", P.n_tiles, P.n_heads);
+    dim3 grid((unsigned)chunks, (unsigned)P.n_tiles, (unsigned)P.n_heads);
     kern<<<grid, SEARCH_THREADS, smem, stream>>>(P);
     HIRA_CHECK_LAUNCH("hira_search launch");
     return HIRA_OK;
@@ -788,6 +831,21 @@ extern "C" int hira_search(const hira_index_t* ix, const float* q, const float* 
     P.flags = flags;
     P.bf_magic = (uint32_t)((0x100000000ull + (uint64_t)bf - 1) / (uint64_t)bf);
     P.ring_offset = 0;
+    P.ng = (tile_parents + bf - 1) / bf;
+    if (tile_parents % bf == 0) {
+        P.tile_gp_shift = -1;
+    } else {
+        const int ratio = bf / tile_parents;  // tiles per grandparent (depth 3: bf % tile_parents == 0)
+        int sh = 0;
+        while ((1 << sh) < ratio) ++sh;
+        if (ix->depth == 3 && bf % tile_parents == 0 && (1 << sh) == ratio) {
+            P.tile_gp_shift = sh;
+        } else {
+            P.tile_gp_shift = -2;
+            HIRA_CHECK_ARG(ix->cap_parents <= (1 << 20), HIRA_ERR_SHAPE,
+                           "hira_search: cap_parents=%d too large for tile_parents=%d with bf=%d", ix->cap_parents, tile_parents, bf);
+        }
+    }
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const bool wide = ix->dim > 128;
     if (ix->dtype == HIRA_BF16)

@@ -15,6 +15,11 @@ void set_error(const char* fmt, ...) {
     va_end(ap);
 }
 
+int active_tiles(const hira_index_t* ix, int tile_parents) {
+    const int active = ix->active_parents > 0 ? ix->active_parents : ix->cap_parents;
+    return (active + tile_parents - 1) / tile_parents;
+}
+
 int validate_index(const hira_index_t* ix, bool need_values) {
     HIRA_CHECK_ARG(ix != nullptr, HIRA_ERR_ARG, "index is NULL");
     HIRA_CHECK_ARG(ix->dtype == HIRA_F32 || ix->dtype == HIRA_BF16, HIRA_ERR_DTYPE,
@@ -29,6 +34,8 @@ int validate_index(const hira_index_t* ix, bool need_values) {
     HIRA_CHECK_ARG((long long)ix->cap_parents * ix->bf < (1ll << 30), HIRA_ERR_SHAPE,
                    "cap_parents*bf = %lld child slots per head exceeds 2^30",
                    (long long)ix->cap_parents * ix->bf);
+    HIRA_CHECK_ARG(ix->active_parents >= 0 && ix->active_parents <= ix->cap_parents, HIRA_ERR_SHAPE,
+                   "active_parents=%d outside 0..cap_parents (%d)", ix->active_parents, ix->cap_parents);
     HIRA_CHECK_ARG(ix->children && ix->parents && ix->parent_radii && ix->child_counts && ix->used,
                    HIRA_ERR_ARG, "index has a NULL children/parents/parent_radii/child_counts/used pointer");
     if (ix->depth == 3) {

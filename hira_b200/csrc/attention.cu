@@ -34,6 +34,7 @@ struct AttnParams {
     const void* queued_v;
     float* ws;
     int n_heads, n_qheads, group, dim, vdim, n_tiles, tile_rows, n_splits, n_queued;
+    int n_tiles_active;  // tiles that can hold keys (<= n_tiles, the stride of `count`)
     long long cap_children;
     long long queued_head_stride;
 };
@@ -69,8 +70,8 @@ sparse_attn_kernel(const AttnParams P) {
     const int split = blockIdx.x;
     const int h = P.q2kv ? P.q2kv[qh] : qh / P.group;
     const TV* values = reinterpret_cast<const TV*>(P.values) + (size_t)h * P.cap_children * P.vdim;
-    const int t0 = (int)(((long long)split * P.n_tiles) / P.n_splits);
-    const int t1 = (int)(((long long)(split + 1) * P.n_tiles) / P.n_splits);
+    const int t0 = (int)(((long long)split * P.n_tiles_active) / P.n_splits);
+    const int t1 = (int)(((long long)(split + 1) * P.n_tiles_active) / P.n_splits);
 
     float m = -CUDART_INF_F;
     float l = 0.f;  // this group's share of the denominator
@@ -355,6 +356,7 @@ extern "C" int hira_sparse_attn(const hira_index_t* ix, const float* q, const fl
     P.group = q2kv ? 1 : n_qheads / ix->n_heads;
     P.dim = ix->dim; P.vdim = ix->vdim;
     P.n_tiles = (ix->cap_parents + tile_parents - 1) / tile_parents;
+    P.n_tiles_active = active_tiles(ix, tile_parents);
     P.tile_rows = tile_parents * ix->bf;
     P.n_splits = n_splits; P.n_queued = n_queued;
     P.cap_children = (long long)ix->cap_parents * ix->bf;

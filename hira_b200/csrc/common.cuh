@@ -47,6 +47,8 @@ void set_error(const char* fmt, ...);
     } while (0)
 
 int validate_index(const hira_index_t* ix, bool need_values);
+// tiles of `tile_parents` parent slots that can hold keys (hira_index_t::active_parents)
+int active_tiles(const hira_index_t* ix, int tile_parents);
 
 // chunks (of 8 elements) each of the 8 lanes owns: 1 for D <= 64, 2 for D <= 128, 4 for D <= 256
 __host__ __device__ inline int chunks_per_lane(int dim) { return dim <= 64 ? 1 : (dim <= 128 ? 2 : 4); }

@@ -52,6 +52,7 @@ struct SearchParams {
     uint32_t* stats;
     int n_heads, n_qheads, group, depth, bf, dim;
     int cap_parents, cap_gp, tile_parents, n_tiles, n_chunks, flags;
+    int n_tiles_active;       // tiles launched (<= n_tiles, which stays the stride of out_count)
     uint32_t ring_offset;     // byte offset of the per-thread prefetch ring in dynamic shared memory
     int ng;                   // grandparents touched by one tile
     int tile_gp_shift;        // first grandparent of tile t: t >> shift (TP * 2^shift == bf), t * ng (-1: TP % bf == 0), t * TP / bf (-2)
@@ -133,7 +134,7 @@ __device__ __forceinline__ void load_row_raw(RawChunk<T> (&raw)[NCH], const T* r
     }
 }
 
-template <typename T, int GT, int NCH, int STAGES, int MINB, bool FULLD, int TH>
+template <typename T, int GT, int NCH, int STAGES, int MINB, bool FULLD, int TH, int RPI>
 __global__ void __launch_bounds__(TH, MINB)
 search_kernel(const SearchParams P) {
     constexpr int SEARCH_THREADS = TH;
@@ -402,7 +403,7 @@ search_kernel(const SearchParams P) {
         constexpr int TPP = (int)(sizeof(T) / 2);   // 16-byte pieces per chunk
         constexpr int PIECES = NCH * TPP;           // 16-byte pieces per thread per row
         constexpr int PIECE_STRIDE = SEARCH_THREADS * 16;
-        constexpr int STAGE_STRIDE = SEARCH_RPI * PIECES * PIECE_STRIDE;
+        constexpr int STAGE_STRIDE = RPI * PIECES * PIECE_STRIDE;
         const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(smem_raw + P.ring_offset) + tid * 16;
         const unsigned char* ring_g = smem_raw + P.ring_offset + tid * 16;
         const int row_bytes = P.dim * (int)sizeof(T);
@@ -441,21 +442,21 @@ search_kernel(const SearchParams P) {
             for (int j = 0; j < GT; ++j) v[j] = __fadd_rn(acc[j].e, acc[j].o);
             return HeadReduce<GT>::run(v, lane, 0xffffffffu);  // the whole warp runs every step
         };
-        if (s_dense && tile_rows % (SEARCH_GROUPS * SEARCH_RPI) == 0) {
+        if (s_dense && tile_rows % (SEARCH_GROUPS * RPI) == 0) {
             // Every parent slot of the tile is full and kept for every head (the usual case:
             // the gates prune little): group g owns the rows [g*R, (g+1)*R) of the tile itself,
             // so the source pointer and the score index only step forward and nothing per row
             // needs testing.
             // The CTA's 16 groups take 16 consecutive rows per sub-step, so one step of the CTA
-            // reads SEARCH_GROUPS * SEARCH_RPI consecutive rows (8 KB of bf16 at D=128).
-            constexpr int STEP_ROWS = SEARCH_GROUPS * SEARCH_RPI;
+            // reads SEARCH_GROUPS * RPI consecutive rows (8 KB of bf16 at D=128).
+            constexpr int STEP_ROWS = SEARCH_GROUPS * RPI;
             const int n_it = tile_rows / STEP_ROWS;
             const char* isrc = gbase + (size_t)grp * row_bytes;
             float* cdst = s_score + (size_t)grp * GT + my_head;
             const size_t sub_bytes = (size_t)SEARCH_GROUPS * row_bytes;
             auto issue_dense = [&](uint32_t stage_off) {
 #pragma unroll
-                for (int u = 0; u < SEARCH_RPI; ++u) {
+                for (int u = 0; u < RPI; ++u) {
 #pragma unroll
                     for (int pc = 0; pc < PIECES; ++pc) {
                         const int coff = (pc / TPP) * GROUP * 8 * (int)sizeof(T) + (pc % TPP) * 16;
@@ -463,7 +464,7 @@ search_kernel(const SearchParams P) {
                             cp_async_16s(ring_s + stage_off + (u * PIECES + pc) * PIECE_STRIDE, isrc + u * sub_bytes + coff);
                     }
                 }
-                isrc += SEARCH_RPI * sub_bytes;
+                isrc += RPI * sub_bytes;
             };
             {
                 uint32_t so = 0;
@@ -486,23 +487,23 @@ search_kernel(const SearchParams P) {
                         if (!last || k == 0) {
                             const uint32_t slot = (uint32_t)((k + STAGES - 1) % STAGES) * STAGE_STRIDE;
 #pragma unroll
-                            for (int u = 0; u < SEARCH_RPI; ++u)
+                            for (int u = 0; u < RPI; ++u)
 #pragma unroll
                                 for (int pc = 0; pc < PIECES; ++pc) {
                                     const int coff = (pc / TPP) * GROUP * 8 * (int)sizeof(T) + (pc % TPP) * 16;
                                     cp_async_16s(ring_s + slot + (u * PIECES + pc) * PIECE_STRIDE,
-                                                 isrc + (k * SEARCH_RPI + u) * SUB + coff);
+                                                 isrc + (k * RPI + u) * SUB + coff);
                                 }
                         }
                         cp_async_commit();
                         cp_async_wait<STAGES - 1>();
 #pragma unroll
-                        for (int u = 0; u < SEARCH_RPI; ++u) {
+                        for (int u = 0; u < RPI; ++u) {
                             const float d = row_score((uint32_t)k * STAGE_STRIDE, u);
-                            if (writer && (emit_all || d >= leaf_thr)) cdst[(k * SEARCH_RPI + u) * SEARCH_GROUPS * GT] = d;
+                            if (writer && (emit_all || d >= leaf_thr)) cdst[(k * RPI + u) * SEARCH_GROUPS * GT] = d;
                         }
                     }
-                    isrc += STAGES * SEARCH_RPI * SUB;
+                    isrc += STAGES * RPI * SUB;
                     cdst += STAGES * STEP_ROWS * GT;
                 };
                 const int n_rounds = n_it / STAGES;
@@ -516,7 +517,7 @@ search_kernel(const SearchParams P) {
                     issue_off = (issue_off == (STAGES - 1) * STAGE_STRIDE) ? 0 : issue_off + STAGE_STRIDE;
                     cp_async_wait<STAGES - 1>();
 #pragma unroll
-                    for (int u = 0; u < SEARCH_RPI; ++u) {
+                    for (int u = 0; u < RPI; ++u) {
                         const float d = row_score(cons_off, u);
                         if (writer && (emit_all || d >= leaf_thr)) cdst[u * SEARCH_GROUPS * GT] = d;
                     }
@@ -527,8 +528,8 @@ search_kernel(const SearchParams P) {
         } else {
             const int total = npass * bf;
             int R = (total + SEARCH_GROUPS - 1) / SEARCH_GROUPS;
-            R = (R + SEARCH_RPI - 1) / SEARCH_RPI * SEARCH_RPI;
-            const int n_it = R / SEARCH_RPI;
+            R = (R + RPI - 1) / RPI * RPI;
+            const int n_it = R / RPI;
 
             // cursor over the rows of this group: parent-list position k, child c, parent word w
             struct Cursor { int k, c, cnt; uint32_t w; };
@@ -547,7 +548,7 @@ search_kernel(const SearchParams P) {
 
             auto issue_rows = [&](uint32_t stage_off) {
     #pragma unroll
-                for (int u = 0; u < SEARCH_RPI; ++u) {
+                for (int u = 0; u < RPI; ++u) {
                     if (ic.c < ic.cnt) {
     #pragma unroll
                         for (int pc = 0; pc < PIECES; ++pc) {
@@ -582,7 +583,7 @@ search_kernel(const SearchParams P) {
                 issue_off = (issue_off == (STAGES - 1) * STAGE_STRIDE) ? 0 : issue_off + STAGE_STRIDE;
                 cp_async_wait<STAGES - 1>();
     #pragma unroll
-                for (int u = 0; u < SEARCH_RPI; ++u) {
+                for (int u = 0; u < RPI; ++u) {
                     const float d = row_score(cons_off, u);
                     if (writer && cgate && cc.c < cc.cnt && (emit_all || d >= leaf_thr)) *cdst = d;
                     ++cc.c;
@@ -689,17 +690,17 @@ search_kernel(const SearchParams P) {
     }
 }
 
-template <typename T, int GT, int NCH, int STAGES, int MINB, bool FULLD>
+template <typename T, int GT, int NCH, int STAGES, int MINB, bool FULLD, int RPI>
 static int launch_search_fd(SearchParams P, int chunks, cudaStream_t stream) {
     constexpr int SEARCH_THREADS = 128;    // 4 warps: one compaction warp per head
     constexpr int BLOCKS = MINB;           // 128-thread CTAs resident per SM
-    auto kern = search_kernel<T, GT, NCH, STAGES, BLOCKS, FULLD, SEARCH_THREADS>;
+    auto kern = search_kernel<T, GT, NCH, STAGES, BLOCKS, FULLD, SEARCH_THREADS, RPI>;
     const size_t tile_rows = (size_t)P.tile_parents * P.bf;
     size_t off = tile_rows * GT * sizeof(float) + (size_t)P.tile_parents * (4 + 2 + 1 + 1);
     off = (off + 15) & ~(size_t)15;
     P.ring_offset = (uint32_t)off;
     const size_t pieces = (size_t)NCH * (sizeof(T) / 2);
-    const size_t smem = off + (size_t)STAGES * SEARCH_RPI * pieces * SEARCH_THREADS * 16;
+    const size_t smem = off + (size_t)STAGES * RPI * pieces * SEARCH_THREADS * 16;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
@@ -710,17 +711,17 @@ static int launch_search_fd(SearchParams P, int chunks, cudaStream_t stream) {
     P.n_chunks = chunks;
     HIRA_CHECK_ARG(P.n_tiles <= 65535 && P.n_heads <= 65535, HIRA_ERR_SHAPE,
                    "hira_search: %d tiles x %d heads exceed the grid limits", P.n_tiles, P.n_heads);
-    dim3 grid((unsigned)chunks, (unsigned)P.n_tiles, (unsigned)P.n_heads);
+    dim3 grid((unsigned)chunks, (unsigned)P.n_tiles_active, (unsigned)P.n_heads);
     kern<<<grid, SEARCH_THREADS, smem, stream>>>(P);
     HIRA_CHECK_LAUNCH("hira_search launch");
     return HIRA_OK;
 }
 
 // FULLD: every lane's chunks lie inside the row (D == 64 * NCH), so the per-chunk bounds tests drop out
-template <typename T, int GT, int NCH, int STAGES, int MINB>
+template <typename T, int GT, int NCH, int STAGES, int MINB, int RPI = SEARCH_RPI>
 static int launch_search(const SearchParams& P, int chunks, cudaStream_t stream) {
-    if (P.dim == 64 * NCH) return launch_search_fd<T, GT, NCH, STAGES, MINB, true>(P, chunks, stream);
-    return launch_search_fd<T, GT, NCH, STAGES, MINB, false>(P, chunks, stream);
+    if (P.dim == 64 * NCH) return launch_search_fd<T, GT, NCH, STAGES, MINB, true, RPI>(P, chunks, stream);
+    return launch_search_fd<T, GT, NCH, STAGES, MINB, false, RPI>(P, chunks, stream);
 }
 
 static int tuning_variant() {
@@ -743,9 +744,9 @@ static int dispatch_gt(const SearchParams& P, int max_group, cudaStream_t stream
     if constexpr (BF && NCH == 2) {
       if (gt == 4) {
         switch (tuning_variant()) {  // prefetch depth / residency of the headline shape
-            case 1: return launch_search<T, 4, NCH, 3, 5>(P, chunks, stream);
-            case 2: return launch_search<T, 4, NCH, 2, 5>(P, chunks, stream);
-            case 3: return launch_search<T, 4, NCH, 2, 6>(P, chunks, stream);
+            case 1: return launch_search<T, 4, NCH, 2, 4, 4>(P, chunks, stream);
+            case 2: return launch_search<T, 4, NCH, 2, 4, 2>(P, chunks, stream);
+            case 3: return launch_search<T, 4, NCH, 8, 4, 1>(P, chunks, stream);
             default: return launch_search<T, 4, NCH, 4, 4>(P, chunks, stream);
         }
       }
@@ -828,6 +829,8 @@ extern "C" int hira_search(const hira_index_t* ix, const float* q, const float* 
     P.bf = bf; P.dim = ix->dim; P.cap_parents = ix->cap_parents; P.cap_gp = ix->cap_gp;
     P.tile_parents = tile_parents;
     P.n_tiles = (ix->cap_parents + tile_parents - 1) / tile_parents;
+    // the dense row is written whole (callers reuse the buffer), the compact output only where keys can be
+    P.n_tiles_active = out_dense ? P.n_tiles : active_tiles(ix, tile_parents);
     P.flags = flags;
     P.bf_magic = (uint32_t)((0x100000000ull + (uint64_t)bf - 1) / (uint64_t)bf);
     P.ring_offset = 0;

@@ -91,7 +91,8 @@ __device__ __forceinline__ float key_to_float(uint32_t k) {
 // radix select, 8 bits per pass, over the compacted scores of one query head
 __global__ void __launch_bounds__(1024)
 kth_kernel(const float* __restrict__ score, const int32_t* __restrict__ count, long long cap_children,
-           int n_tiles, int tile_rows, const int32_t* __restrict__ kk, float* __restrict__ tau_out) {
+           int n_tiles, int n_tiles_active, int tile_rows, const int32_t* __restrict__ kk,
+           float* __restrict__ tau_out) {
     __shared__ unsigned int hist[256];
     __shared__ unsigned int s_prefix, s_remaining;
     const int qh = blockIdx.x;
@@ -105,7 +106,7 @@ kth_kernel(const float* __restrict__ score, const int32_t* __restrict__ count, l
         const int shift = 24 - 8 * pass;
         if (tid < 256) hist[tid] = 0;
         __syncthreads();
-        for (int t = 0; t < n_tiles; ++t) {
+        for (int t = 0; t < n_tiles_active; ++t) {
             const int c = cnt[t];
             for (int i = tid; i < c; i += blockDim.x) {
                 const uint32_t key = order_key(sc[(size_t)t * tile_rows + i]);
@@ -219,7 +220,8 @@ extern "C" int hira_kth_score(const hira_index_t* ix, int32_t n_qheads, int32_t 
                    n_qheads, tile_parents);
     const int n_tiles = (ix->cap_parents + tile_parents - 1) / tile_parents;
     kth_kernel<<<n_qheads, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        score, count, (long long)ix->cap_parents * ix->bf, n_tiles, tile_parents * ix->bf, k, tau_out);
+        score, count, (long long)ix->cap_parents * ix->bf, n_tiles, active_tiles(ix, tile_parents), tile_parents * ix->bf, k,
+        tau_out);
     HIRA_CHECK_LAUNCH("hira_kth_score launch");
     return HIRA_OK;
 }

@@ -49,6 +49,7 @@ class IndexState:
         self.used = z((n_heads, 4), dtype=torch.int32, device=dev)
         self.status = z((1,), dtype=torch.int32, device=dev)
         self._struct = None
+        self._active_parents = 0
         self.refresh_struct()
 
     ARRAYS = ("children", "values", "slot2token", "parents", "parent_radii", "parent_sqnorm", "child_counts",
@@ -64,10 +65,25 @@ class IndexState:
         s.vdtype = L.dtype_code(self.vdtype)
         s.depth, s.bf, s.dim, s.vdim = self.depth, self.bf, self.dim, self.vdim
         s.n_heads, s.cap_parents, s.cap_gp = self.n_heads, self.cap_parents, self.cap_gp
+        s.active_parents = self._active_parents
         for name in self.ARRAYS:
             setattr(s, name, L.ptr(getattr(self, name)))
         self._struct = s
         return s
+
+    @property
+    def active_parents(self) -> int:
+        """Host's upper bound on the parent slots in use; 0 = unknown (all of cap_parents).
+        Search, sparse attention and kth_score skip the tiles beyond it."""
+        return self._active_parents
+
+    @active_parents.setter
+    def active_parents(self, n: int):
+        n = int(n)
+        if n < 0 or n >= self.cap_parents:
+            n = 0
+        self._active_parents = n
+        self._struct.active_parents = n
 
     @property
     def struct(self):
@@ -116,6 +132,7 @@ class CompactResult:
     count: torch.Tensor    # (H_q, n_tiles) int32
     tile_parents: int
     tile_rows: int
+    n_tiles_active: Optional[int] = None   # tiles the last search wrote (None: all)
 
     def to_lists(self):
         """Per query head: (slots, scores) as 1-D CPU tensors, ascending slot order."""
@@ -123,7 +140,7 @@ class CompactResult:
         out = []
         for qh in range(idx.shape[0]):
             sl, sc = [], []
-            for t in range(count.shape[1]):
+            for t in range(count.shape[1] if self.n_tiles_active is None else self.n_tiles_active):
                 c = int(count[qh, t])
                 if c:
                     b = t * self.tile_rows
@@ -135,7 +152,10 @@ class CompactResult:
 
 
 def tile_parents(st: IndexState) -> int:
-    return int(L.load().hira_search_tile_parents(st.struct))
+    tp = getattr(st, "_tile_parents", None)
+    if tp is None:   # depends on bf, depth and the capacity only: fixed for the life of the state
+        tp = st._tile_parents = int(L.load().hira_search_tile_parents(st.struct))
+    return tp
 
 
 def n_tiles(st: IndexState, tp: Optional[int] = None) -> int:
@@ -163,6 +183,9 @@ def search(st: IndexState, q: torch.Tensor, tau: torch.Tensor, *, scaling=None, 
                          L.ptr(compact.idx) if compact else None, L.ptr(compact.score) if compact else None,
                          L.ptr(compact.count) if compact else None, L.ptr(stats), L.current_stream(st.device))
     L.check(rc, "hira_search")
+    if compact is not None:
+        compact.n_tiles_active = None if (st.active_parents == 0 or out_dense is not None) \
+            else -(-st.active_parents // tp)
     return out_dense, compact
 
 
@@ -177,7 +200,9 @@ def alloc_compact(st: IndexState, hq: int, tp: Optional[int] = None) -> CompactR
 
 
 def attn_splits(st: IndexState, hq: int, tp: Optional[int] = None) -> int:
-    return int(L.load().hira_attn_default_splits(hq, n_tiles(st, tp)))
+    tp = tp or tile_parents(st)
+    tiles = n_tiles(st, tp) if st.active_parents == 0 else -(-st.active_parents // tp)
+    return int(L.load().hira_attn_default_splits(hq, tiles))
 
 
 def sparse_attn(st: IndexState, q, scaling, compact: CompactResult, *, q2kv=None, queued_k=None, queued_v=None,

@@ -53,6 +53,9 @@ class CUDAIndexer(BaseIndexer):
         self.state: Optional[S.IndexState] = None
         self._parents_bound = 0   # host-side upper bounds on used parent / grandparent slots
         self._gp_bound = 0
+        self._snapshot = None     # (pinned copy of `used`, event, keys appended when it was taken)
+        self._pinned = None
+        self._appended = 0        # keys appended since the build
         self._n_keys = 0
 
     # ---- reference attribute names as views ---------------------------------
@@ -160,6 +163,7 @@ class CUDAIndexer(BaseIndexer):
         self._n_keys = n
         self._parents_bound = k2 * bf if st.depth == 3 else k1
         self._gp_bound = k2
+        self._snapshot = None
         return self
 
     # ---- update -------------------------------------------------------------
@@ -173,6 +177,7 @@ class CUDAIndexer(BaseIndexer):
         # tighten the bounds from the device state before paying for a reallocation
         used = st.used.max(dim=0).values.tolist()
         self._parents_bound, self._gp_bound = int(used[0]), int(used[1])
+        self._snapshot = None
         need_p, need_g = self._parents_bound + m, self._gp_bound + m
         if st.depth == 3:
             if need_g <= st.cap_gp:
@@ -209,7 +214,49 @@ class CUDAIndexer(BaseIndexer):
         self._parents_bound += m
         self._gp_bound += m
         self._n_keys += m
+        self._appended += m
+        if self._snapshot is not None or self._appended % self.BOUND_REFRESH_EVERY < m:
+            self._tighten_bounds()
         return self
+
+    BOUND_REFRESH_EVERY = 8   # appended keys between two read-backs of the device counters
+
+    def _tighten_bounds(self):
+        """The bounds grow by the worst case (one new parent and one new grandparent per key);
+        the counts the device actually reached come back through a small asynchronous copy, read
+        one or more appends later without ever blocking on the stream."""
+        st = self.state
+        if st.device.type != "cuda":
+            return
+        snap = self._snapshot
+        if snap is not None:
+            host, event, appended_then = snap
+            if not event.query():
+                return
+            used = host.max(dim=0).values.tolist()
+            since = self._appended - appended_then
+            self._parents_bound = min(self._parents_bound, int(used[0]) + since)
+            self._gp_bound = min(self._gp_bound, int(used[1]) + since)
+            self._snapshot = None
+            return
+        if self._pinned is None or self._pinned[0].shape != st.used.shape:
+            self._pinned = [torch.empty(tuple(st.used.shape), dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._pinned.reverse()
+        host = self._pinned[0]
+        host.copy_(st.used, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record(torch.cuda.current_stream(st.device))
+        self._snapshot = (host, event, self._appended)
+
+    @property
+    def active_parents(self) -> int:
+        """Upper bound on the parent slots that can hold keys (for depth 3 whole grandparent
+        blocks): what the searcher passes down so that empty capacity is not visited."""
+        st = self.state
+        if st is None:
+            return 0
+        n = self._gp_bound * st.bf if st.depth == 3 else self._parents_bound
+        return min(int(n), st.cap_parents)
 
     def check_status(self):
         """Raises if an append ran out of pre-allocated slots (reads one word from the device)."""
@@ -227,6 +274,7 @@ class CUDAIndexer(BaseIndexer):
                            max_context=self.max_context, use_tensor_cores=self.use_tensor_cores, seed=self.seed)
         b.build(keys.unsqueeze(0), None if values is None else values.unsqueeze(0))
         self.state, self._parents_bound, self._gp_bound = b.state, b._parents_bound, b._gp_bound
+        self._snapshot = None
         return self
 
     # ---- checkpoint ---------------------------------------------------------

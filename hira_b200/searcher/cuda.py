@@ -79,6 +79,7 @@ class CUDASearcher(BaseSearcher):
         st: S.IndexState = getattr(indexer, "state", None)
         if st is None:
             raise ValueError("Indexer is not built: missing children tensor.")
+        st.active_parents = getattr(indexer, "active_parents", 0)   # empty capacity is not visited
         q = self._coerce_query(query, st.dim, st.device)
         hq = q.shape[0]
         threshold = torch.as_tensor(threshold)

@@ -71,7 +71,11 @@ typedef struct hira_index {
     int32_t n_heads;      /* (batch, kv_head) pairs                                    */
     int32_t cap_parents;  /* parent slots allocated per head (depth 3: cap_gp * bf)    */
     int32_t cap_gp;       /* grandparent slots allocated per head (depth 3), else 0    */
-    int32_t reserved0;
+    int32_t active_parents; /* host's upper bound on the parent slots in use (0 = unknown: all of
+                               cap_parents).  Search, sparse attention and hira_kth_score skip the
+                               tiles beyond it: their out_count entries are neither written nor read.
+                               The reference has no such field (it sizes every launch by the
+                               tensors' extents, searcher/cuda.py:96-143).                    */
     void* children;        /* [n_heads][cap_parents*bf][dim]                           */
     void* values;          /* [n_heads][cap_parents*bf][vdim] or NULL                  */
     int32_t* slot2token;   /* [n_heads][cap_parents*bf] token position in slot, -1 empty */

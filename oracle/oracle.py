@@ -29,7 +29,7 @@ class _IndexStruct(C.Structure):
     _fields_ = [
         ("dtype", C.c_int32), ("vdtype", C.c_int32), ("depth", C.c_int32), ("bf", C.c_int32),
         ("dim", C.c_int32), ("vdim", C.c_int32), ("n_heads", C.c_int32), ("cap_parents", C.c_int32),
-        ("cap_gp", C.c_int32), ("reserved0", C.c_int32),
+        ("cap_gp", C.c_int32), ("active_parents", C.c_int32),
         ("children", C.c_void_p), ("values", C.c_void_p), ("slot2token", C.c_void_p),
         ("parents", C.c_void_p), ("parent_radii", C.c_void_p), ("parent_sqnorm", C.c_void_p),
         ("child_counts", C.c_void_p), ("grand_parents", C.c_void_p), ("gp_radii", C.c_void_p),

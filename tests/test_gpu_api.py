@@ -259,3 +259,48 @@ def test_patched_llama_generates_like_dense_attention():
     for a, b in zip(got, ref):
         torch.testing.assert_close(a, b, atol=2e-3, rtol=2e-3)
         assert torch.equal(a.argmax(-1), b.argmax(-1))
+
+
+@pytest.mark.parametrize("levels", [2, 3])
+def test_active_bound_skips_empty_capacity_without_changing_results(levels):
+    """An index sized for a long context visits only the tiles that can hold keys: the host's
+    bound (tightened from the device counters by an asynchronous copy) leaves selected sets,
+    scores and attention output unchanged."""
+    from hira_b200 import index_state as S
+    from hira_b200.cache import CacheOutput
+    h, hq, n, d, bf = 2, 4, 2048, 64, 8
+    keys, vals = _keys(h, n, d, 41), _keys(h, n, d, 42)
+    ix = CUDAIndexer(levels, 1, bf, max_context=n + 4096).build(keys, vals)
+    more_k, more_v = _keys(h, 24, d, 43), _keys(h, 24, d, 44)
+    for i in range(24):
+        ix.update(more_k[:, :, i:i + 1], more_v[:, :, i:i + 1])
+    torch.cuda.synchronize()
+    ix.update(_keys(h, 1, d, 45), _keys(h, 1, d, 46))       # reads the counters copied back meanwhile
+    ix.check_status()
+    st = ix.state
+    bound = ix.active_parents
+    used = st.used.max(dim=0).values.tolist()
+    in_use = used[1] * bf if levels == 3 else used[0]
+    assert in_use <= bound < st.cap_parents // 2            # tight, far below the capacity
+    q = _query(hq, d, 47)
+    tau = torch.full((hq,), 0.1, device="cuda")
+    srch = CUDASearcher(bf, gate="ge", leaf="ge")
+    empty = torch.empty((1, h, 0, d), device="cuda")
+    co = CacheOutput(queued_keys=empty, queued_values=empty, prefill_keys=None, prefill_values=None, indexer=ix,
+                     searcher=srch)
+    out_b, comp_b = hira_decode_attention(q, co, threshold=tau, return_compact=True)
+    assert st.active_parents == bound and comp_b.n_tiles_active < comp_b.count.shape[1]
+    lists_b = comp_b.to_lists()
+    kth_b = S.kth_score(st, comp_b, torch.full((hq,), 5, dtype=torch.int32, device="cuda")).clone()
+    out_b = out_b.clone()
+    # the same with the bound switched off
+    ix._gp_bound, ix._parents_bound = st.cap_gp, st.cap_parents
+    out_f, comp_f = hira_decode_attention(q, co, threshold=tau, return_compact=True)
+    assert st.active_parents == 0 and comp_f.n_tiles_active is None
+    lists_f = comp_f.to_lists()
+    kth_f = S.kth_score(st, comp_f, torch.full((hq,), 5, dtype=torch.int32, device="cuda"))
+    assert sum(len(a[0]) for a in lists_f) > 0
+    for a, b in zip(lists_b, lists_f):
+        assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+    # the split of the tile range over CTAs differs, so the output may differ in the last bits
+    assert torch.allclose(out_b, out_f, rtol=1e-5, atol=1e-6) and torch.equal(kth_b, kth_f)

@@ -405,9 +405,9 @@ def run_e2e(args, st, qsets, n_groups, group, k2, dev, CUDAIndexer, CUDASearcher
 
     def one(i):
         q = h_q[i % nset].to(dev, non_blocking=True)
-        k = h_k[i % 4].to(dev, non_blocking=True)
-        v = h_v[i % 4].to(dev, non_blocking=True)
         o = hira_decode_attention(q, co, threshold=taus[i % nset])
+        k = h_k[i % 4].to(dev, non_blocking=True)       # queued behind the attention: not on its critical path
+        v = h_v[i % 4].to(dev, non_blocking=True)
         idx.update(k, v)
         h_out.copy_(o, non_blocking=True)
 

@@ -25,7 +25,7 @@ EXPORTED_SYMBOLS = [
     "hira_attn_default_splits", "hira_sparse_attn", "hira_merge_partials", "hira_append",
     "hira_append_workspace_bytes",
     "hira_threshold", "hira_kth_score", "hira_prepare_query", "hira_build_workspace_bytes", "hira_build",
-    "hira_recompute_radii", "hira_export", "hira_assign", "hira_sparse_attn_noalloc",
+    "hira_recompute_radii", "hira_export", "hira_assign", "hira_sparse_attn_noalloc", "hira_decode_attention",
 ]
 NOALLOC_SCRATCH_FLOATS = 1 << 20
 
@@ -61,6 +61,9 @@ def _declare(lib):
     lib.hira_attn_default_splits.argtypes = [I32, I32]
     lib.hira_sparse_attn.restype = C.c_int
     lib.hira_sparse_attn.argtypes = [IX, P, P, P, I32, I32, P, P, P, P, P, I32, I64, I32, P, P, P, P]
+    lib.hira_decode_attention.restype = C.c_int
+    lib.hira_decode_attention.argtypes = [IX, P, I32, C.c_float, P, P, I32, I32, I32, I32, P, P, P, P, P, P, P, I32, I64,
+                                          I32, P, P, P, P]
     lib.hira_sparse_attn_noalloc.restype = C.c_int
     lib.hira_sparse_attn_noalloc.argtypes = [IX, P, P, P, I32, I32, P, P, P, P, P, I32, I64, I32, P, P, P]
     lib.hira_merge_partials.restype = C.c_int

@@ -78,32 +78,50 @@ def hira_decode_attention(query: torch.Tensor, cache_output, *, scaling: Optiona
             searcher._decode_bufs = bufs
         except AttributeError:
             pass
-    q_hat, logit_scale = S.prepare_query(q.contiguous(), sm_scale, bufs[0], bufs[1])
-    if threshold is None and threshold_method == "none":
-        threshold = torch.full((b * hq,), float("-inf"), device=st.device)      # keep every key: dense-equivalent
-    if threshold is None:
-        samples = _samples_for(indexer, sample_size)
-        fn = THRESHOLD_METHODS[threshold_method]
-        if threshold_method == "sample_max":
-            threshold = fn(samples, q_hat, q_head_to_kv)
-        else:
-            threshold = fn(samples, q_hat, min(topk, samples.shape[1]), q_head_to_kv)
     srch = _attn_searcher(searcher, gate)
-    compact = srch.search_compact(q_hat, threshold, indexer, q_head_to_kv=q_head_to_kv, scaling=logit_scale)
+    n_q = b * hq
+    q2kv, max_group = srch._coerce_q2kv(q_head_to_kv, n_q, st.n_heads, st.device)
+    st.active_parents = getattr(indexer, "active_parents", 0)   # empty capacity is not visited
+    compact = srch._compact
+    if compact is None or compact.idx.device != st.device or tuple(compact.idx.shape) != (n_q, st.cap_children):
+        compact = srch._compact = S.alloc_compact(st, n_q)
     qk = cache_output.queued_keys
     queued_k = queued_v = None
     if qk is not None and qk.shape[-2] > 0:
         queued_k = qk.reshape(-1, qk.shape[-2], qk.shape[-1]).to(st.dtype).contiguous()
         qv = cache_output.queued_values
         queued_v = qv.reshape(-1, qv.shape[-2], qv.shape[-1]).to(st.vdtype).contiguous()
-    q2kv, _ = srch._coerce_q2kv(q_head_to_kv, b * hq, st.n_heads, st.device)
-    n_splits = S.attn_splits(st, b * hq, compact.tile_parents)
+    n_splits = S.attn_splits(st, n_q, compact.tile_parents)
     ws = getattr(srch, "_attn_ws", None)
-    need = b * hq * n_splits * (st.vdim + 2)
+    need = n_q * n_splits * (st.vdim + 2)
     if ws is None or ws.numel() < need or ws.device != st.device:
         ws = srch._attn_ws = torch.empty((need,), dtype=torch.float32, device=st.device)
-    out = S.sparse_attn(st, q_hat, logit_scale, compact, q2kv=q2kv, queued_k=queued_k, queued_v=queued_v,
-                        n_splits=n_splits, workspace=ws)
+    out = torch.empty((n_q, st.vdim), dtype=torch.float32, device=st.device)
+    q = q.contiguous()
+    if threshold is not None and threshold_method != "none":
+        # the usual decode step: the threshold is known, one library call does the rest
+        tau = threshold
+        if tau.shape != (n_q,):
+            raise ValueError(f"threshold must have shape ({n_q},), got {tuple(tau.shape)}")
+        if tau.device != st.device or tau.dtype != torch.float32 or not tau.is_contiguous():
+            tau = tau.to(device=st.device, dtype=torch.float32).contiguous()
+        S.decode_attention(st, q, sm_scale, tau, compact, bufs[0], bufs[1], q2kv=q2kv, max_group=max_group,
+                           flags=srch.flags, queued_k=queued_k, queued_v=queued_v, n_splits=n_splits, workspace=ws,
+                           out=out)
+    else:
+        q_hat, logit_scale = S.prepare_query(q, sm_scale, bufs[0], bufs[1])
+        if threshold is None and threshold_method == "none":
+            threshold = torch.full((n_q,), float("-inf"), device=st.device)      # keep every key: dense-equivalent
+        if threshold is None:
+            samples = _samples_for(indexer, sample_size)
+            fn = THRESHOLD_METHODS[threshold_method]
+            if threshold_method == "sample_max":
+                threshold = fn(samples, q_hat, q_head_to_kv)
+            else:
+                threshold = fn(samples, q_hat, min(topk, samples.shape[1]), q_head_to_kv)
+        compact = srch.search_compact(q_hat, threshold, indexer, q_head_to_kv=q_head_to_kv, scaling=logit_scale)
+        S.sparse_attn(st, q_hat, logit_scale, compact, q2kv=q2kv, queued_k=queued_k, queued_v=queued_v,
+                      n_splits=n_splits, workspace=ws, out=out)
     out = out.reshape(b, hq, 1, st.vdim)
     return (out, compact) if return_compact else out
 

@@ -58,3 +58,22 @@ int validate_index(const hira_index_t* ix, bool need_values) {
 
 extern "C" const char* hira_last_error(void) { return hira::g_err; }
 extern "C" const char* hira_version(void) { return "hira_b200 0.1 (sm_100a)"; }
+
+extern "C" int hira_decode_attention(const hira_index_t* index, const void* q, int32_t q_dtype, float sm_scale,
+                                     const float* tau, const int32_t* q2kv, int32_t n_qheads, int32_t max_group,
+                                     int32_t flags, int32_t tile_parents, float* q_hat, float* logit_scale,
+                                     int32_t* idx, float* score, int32_t* count,
+                                     const void* queued_k, const void* queued_v, int32_t n_queued,
+                                     int64_t queued_head_stride, int32_t n_splits, float* workspace,
+                                     float* out, float* out_ml, void* stream) {
+    HIRA_CHECK_ARG(index != nullptr, HIRA_ERR_ARG, "hira_decode_attention: index is NULL");
+    HIRA_CHECK_ARG(q && q_hat && logit_scale, HIRA_ERR_ARG, "hira_decode_attention: q, q_hat and logit_scale must not be NULL");
+    int rc = hira_prepare_query(q, q_dtype, n_qheads, index->dim, sm_scale, q_hat, logit_scale, stream);
+    if (rc != HIRA_OK) return rc;
+    rc = hira_search(index, q_hat, tau, logit_scale, nullptr, q2kv, n_qheads, max_group, flags, tile_parents,
+                     nullptr, idx, score, count, nullptr, stream);
+    if (rc != HIRA_OK) return rc;
+    return hira_sparse_attn(index, q_hat, logit_scale, q2kv, n_qheads, tile_parents, idx, score, count,
+                            queued_k, queued_v, n_queued, queued_head_stride, n_splits, workspace, out, out_ml,
+                            stream);
+}

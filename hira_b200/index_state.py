@@ -291,6 +291,33 @@ def prepare_query(q: torch.Tensor, sm_scale: float, q_hat=None, logit_scale=None
     return q_hat, logit_scale
 
 
+def decode_attention(st: IndexState, q: torch.Tensor, sm_scale: float, tau: torch.Tensor, compact: CompactResult,
+                     q_hat: torch.Tensor, logit_scale: torch.Tensor, *, q2kv=None, max_group: int = 0, flags: int = 0,
+                     queued_k=None, queued_v=None, n_splits: int, workspace: torch.Tensor, out: torch.Tensor,
+                     out_ml=None):
+    """prepare_query + search (compact) + sparse_attn in one library call.  q (H_q, D) fp32/bf16
+    contiguous; everything else preallocated by the caller."""
+    lib = L.load()
+    hq = q.shape[0]
+    n_queued, qstride = 0, 0
+    if queued_k is not None and queued_k.shape[-2] > 0:
+        assert queued_k.is_contiguous() and queued_v.is_contiguous()
+        assert queued_k.dtype == st.dtype and queued_v.dtype == st.vdtype
+        n_queued = queued_k.shape[-2]
+        qstride = n_queued * st.dim
+        if st.vdim != st.dim:
+            raise ValueError("queued keys/values with vdim != dim are not supported")
+    rc = lib.hira_decode_attention(st.struct, L.ptr(q), L.dtype_code(q.dtype), float(sm_scale), L.ptr(tau), L.ptr(q2kv),
+                                   hq, max_group, flags, compact.tile_parents, L.ptr(q_hat), L.ptr(logit_scale),
+                                   L.ptr(compact.idx), L.ptr(compact.score), L.ptr(compact.count),
+                                   L.ptr(queued_k) if n_queued else None, L.ptr(queued_v) if n_queued else None,
+                                   n_queued, qstride, n_splits, L.ptr(workspace), L.ptr(out), L.ptr(out_ml),
+                                   L.current_stream(st.device))
+    L.check(rc, "hira_decode_attention")
+    compact.n_tiles_active = None if st.active_parents == 0 else -(-st.active_parents // compact.tile_parents)
+    return out
+
+
 def kth_score(st: IndexState, compact: CompactResult, k: torch.Tensor, out=None):
     lib = L.load()
     hq = compact.idx.shape[0]

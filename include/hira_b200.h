@@ -240,6 +240,22 @@ int hira_threshold(const void* samples, int32_t dtype, int32_t n_heads,
 int hira_prepare_query(const void* q, int32_t dtype, int32_t n_qheads, int32_t dim,
                        float sm_scale, float* q_hat, float* logit_scale, void* stream);
 
+/* One decode step's attention in one call: hira_prepare_query, hira_search (compact output, gate
+ * and leaf rule in `flags`, scores scaled to logits) and hira_sparse_attn, enqueued back to back on
+ * `stream`.  It is what a host does per generated token for one layer once the threshold is known
+ * (the reference's decode path: cache/hira_cache.py:95-140 -> searcher.search -> attention);
+ * folding the three calls into one saves the caller two trips through its FFI.
+ *   q [n_qheads][dim] raw queries in `q_dtype`;  tau [n_qheads] on the scale of q_hat . k;
+ *   q_hat [n_qheads][dim], logit_scale [n_qheads]: scratch, left holding the prepared query;
+ *   idx/score/count, workspace, out, out_ml, queued_*: as in hira_search / hira_sparse_attn. */
+int hira_decode_attention(const hira_index_t* index, const void* q, int32_t q_dtype, float sm_scale,
+                          const float* tau, const int32_t* q2kv, int32_t n_qheads, int32_t max_group,
+                          int32_t flags, int32_t tile_parents, float* q_hat, float* logit_scale,
+                          int32_t* idx, float* score, int32_t* count,
+                          const void* queued_k, const void* queued_v, int32_t n_queued,
+                          int64_t queued_head_stride, int32_t n_splits, float* workspace,
+                          float* out, float* out_ml, void* stream);
+
 /* Exact k-th largest of the scores in a compacted search output (run
  * hira_search with HIRA_LEAF_CANDIDATES, tau = -inf and scaling = NULL first).
  * k [n_qheads] int32 per-head ranks (1 = largest).  tau_out[qh] = that score,

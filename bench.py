@@ -10,7 +10,9 @@ once at set-up).  The (batch, kv_head) groups are independent and are partitione
 the N ranks (no collective on the data path); the timed value is the step time, max over
 ranks, so scaling is strong (the job is fixed).
 
-One JSON line on stdout from rank 0 (see DESIGN.md for the field meanings).
+One JSON line on stdout from rank 0: `value` = device-timed step, `e2e` = the same step through
+the public classes with host buffers, `roofline` = the search kernel's algorithmic bytes over its
+CUDA-event time against the measured copy bandwidth, `cpu_baseline` = the CPU path on a sample.
 `--impl reference` times the reference's CPU path (its fused_tree_search_v3 kernel built
 from the reference sources into oracle/_ref, else the oracle port) on the host cores on a
 bounded sample of the same workload.
@@ -41,9 +43,9 @@ ROPE_BASE = 500000.0
 OUTLIER_CHANNELS = (7, 42, 71, 110)
 N_QUERY_SETS = 4
 # DRAM bytes (read + write) of one search_kernel launch per (batch, kv head) group of 131,072 keys, from
-# the ncu capture summarised in profiles/search_kernel_bf16_g4_batch2_ctx131072.md (16 groups:
-# 559.04 MB read + 6.08 MB written); traffic grows in proportion to the groups a launch covers.
-SEARCH_DRAM_BYTES_PER_GROUP_AT_CTX = (559.043840e6 + 6.076416e6) / 16
+# an ncu capture of this bench at --batch 2 (16 groups: dram__bytes_read.sum 559.07 MB,
+# dram__bytes_write.sum 7.25 MB); traffic grows in proportion to the groups a launch covers.
+SEARCH_DRAM_BYTES_PER_GROUP_AT_CTX = (559.073280e6 + 7.247872e6) / 16
 
 
 def peaks():
@@ -347,7 +349,7 @@ def run_ours(args):
                    "sharding": f"kv_head x{world}", "l2": "inputs>L2 (keys per GPU >> 126 MB)",
                    "gate": "ge", "leaf": "ge"},
         "e2e": {"value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]},
-        "gpu_launches": args.steps * 4,
+        "gpu_launches": args.steps * 5,   # search, sparse_attn, merge, append_scan, append
         "roofline": {"bound": "hbm", "kernel": "search_kernel", "achieved": achieved, "peak": peak,
                      "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": (SEARCH_DRAM_BYTES_PER_GROUP_AT_CTX * n_groups if ctx == CTX else None),

@@ -2,7 +2,7 @@
 
 Run where the reference checkout exists (it is not needed to run the tests):
 
-    cd /tmp && python -O /path/to/repo/tests/golden/make_golden.py [--ref /root/reference]
+    cd /tmp && python -O /path/to/repo/tests/golden/make_golden.py [--ref /path/to/reference]
 
 What runs, and how it runs without a GPU and without faiss:
   * `python -O` strips the `assert x.is_cuda` lines of indexer/cuda.py, so CUDAIndexer's

@@ -261,11 +261,28 @@ def run_ours(args):
     scanned_frac = rows_read / float(n_groups * ctx)
     setup_s = time.time() - t_setup
 
+    # fused: the search scores the parent rows it reads against the key appended right after,
+    # so the append needs no parent scan of its own (four kernels per step instead of five)
+    fused = not args.unfused
+    scan = S.new_scan_slots(st)
+
+    def search_step(i, q_hat, tau, lscale):
+        if fused:
+            S.search(st, q_hat, tau, scaling=lscale, flags=flags, compact=compact, tp=tp, scan_key=new_k[i], scan_out=scan)
+        else:
+            S.search(st, q_hat, tau, scaling=lscale, flags=flags, compact=compact, tp=tp)
+
+    def append_step(i):
+        if fused:
+            S.append_scanned(st, new_k[i].unsqueeze(1), new_v[i].unsqueeze(1), scan)
+        else:
+            S.append(st, new_k[i].unsqueeze(1), new_v[i].unsqueeze(1))
+
     def step(i: int):
         q_hat, tau, lscale, _ = qsets[i % N_QUERY_SETS]
-        S.search(st, q_hat, tau, scaling=lscale, flags=flags, compact=compact, tp=tp)
+        search_step(i, q_hat, tau, lscale)
         S.sparse_attn(st, q_hat, lscale, compact, n_splits=n_splits, workspace=ws, out=out)
-        S.append(st, new_k[i].unsqueeze(1), new_v[i].unsqueeze(1))
+        append_step(i)
 
     def barrier():
         if dist is not None:
@@ -287,11 +304,11 @@ def run_ours(args):
         i = args.warmup + j
         q_hat, tau, lscale, _ = qsets[i % N_QUERY_SETS]
         ev[j][0].record()
-        S.search(st, q_hat, tau, scaling=lscale, flags=flags, compact=compact, tp=tp)
+        search_step(i, q_hat, tau, lscale)
         ev[j][1].record()
         S.sparse_attn(st, q_hat, lscale, compact, n_splits=n_splits, workspace=ws, out=out)
         ev[j][2].record()
-        S.append(st, new_k[i].unsqueeze(1), new_v[i].unsqueeze(1))
+        append_step(i)
         ev[j][3].record()
     t_end.record()
     barrier()
@@ -349,7 +366,7 @@ def run_ours(args):
                    "sharding": f"kv_head x{world}", "l2": "inputs>L2 (keys per GPU >> 126 MB)",
                    "gate": "ge", "leaf": "ge"},
         "e2e": {"value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]},
-        "gpu_launches": args.steps * 5,   # search, sparse_attn, merge, append_scan, append
+        "gpu_launches": args.steps * (4 if fused else 5),   # search, sparse_attn, merge, [append_scan,] append
         "roofline": {"bound": "hbm", "kernel": "search_kernel", "achieved": achieved, "peak": peak,
                      "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": (SEARCH_DRAM_BYTES_PER_GROUP_AT_CTX * n_groups if ctx == CTX else None),
@@ -407,6 +424,8 @@ def run_e2e(args, st, qsets, n_groups, group, k2, dev, CUDAIndexer, CUDASearcher
 
     def one(i):
         q = h_q[i % nset].to(dev, non_blocking=True)
+        # (the scan folded into the search, `append_key=` / `update(scanned=True)`, would put the
+        # key's copy in front of the search: through host buffers the plain order is faster)
         o = hira_decode_attention(q, co, threshold=taus[i % nset])
         k = h_k[i % 4].to(dev, non_blocking=True)       # queued behind the attention: not on its critical path
         v = h_v[i % 4].to(dev, non_blocking=True)
@@ -608,6 +627,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-tc", action="store_true", help="build the index with the CUDA-core assignment")
     ap.add_argument("--dense", action="store_true", help="also time torch SDPA over the full cache")
+    ap.add_argument("--unfused", action="store_true",
+                    help="separate parent scan in the append instead of the scan folded into the search")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

@@ -26,6 +26,7 @@ EXPORTED_SYMBOLS = [
     "hira_append_workspace_bytes",
     "hira_threshold", "hira_kth_score", "hira_prepare_query", "hira_build_workspace_bytes", "hira_build",
     "hira_recompute_radii", "hira_export", "hira_assign", "hira_sparse_attn_noalloc", "hira_decode_attention",
+    "hira_search_scan", "hira_append_scanned",
 ]
 NOALLOC_SCRATCH_FLOATS = 1 << 20
 
@@ -63,7 +64,11 @@ def _declare(lib):
     lib.hira_sparse_attn.argtypes = [IX, P, P, P, I32, I32, P, P, P, P, P, I32, I64, I32, P, P, P, P]
     lib.hira_decode_attention.restype = C.c_int
     lib.hira_decode_attention.argtypes = [IX, P, I32, C.c_float, P, P, I32, I32, I32, I32, P, P, P, P, P, P, P, I32, I64,
-                                          I32, P, P, P, P]
+                                          I32, P, P, P, P, I64, P, P]
+    lib.hira_search_scan.restype = C.c_int
+    lib.hira_search_scan.argtypes = [IX, P, P, P, P, I32, I32, I32, P, P, P, P, P, P, I64, P, P]
+    lib.hira_append_scanned.restype = C.c_int
+    lib.hira_append_scanned.argtypes = [IX, P, P, I64, I64, I32, P, P, P]
     lib.hira_sparse_attn_noalloc.restype = C.c_int
     lib.hira_sparse_attn_noalloc.argtypes = [IX, P, P, P, I32, I32, P, P, P, P, P, I32, I64, I32, P, P, P]
     lib.hira_merge_partials.restype = C.c_int

@@ -58,9 +58,14 @@ def _attn_searcher(searcher, gate: str) -> CUDASearcher:
 def hira_decode_attention(query: torch.Tensor, cache_output, *, scaling: Optional[float] = None,
                           threshold: Optional[torch.Tensor] = None, threshold_method: str = "sample_mean_topk",
                           sample_size: int = 1000, topk: int = 16, gate: str = "ge",
-                          q_head_to_kv: Optional[torch.Tensor] = None, return_compact: bool = False):
+                          q_head_to_kv: Optional[torch.Tensor] = None, return_compact: bool = False,
+                          append_key: Optional[torch.Tensor] = None):
     """query (B, H_q, 1, D) -> (B, H_q, 1, V) float32.  `threshold` (B*H_q,) is on the scale of
-    `q_hat . k` with `q_hat = q / ||q||`."""
+    `q_hat . k` with `q_hat = q / ||q||`.
+
+    `append_key` (B, H_kv, 1, D): the key the caller appends right after this call with
+    `indexer.update(append_key, value, scanned=True)`.  The search then scores the parent rows it
+    reads against that key as well, and the update needs no parent scan of its own."""
     indexer, searcher = cache_output.indexer, cache_output.searcher
     st: S.IndexState = indexer.state
     b, hq, lq, d = query.shape
@@ -98,6 +103,11 @@ def hira_decode_attention(query: torch.Tensor, cache_output, *, scaling: Optiona
         ws = srch._attn_ws = torch.empty((need,), dtype=torch.float32, device=st.device)
     out = torch.empty((n_q, st.vdim), dtype=torch.float32, device=st.device)
     q = q.contiguous()
+    scan_key = scan_out = None
+    if append_key is not None:
+        if q2kv is not None:
+            raise ValueError("append_key needs the default query-head grouping")
+        scan_key, scan_out = indexer.begin_scanned_update(append_key)
     if threshold is not None and threshold_method != "none":
         # the usual decode step: the threshold is known, one library call does the rest
         tau = threshold
@@ -107,7 +117,7 @@ def hira_decode_attention(query: torch.Tensor, cache_output, *, scaling: Optiona
             tau = tau.to(device=st.device, dtype=torch.float32).contiguous()
         S.decode_attention(st, q, sm_scale, tau, compact, bufs[0], bufs[1], q2kv=q2kv, max_group=max_group,
                            flags=srch.flags, queued_k=queued_k, queued_v=queued_v, n_splits=n_splits, workspace=ws,
-                           out=out)
+                           out=out, scan_key=scan_key, scan_out=scan_out)
     else:
         q_hat, logit_scale = S.prepare_query(q, sm_scale, bufs[0], bufs[1])
         if threshold is None and threshold_method == "none":
@@ -119,7 +129,11 @@ def hira_decode_attention(query: torch.Tensor, cache_output, *, scaling: Optiona
                 threshold = fn(samples, q_hat, q_head_to_kv)
             else:
                 threshold = fn(samples, q_hat, min(topk, samples.shape[1]), q_head_to_kv)
-        compact = srch.search_compact(q_hat, threshold, indexer, q_head_to_kv=q_head_to_kv, scaling=logit_scale)
+        tau = torch.as_tensor(threshold).to(device=st.device, dtype=torch.float32).contiguous()
+        if tau.shape != (n_q,):
+            raise ValueError(f"threshold must have shape ({n_q},), got {tuple(tau.shape)}")
+        S.search(st, q_hat, tau, scaling=logit_scale, q2kv=q2kv, max_group=max_group, flags=srch.flags,
+                 compact=compact, scan_key=scan_key, scan_out=scan_out)
         S.sparse_attn(st, q_hat, logit_scale, compact, q2kv=q2kv, queued_k=queued_k, queued_v=queued_v,
                       n_splits=n_splits, workspace=ws, out=out)
     out = out.reshape(b, hq, 1, st.vdim)

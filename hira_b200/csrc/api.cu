@@ -65,13 +65,20 @@ extern "C" int hira_decode_attention(const hira_index_t* index, const void* q, i
                                      int32_t* idx, float* score, int32_t* count,
                                      const void* queued_k, const void* queued_v, int32_t n_queued,
                                      int64_t queued_head_stride, int32_t n_splits, float* workspace,
-                                     float* out, float* out_ml, void* stream) {
+                                     float* out, float* out_ml,
+                                     const void* scan_key, int64_t scan_key_stride, uint64_t* scan_out, void* stream) {
     HIRA_CHECK_ARG(index != nullptr, HIRA_ERR_ARG, "hira_decode_attention: index is NULL");
     HIRA_CHECK_ARG(q && q_hat && logit_scale, HIRA_ERR_ARG, "hira_decode_attention: q, q_hat and logit_scale must not be NULL");
     int rc = hira_prepare_query(q, q_dtype, n_qheads, index->dim, sm_scale, q_hat, logit_scale, stream);
     if (rc != HIRA_OK) return rc;
-    rc = hira_search(index, q_hat, tau, logit_scale, nullptr, q2kv, n_qheads, max_group, flags, tile_parents,
-                     nullptr, idx, score, count, nullptr, stream);
+    if (scan_out != nullptr) {
+        HIRA_CHECK_ARG(q2kv == nullptr, HIRA_ERR_ARG, "hira_decode_attention: the fused parent scan needs q2kv == NULL");
+        rc = hira_search_scan(index, q_hat, tau, logit_scale, nullptr, n_qheads, flags, tile_parents, nullptr, idx,
+                              score, count, nullptr, scan_key, scan_key_stride, scan_out, stream);
+    } else {
+        rc = hira_search(index, q_hat, tau, logit_scale, nullptr, q2kv, n_qheads, max_group, flags, tile_parents,
+                         nullptr, idx, score, count, nullptr, stream);
+    }
     if (rc != HIRA_OK) return rc;
     return hira_sparse_attn(index, q_hat, logit_scale, q2kv, n_qheads, tile_parents, idx, score, count,
                             queued_k, queued_v, n_queued, queued_head_stride, n_splits, workspace, out, out_ml,

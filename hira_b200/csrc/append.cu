@@ -35,6 +35,8 @@ struct AppendParams {
     // two-kernel path: partial arg-mins of the scan kernel, [head][key][part], or NULL
     struct BestRec* partial;
     int n_parts;
+    unsigned long long* scan;  // [n_heads] nearest valid parent found by hira_search_scan (n_new == 1), or NULL
+    uint32_t bf_magic;  // ceil(2^32 / bf): p / bf == __umulhi(p, bf_magic) for p < 2^20 (0: divide)
 };
 
 struct BestRec { float s; int i; };
@@ -125,7 +127,11 @@ append_scan_kernel(const AppendParams P) {
         Best b;
         if (ix.depth == 3)
             b = nearest_row<T, NCH, SCAN_THREADS>(parents + (size_t)lo * dim, psq + lo, hi - lo, x, dim,
-                                                  [&](int p) { return ((p + lo) % bf) < gc[(p + lo) / bf]; }, s_best);
+                                                  [&](int p) {
+                                                      const int pp = p + lo;
+                                                      const int g = P.bf_magic ? (int)__umulhi((uint32_t)pp, P.bf_magic) : pp / bf;
+                                                      return (pp - g * bf) < gc[g];
+                                                  }, s_best);
         else
             b = nearest_row<T, NCH, SCAN_THREADS>(parents + (size_t)lo * dim, psq + lo, hi - lo, x, dim,
                                                   [&](int) { return true; }, s_best);
@@ -174,7 +180,14 @@ append_kernel(const AppendParams P) {
 
         // ---- nearest valid parent ---------------------------------------------
         Best bp;
-        if (P.partial != nullptr) {
+        if (P.scan != nullptr) {
+            // found by the search that ran just before on the same index state
+            const unsigned long long k = P.scan[h];
+            bp = (k == ~0ull) ? Best{CUDART_INF_F, 0x7fffffff}
+                              : Best{key_to_float((uint32_t)(k >> 32)), (int)(uint32_t)(k & 0xffffffffu)};
+            __syncthreads();                      // every thread has read the slot
+            if (tid == 0) P.scan[h] = ~0ull;      // ready for the next search
+        } else if (P.partial != nullptr) {
             // arg-min over the scanned slices, then over the parents this call created itself
             bp = Best{CUDART_INF_F, 0x7fffffff};
             const BestRec* pr_ = P.partial + ((size_t)h * P.n_new + key) * P.n_parts;
@@ -201,7 +214,10 @@ append_kernel(const AppendParams P) {
         } else if (ix.depth == 3) {
             const int n_scan = used_g * bf;
             bp = nearest_row<T, NCH, APPEND_THREADS>(parents, psq, n_scan, x, dim,
-                                     [&](int p) { return (p % bf) < gc[p / bf]; }, s_best);
+                                     [&](int p) {
+                                         const int g = P.bf_magic ? (int)__umulhi((uint32_t)p, P.bf_magic) : p / bf;
+                                         return (p - g * bf) < gc[g];
+                                     }, s_best);
         } else {
             bp = nearest_row<T, NCH, APPEND_THREADS>(parents, psq, used_p, x, dim, [&](int) { return true; }, s_best);
         }
@@ -381,12 +397,40 @@ extern "C" int hira_append(const hira_index_t* ix, const void* new_k, const void
     P.ix = *ix; P.new_k = new_k; P.new_v = new_v; P.n_new = n_new;
     P.k_head_stride = k_head_stride; P.v_head_stride = v_head_stride;
     P.token_base = token_base; P.status = status;
-    P.partial = nullptr; P.n_parts = 0;
+    P.partial = nullptr; P.n_parts = 0; P.scan = nullptr;
+    P.bf_magic = (ix->bf > 1 && ix->cap_parents < (1 << 20))
+                     ? (uint32_t)((0x100000000ull + (uint64_t)ix->bf - 1) / (uint64_t)ix->bf) : 0u;
     const size_t need = hira_append_workspace_bytes(ix, n_new);
     if (workspace != nullptr && need > 0 && workspace_bytes >= need && append_parts(ix) > 1) {
         P.partial = reinterpret_cast<BestRec*>(workspace);
         P.n_parts = append_parts(ix);
     }
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    const bool kb = ix->dtype == HIRA_BF16, vb = ix->vdtype == HIRA_BF16 || !ix->values;
+    if (kb && vb) return launch_append<__nv_bfloat16, __nv_bfloat16>(P, s);
+    if (kb && !vb) return launch_append<__nv_bfloat16, float>(P, s);
+    if (!kb && vb && ix->values) return launch_append<float, __nv_bfloat16>(P, s);
+    return launch_append<float, float>(P, s);
+}
+
+extern "C" int hira_append_scanned(const hira_index_t* ix, const void* new_k, const void* new_v,
+                                   int64_t k_head_stride, int64_t v_head_stride, int32_t token_base,
+                                   int32_t* status, uint64_t* scan, void* stream) {
+    int rc = validate_index(ix, false);
+    if (rc != HIRA_OK) return rc;
+    HIRA_CHECK_ARG(new_k && status && scan, HIRA_ERR_ARG, "hira_append_scanned: new_k, status and scan must not be NULL");
+    HIRA_CHECK_ARG((ix->values == nullptr) == (new_v == nullptr), HIRA_ERR_ARG,
+                   "hira_append_scanned: values must be given iff the index stores values");
+    HIRA_CHECK_ARG(ix->parent_sqnorm && (ix->depth == 2 || ix->gp_sqnorm), HIRA_ERR_ARG,
+                   "hira_append_scanned: the index needs its parent_sqnorm / gp_sqnorm caches");
+    AppendParams P;
+    P.ix = *ix; P.new_k = new_k; P.new_v = new_v; P.n_new = 1;
+    P.k_head_stride = k_head_stride; P.v_head_stride = v_head_stride;
+    P.token_base = token_base; P.status = status;
+    P.partial = nullptr; P.n_parts = 0;
+    P.scan = reinterpret_cast<unsigned long long*>(scan);
+    P.bf_magic = (ix->bf > 1 && ix->cap_parents < (1 << 20))
+                     ? (uint32_t)((0x100000000ull + (uint64_t)ix->bf - 1) / (uint64_t)ix->bf) : 0u;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const bool kb = ix->dtype == HIRA_BF16, vb = ix->vdtype == HIRA_BF16 || !ix->values;
     if (kb && vb) return launch_append<__nv_bfloat16, __nv_bfloat16>(P, s);

@@ -50,6 +50,17 @@ int validate_index(const hira_index_t* ix, bool need_values);
 // tiles of `tile_parents` parent slots that can hold keys (hira_index_t::active_parents)
 int active_tiles(const hira_index_t* ix, int tile_parents);
 
+// order-preserving map float -> uint32 (a < b  <=>  order_key(a) < order_key(b), -0 before +0) and back
+__device__ __forceinline__ uint32_t order_key(float f) {
+    const uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_to_float(uint32_t k) {
+    const uint32_t u = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
+    return __uint_as_float(u);
+}
+
+
 // chunks (of 8 elements) each of the 8 lanes owns: 1 for D <= 64, 2 for D <= 128, 4 for D <= 256
 __host__ __device__ inline int chunks_per_lane(int dim) { return dim <= 64 ? 1 : (dim <= 128 ? 2 : 4); }
 

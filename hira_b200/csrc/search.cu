@@ -50,6 +50,11 @@ struct SearchParams {
     float* out_score;
     int32_t* out_count;
     uint32_t* stats;
+    // optional by-product for the append that follows: nearest valid parent of one new key per head
+    const void* scan_key;              // [n_heads] rows of `dim` elements in the index dtype, or NULL
+    long long scan_key_stride;         // elements between the heads' keys
+    const float* parent_sqnorm;        // [n_heads][cap_parents]
+    unsigned long long* scan_out;      // [n_heads] packed (order_key(score) << 32 | parent slot), atomicMin
     int n_heads, n_qheads, group, depth, bf, dim;
     int cap_parents, cap_gp, tile_parents, n_tiles, n_chunks, flags;
     int n_tiles_active;       // tiles launched (<= n_tiles, which stays the stride of out_count)
@@ -134,7 +139,7 @@ __device__ __forceinline__ void load_row_raw(RawChunk<T> (&raw)[NCH], const T* r
     }
 }
 
-template <typename T, int GT, int NCH, int STAGES, int MINB, bool FULLD, int TH, int RPI>
+template <typename T, int GT, int NCH, int STAGES, int MINB, bool FULLD, int TH, int RPI, bool SCAN>
 __global__ void __launch_bounds__(TH, MINB)
 search_kernel(const SearchParams P) {
     constexpr int SEARCH_THREADS = TH;
@@ -154,6 +159,8 @@ search_kernel(const SearchParams P) {
     __shared__ float s_scale[GT];
     __shared__ int s_nq, s_npass, s_dense;
     __shared__ uint32_t s_stat[GT][8];
+    __shared__ unsigned long long s_scan[TH / GROUP];
+    __shared__ __align__(16) float s_xkey[SCAN ? GROUP * NCH * 8 : 4];  // the scanned key: [lane][chunk][8]
 
     const int tid = threadIdx.x;
     const int lane = tid & (GROUP - 1);  // lane inside the 8-lane group
@@ -260,6 +267,27 @@ search_kernel(const SearchParams P) {
         pcnt[u] = in ? P.child_counts[(size_t)h * P.cap_parents + p] : 0;
         pgc[u] = (in && P.depth == 3) ? P.gp_counts[(size_t)h * P.cap_gp + g0 + div_bf(p - g0 * bf, bf, P.bf_magic)] : 0;
     }
+    // the new key of this head and the cached squared norms of the same parents, for the scan
+    const bool do_scan = SCAN && chunk == 0;  // SCAN: the launch was given a scan_out
+    float psq[PRE];
+    if (do_scan) {
+        if constexpr (SCAN) {
+            if (tid < GROUP) {  // kept in shared memory: the gates have no registers to spare
+                float xk[NCH][8];
+                load_vec<T, NCH>(reinterpret_cast<const T*>(P.scan_key) + (size_t)h * P.scan_key_stride, xk, lane, P.dim);
+#pragma unroll
+                for (int ci = 0; ci < NCH; ++ci)
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) s_xkey[(lane * NCH + ci) * 8 + e] = xk[ci][e];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < PRE; ++u) {
+            const int p = tile_p0 + u * SEARCH_GROUPS + grp;
+            psq[u] = (u * SEARCH_GROUPS + grp < TP && p < P.cap_parents) ? P.parent_sqnorm[(size_t)h * P.cap_parents + p] : 0.f;
+        }
+    }
+    unsigned long long scan_best = ~0ull;  // the same in the 8 lanes of a group
     // score buffer starts as "nothing emitted"
     {
         uint4* sc4 = reinterpret_cast<uint4*>(s_score);
@@ -310,7 +338,7 @@ search_kernel(const SearchParams P) {
         __syncthreads();  // s_gpmask, s_stat zeroing, score sentinel
 
         // ---- 3b. parent gate --------------------------------------------------
-        auto gate_parent = [&](int i0, float d, float r, int cnt, int gc) {
+        auto gate_parent = [&](int i0, float d, float r, int cnt, int gc, float scan_s) {
             const int i = i0 + grp;
             const int p = tile_p0 + i;
             const bool in = (i < TP) && (p < P.cap_parents);
@@ -324,6 +352,10 @@ search_kernel(const SearchParams P) {
                 } else {
                     valid = p < used_parents;
                 }
+            }
+            if (do_scan && valid) {  // every valid parent is a candidate, whatever the gates say
+                const unsigned long long key = ((unsigned long long)order_key(scan_s) << 32) | (uint32_t)p;
+                if (key < scan_best) scan_best = key;
             }
             const bool work = valid && gm != 0;
             const bool keep = work && head_on && ((gm >> my_head) & 1u) && gate_keep(d, r, my_qn, has_qn, my_tau, ge);
@@ -347,9 +379,34 @@ search_kernel(const SearchParams P) {
             }
         };
 #pragma unroll
+        // sq - 2 x.c of a parent row against the new key: the score the append's nearest-parent
+        // search minimises, in the same arithmetic (chunk order, 8-lane tree)
+        auto scan_score = [&](const RawChunk<T> (&raw)[NCH], float sq) -> float {
+            if constexpr (SCAN) {
+                Acc2 acc{0.f, 0.f};
+#pragma unroll
+                for (int ci = 0; ci < NCH; ++ci) {
+                    float a[8], xk[8];
+                    to_float(raw[ci], a);
+                    const float4 x0 = *reinterpret_cast<const float4*>(&s_xkey[(lane * NCH + ci) * 8]);
+                    const float4 x1 = *reinterpret_cast<const float4*>(&s_xkey[(lane * NCH + ci) * 8 + 4]);
+                    xk[0] = x0.x; xk[1] = x0.y; xk[2] = x0.z; xk[3] = x0.w;
+                    xk[4] = x1.x; xk[5] = x1.y; xk[6] = x1.z; xk[7] = x1.w;
+                    chunk_fma(acc, a, xk);
+                }
+                const float d = group_sum(__fadd_rn(acc.e, acc.o));
+                return __fsub_rn(sq, __fmul_rn(2.0f, d));
+            } else {
+                return 0.f;
+            }
+        };
+#pragma unroll
         for (int u = 0; u < PRE; ++u) {  // rows loaded in step 2; the trip test is uniform over the CTA
-            if (u * SEARCH_GROUPS < TP)
-                gate_parent(u * SEARCH_GROUPS, gate_dot_raw<T, GT, NCH>(praw[u], qreg, lane), prad[u], pcnt[u], pgc[u]);
+            if (u * SEARCH_GROUPS < TP) {
+                float ss = 0.f;
+                if (do_scan) ss = scan_score(praw[u], psq[u]);  // uniform over the CTA
+                gate_parent(u * SEARCH_GROUPS, gate_dot_raw<T, GT, NCH>(praw[u], qreg, lane), prad[u], pcnt[u], pgc[u], ss);
+            }
         }
         for (int i0 = PRE * SEARCH_GROUPS; i0 < TP; i0 += SEARCH_GROUPS) {  // uniform trip count
             const int p = tile_p0 + i0 + grp;
@@ -358,8 +415,15 @@ search_kernel(const SearchParams P) {
             const float r = in ? P.parent_radii[(size_t)h * P.cap_parents + p] : 0.f;
             const int cnt = in ? P.child_counts[(size_t)h * P.cap_parents + p] : 0;
             const int gc = (in && P.depth == 3) ? P.gp_counts[(size_t)h * P.cap_gp + g0 + div_bf(p - g0 * bf, bf, P.bf_magic)] : 0;
-            gate_parent(i0, d, r, cnt, gc);
+            float ss = 0.f;
+            if (do_scan) {  // uniform over the CTA
+                RawChunk<T> raw[NCH];
+                load_row_raw<T, NCH>(raw, parents + (size_t)p * P.dim, lane, P.dim, in);
+                ss = scan_score(raw, in ? P.parent_sqnorm[(size_t)h * P.cap_parents + p] : 0.f);
+            }
+            gate_parent(i0, d, r, cnt, gc, ss);
         }
+        if (do_scan && lane == 0) s_scan[grp] = scan_best;
         __syncthreads();
 
         // ---- 4. ordered list of parents kept for at least one head ------------
@@ -387,6 +451,15 @@ search_kernel(const SearchParams P) {
             if (wl == 0) {
                 s_npass = n;
                 s_dense = dense;
+            }
+            if (do_scan) {  // nearest parent of the tile -> nearest of the head
+                unsigned long long best = wl < SEARCH_GROUPS ? s_scan[wl] : ~0ull;
+#pragma unroll
+                for (int sft = 16; sft >= 1; sft >>= 1) {
+                    const unsigned long long o = __shfl_xor_sync(0xffffffffu, best, sft);
+                    best = o < best ? o : best;
+                }
+                if (wl == 0 && best != ~0ull) atomicMin(P.scan_out + h, best);
             }
         }
         __syncthreads();
@@ -690,11 +763,11 @@ search_kernel(const SearchParams P) {
     }
 }
 
-template <typename T, int GT, int NCH, int STAGES, int MINB, bool FULLD, int RPI>
-static int launch_search_fd(SearchParams P, int chunks, cudaStream_t stream) {
+template <typename T, int GT, int NCH, int STAGES, int MINB, bool FULLD, int RPI, bool SCAN>
+static int launch_search_sc(SearchParams P, int chunks, cudaStream_t stream) {
     constexpr int SEARCH_THREADS = 128;    // 4 warps: one compaction warp per head
     constexpr int BLOCKS = MINB;           // 128-thread CTAs resident per SM
-    auto kern = search_kernel<T, GT, NCH, STAGES, BLOCKS, FULLD, SEARCH_THREADS, RPI>;
+    auto kern = search_kernel<T, GT, NCH, STAGES, BLOCKS, FULLD, SEARCH_THREADS, RPI, SCAN>;
     const size_t tile_rows = (size_t)P.tile_parents * P.bf;
     size_t off = tile_rows * GT * sizeof(float) + (size_t)P.tile_parents * (4 + 2 + 1 + 1);
     off = (off + 15) & ~(size_t)15;
@@ -715,6 +788,12 @@ static int launch_search_fd(SearchParams P, int chunks, cudaStream_t stream) {
     kern<<<grid, SEARCH_THREADS, smem, stream>>>(P);
     HIRA_CHECK_LAUNCH("hira_search launch");
     return HIRA_OK;
+}
+
+template <typename T, int GT, int NCH, int STAGES, int MINB, bool FULLD, int RPI>
+static int launch_search_fd(const SearchParams& P, int chunks, cudaStream_t stream) {
+    if (P.scan_out != nullptr) return launch_search_sc<T, GT, NCH, STAGES, MINB, FULLD, RPI, true>(P, chunks, stream);
+    return launch_search_sc<T, GT, NCH, STAGES, MINB, FULLD, RPI, false>(P, chunks, stream);
 }
 
 // FULLD: every lane's chunks lie inside the row (D == 64 * NCH), so the per-chunk bounds tests drop out
@@ -788,13 +867,21 @@ extern "C" int hira_search_tile_parents(const hira_index_t* ix) {
     return tp;
 }
 
-extern "C" int hira_search(const hira_index_t* ix, const float* q, const float* tau,
-                           const float* scaling, const float* qnorm, const int32_t* q2kv,
-                           int32_t n_qheads, int32_t max_group, int32_t flags,
-                           int32_t tile_parents, float* out_dense, int32_t* out_idx,
-                           float* out_score, int32_t* out_count, uint32_t* stats, void* stream) {
+static int search_impl(const hira_index_t* ix, const float* q, const float* tau,
+                       const float* scaling, const float* qnorm, const int32_t* q2kv,
+                       int32_t n_qheads, int32_t max_group, int32_t flags,
+                       int32_t tile_parents, float* out_dense, int32_t* out_idx,
+                       float* out_score, int32_t* out_count, uint32_t* stats,
+                       const void* scan_key, int64_t scan_key_stride, unsigned long long* scan_out, void* stream) {
     int rc = validate_index(ix, false);
     if (rc != HIRA_OK) return rc;
+    if (scan_out != nullptr) {
+        HIRA_CHECK_ARG(scan_key != nullptr && ix->parent_sqnorm != nullptr, HIRA_ERR_ARG,
+                       "hira_search_scan: scan_key and the index's parent_sqnorm cache are required");
+        HIRA_CHECK_ARG(q2kv == nullptr, HIRA_ERR_ARG,
+                       "hira_search_scan: the fused scan needs the default head grouping (q2kv == NULL), so that "
+                       "every kv head is visited");
+    }
     HIRA_CHECK_ARG(q && tau, HIRA_ERR_ARG, "hira_search: q and tau must not be NULL");
     HIRA_CHECK_ARG(n_qheads >= 1, HIRA_ERR_SHAPE, "hira_search: n_qheads=%d must be >= 1", n_qheads);
     HIRA_CHECK_ARG((flags & ~0x7) == 0 && (flags & 0x6) != 0x6, HIRA_ERR_ARG, "hira_search: bad flags 0x%x", flags);
@@ -825,6 +912,8 @@ extern "C" int hira_search(const hira_index_t* ix, const float* q, const float* 
     P.q = q; P.tau = tau; P.scaling = scaling; P.qnorm = qnorm; P.q2kv = q2kv;
     P.out_dense = out_dense; P.out_idx = out_idx; P.out_score = out_score; P.out_count = out_count;
     P.stats = stats;
+    P.scan_key = scan_key; P.scan_key_stride = scan_key_stride; P.scan_out = scan_out;
+    P.parent_sqnorm = ix->parent_sqnorm;
     P.n_heads = ix->n_heads; P.n_qheads = n_qheads; P.group = group; P.depth = ix->depth;
     P.bf = bf; P.dim = ix->dim; P.cap_parents = ix->cap_parents; P.cap_gp = ix->cap_gp;
     P.tile_parents = tile_parents;
@@ -854,4 +943,24 @@ extern "C" int hira_search(const hira_index_t* ix, const float* q, const float* 
     if (ix->dtype == HIRA_BF16)
         return wide ? dispatch_gt<__nv_bfloat16, 4>(P, max_group, s) : dispatch_gt<__nv_bfloat16, 2>(P, max_group, s);
     return wide ? dispatch_gt<float, 4>(P, max_group, s) : dispatch_gt<float, 2>(P, max_group, s);
+}
+
+extern "C" int hira_search(const hira_index_t* ix, const float* q, const float* tau,
+                           const float* scaling, const float* qnorm, const int32_t* q2kv,
+                           int32_t n_qheads, int32_t max_group, int32_t flags,
+                           int32_t tile_parents, float* out_dense, int32_t* out_idx,
+                           float* out_score, int32_t* out_count, uint32_t* stats, void* stream) {
+    return search_impl(ix, q, tau, scaling, qnorm, q2kv, n_qheads, max_group, flags, tile_parents, out_dense,
+                       out_idx, out_score, out_count, stats, nullptr, 0, nullptr, stream);
+}
+
+extern "C" int hira_search_scan(const hira_index_t* ix, const float* q, const float* tau,
+                                const float* scaling, const float* qnorm, int32_t n_qheads, int32_t flags,
+                                int32_t tile_parents, float* out_dense, int32_t* out_idx,
+                                float* out_score, int32_t* out_count, uint32_t* stats,
+                                const void* scan_key, int64_t scan_key_stride, uint64_t* scan_out, void* stream) {
+    HIRA_CHECK_ARG(scan_out != nullptr, HIRA_ERR_ARG, "hira_search_scan: scan_out must not be NULL");
+    return search_impl(ix, q, tau, scaling, qnorm, nullptr, n_qheads, 0, flags, tile_parents, out_dense,
+                       out_idx, out_score, out_count, stats, scan_key, scan_key_stride,
+                       reinterpret_cast<unsigned long long*>(scan_out), stream);
 }

@@ -79,15 +79,6 @@ threshold_kernel(const T* __restrict__ samples, long long head_stride, int n_sam
     }
 }
 
-__device__ __forceinline__ uint32_t order_key(float f) {
-    const uint32_t u = __float_as_uint(f);
-    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
-}
-__device__ __forceinline__ float key_to_float(uint32_t k) {
-    const uint32_t u = (k & 0x80000000u) ? (k & 0x7fffffffu) : ~k;
-    return __uint_as_float(u);
-}
-
 // radix select, 8 bits per pass, over the compacted scores of one query head
 __global__ void __launch_bounds__(1024)
 kth_kernel(const float* __restrict__ score, const int32_t* __restrict__ count, long long cap_children,

@@ -171,13 +171,29 @@ def _f32(t: Optional[torch.Tensor], dev) -> Optional[torch.Tensor]:
 
 def search(st: IndexState, q: torch.Tensor, tau: torch.Tensor, *, scaling=None, qnorm=None, q2kv=None,
            max_group: int = 0, flags: int = 0, out_dense=None, compact: Optional[CompactResult] = None,
-           want_compact: bool = False, stats=None, tp: Optional[int] = None):
-    """q (H_q, D) fp32, tau (H_q,) fp32 on the index device.  Returns (out_dense, CompactResult|None)."""
+           want_compact: bool = False, stats=None, tp: Optional[int] = None, scan_key=None, scan_out=None):
+    """q (H_q, D) fp32, tau (H_q,) fp32 on the index device.  Returns (out_dense, CompactResult|None).
+    With `scan_key` (n_heads, D) in the index dtype and `scan_out` (new_scan_slots), the parents are
+    also scored against that key for the `append_scanned` that follows."""
     lib = L.load()
     hq = q.shape[0]
     tp = tp or tile_parents(st)
     if want_compact and compact is None:
         compact = alloc_compact(st, hq, tp)
+    if scan_out is not None:
+        if q2kv is not None:
+            raise ValueError("the fused parent scan needs the default head grouping")
+        assert scan_key.dtype == st.dtype and scan_key.shape[0] == st.n_heads and scan_key.stride(-1) == 1
+        rc = lib.hira_search_scan(st.struct, L.ptr(q), L.ptr(tau), L.ptr(scaling), L.ptr(qnorm), hq, flags, tp,
+                                  L.ptr(out_dense), L.ptr(compact.idx) if compact else None,
+                                  L.ptr(compact.score) if compact else None, L.ptr(compact.count) if compact else None,
+                                  L.ptr(stats), L.ptr(scan_key), scan_key.stride(0), L.ptr(scan_out),
+                                  L.current_stream(st.device))
+        L.check(rc, "hira_search_scan")
+        if compact is not None:
+            compact.n_tiles_active = None if (st.active_parents == 0 or out_dense is not None) \
+                else -(-st.active_parents // tp)
+        return out_dense, compact
     rc = lib.hira_search(st.struct, L.ptr(q), L.ptr(tau), L.ptr(scaling), L.ptr(qnorm), L.ptr(q2kv), hq,
                          max_group, flags, tp, L.ptr(out_dense),
                          L.ptr(compact.idx) if compact else None, L.ptr(compact.score) if compact else None,
@@ -264,6 +280,25 @@ def append(st: IndexState, new_k: torch.Tensor, new_v: Optional[torch.Tensor], t
     L.check(rc, "hira_append")
 
 
+def new_scan_slots(st: IndexState) -> torch.Tensor:
+    """The (n_heads,) buffer `search(..., scan_out=)` fills and `append_scanned` consumes."""
+    return torch.full((st.n_heads,), -1, dtype=torch.int64, device=st.device)
+
+
+def append_scanned(st: IndexState, new_k: torch.Tensor, new_v: Optional[torch.Tensor], scan: torch.Tensor,
+                   token_base: int = -1):
+    """One key per head, new_k (n_heads, 1, D) / new_v (n_heads, 1, V) in the index dtypes, whose
+    nearest parent the preceding `search(..., scan_key=new_k[:, 0], scan_out=scan)` found."""
+    lib = L.load()
+    assert new_k.dtype == st.dtype and new_k.shape[1] == 1 and new_k.stride(-1) == 1
+    if new_v is not None:
+        assert new_v.dtype == st.vdtype and new_v.stride(-1) == 1
+    rc = lib.hira_append_scanned(st.struct, L.ptr(new_k), L.ptr(new_v), new_k.stride(0),
+                                 new_v.stride(0) if new_v is not None else 0, token_base, L.ptr(st.status),
+                                 L.ptr(scan), L.current_stream(st.device))
+    L.check(rc, "hira_append_scanned")
+
+
 def threshold(samples: torch.Tensor, q: torch.Tensor, method: int, k: int = 1, q2kv=None, out=None):
     """samples (H_kv, S, D) contiguous fp32/bf16, q (H_q, D) fp32 -> tau (H_q,)."""
     lib = L.load()
@@ -294,7 +329,7 @@ def prepare_query(q: torch.Tensor, sm_scale: float, q_hat=None, logit_scale=None
 def decode_attention(st: IndexState, q: torch.Tensor, sm_scale: float, tau: torch.Tensor, compact: CompactResult,
                      q_hat: torch.Tensor, logit_scale: torch.Tensor, *, q2kv=None, max_group: int = 0, flags: int = 0,
                      queued_k=None, queued_v=None, n_splits: int, workspace: torch.Tensor, out: torch.Tensor,
-                     out_ml=None):
+                     out_ml=None, scan_key=None, scan_out=None):
     """prepare_query + search (compact) + sparse_attn in one library call.  q (H_q, D) fp32/bf16
     contiguous; everything else preallocated by the caller."""
     lib = L.load()
@@ -312,6 +347,8 @@ def decode_attention(st: IndexState, q: torch.Tensor, sm_scale: float, tau: torc
                                    L.ptr(compact.idx), L.ptr(compact.score), L.ptr(compact.count),
                                    L.ptr(queued_k) if n_queued else None, L.ptr(queued_v) if n_queued else None,
                                    n_queued, qstride, n_splits, L.ptr(workspace), L.ptr(out), L.ptr(out_ml),
+                                   L.ptr(scan_key) if scan_out is not None else None,
+                                   scan_key.stride(0) if scan_out is not None else 0, L.ptr(scan_out),
                                    L.current_stream(st.device))
     L.check(rc, "hira_decode_attention")
     compact.n_tiles_active = None if st.active_parents == 0 else -(-st.active_parents // compact.tile_parents)

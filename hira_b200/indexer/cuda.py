@@ -54,6 +54,8 @@ class CUDAIndexer(BaseIndexer):
         self._parents_bound = 0   # host-side upper bounds on used parent / grandparent slots
         self._gp_bound = 0
         self._snapshot = None     # (pinned copy of `used`, event, keys appended when it was taken)
+        self._scan_slots = None   # nearest-parent results of a search that scanned for the next update
+        self._scan_pending = False
         self._pinned = None
         self._appended = 0        # keys appended since the build
         self._n_keys = 0
@@ -164,6 +166,7 @@ class CUDAIndexer(BaseIndexer):
         self._parents_bound = k2 * bf if st.depth == 3 else k1
         self._gp_bound = k2
         self._snapshot = None
+        self._scan_slots, self._scan_pending = None, False
         return self
 
     # ---- update -------------------------------------------------------------
@@ -190,8 +193,30 @@ class CUDAIndexer(BaseIndexer):
         self.state = st.grown(new_cap)
 
     @torch.no_grad()
-    def update(self, new_keys: torch.Tensor, new_values: Optional[torch.Tensor] = None):
-        """new_keys (B, H, M, D), new_values optional (B, H, M, V) -- appended one after another."""
+    def begin_scanned_update(self, key: torch.Tensor):
+        """For the search that precedes `update(key, value, scanned=True)`: the key folded to
+        (B*H, D) in the index dtype and the per-head slots the search leaves its nearest-parent
+        result in."""
+        st = self.state
+        if st is None:
+            raise ValueError("Indexer is not built")
+        if key.ndim != 4 or key.shape[2] != 1:
+            raise ValueError(f"append_key must be (B, H, 1, D), got {tuple(key.shape)}")
+        k = self._fold(key.to(st.device)).to(st.dtype)[:, 0].contiguous()
+        if k.shape != (self.num_heads, self.dim):
+            raise ValueError(f"append_key has (heads, dim)={tuple(k.shape)}, index has ({self.num_heads}, {self.dim})")
+        if self._scan_slots is None or self._scan_slots.device != st.device or self._scan_slots.numel() != st.n_heads:
+            self._scan_slots = S.new_scan_slots(st)
+        elif self._scan_pending:
+            self._scan_slots.fill_(-1)        # an earlier scan was never consumed
+        self._scan_pending = True
+        return k, self._scan_slots
+
+    @torch.no_grad()
+    def update(self, new_keys: torch.Tensor, new_values: Optional[torch.Tensor] = None, scanned: bool = False):
+        """new_keys (B, H, M, D), new_values optional (B, H, M, V) -- appended one after another.
+        `scanned=True` (M == 1): the search that ran just before was given this key
+        (`hira_decode_attention(..., append_key=new_keys)`) and already found its nearest parent."""
         if self.state is None:
             raise ValueError("Indexer is not built")
         assert new_values is None or new_keys.shape[:3] == new_values.shape[:3]
@@ -210,7 +235,15 @@ class CUDAIndexer(BaseIndexer):
         if m == 0:
             return self
         self._ensure_capacity(m)
-        S.append(self.state, k.to(self.state.dtype), v)
+        if scanned:
+            if m != 1 or not self._scan_pending:
+                raise ValueError("update(scanned=True) needs one key per head and a search that scanned for it")
+            S.append_scanned(self.state, k.to(self.state.dtype), v, self._scan_slots)
+        else:
+            if self._scan_pending:
+                self._scan_slots.fill_(-1)    # the index changes: that scan is void
+            S.append(self.state, k.to(self.state.dtype), v)
+        self._scan_pending = False
         self._parents_bound += m
         self._gp_bound += m
         self._n_keys += m
@@ -275,6 +308,7 @@ class CUDAIndexer(BaseIndexer):
         b.build(keys.unsqueeze(0), None if values is None else values.unsqueeze(0))
         self.state, self._parents_bound, self._gp_bound = b.state, b._parents_bound, b._gp_bound
         self._snapshot = None
+        self._scan_slots, self._scan_pending = None, False
         return self
 
     # ---- checkpoint ---------------------------------------------------------

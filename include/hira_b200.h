@@ -233,6 +233,27 @@ int hira_threshold(const void* samples, int32_t dtype, int32_t n_heads,
                    const float* q, const int32_t* q2kv, int32_t n_qheads,
                    int32_t method, int32_t k, float* tau_out, void* stream);
 
+/* Search with the next append's parent scan folded in.  A decode step that appends one key
+ * per head right after its search reads every parent row twice: once for the search gates, once
+ * for the append's nearest-parent scan.  hira_search_scan does both on the single read: while the
+ * gates of a tile are computed, the same parent rows are scored against `scan_key` (the key that
+ * will be appended) exactly as hira_append scores them, and the best (score, slot) of each head is
+ * kept in scan_out by a 64-bit atomicMin.  hira_append_scanned then inserts that key without a scan
+ * of its own and resets the slot.  The index must not change between the two calls.  The reference
+ * has no counterpart: its update runs its own nearest-parent kernel (kernels/
+ * triton_update_kernels.py:6-60).  Default head grouping only (no q2kv).
+ *   scan_key [n_heads] rows of `dim` elements in the index dtype, stride in elements
+ *   scan_out [n_heads] uint64, all bits set before the first call (hira_append_scanned leaves
+ *            it so); holds order-preserving-key(score) << 32 | parent slot                     */
+int hira_search_scan(const hira_index_t* index, const float* q, const float* tau,
+                     const float* scaling, const float* qnorm, int32_t n_qheads, int32_t flags,
+                     int32_t tile_parents, float* out_dense, int32_t* out_idx,
+                     float* out_score, int32_t* out_count, uint32_t* stats,
+                     const void* scan_key, int64_t scan_key_stride, uint64_t* scan_out, void* stream);
+int hira_append_scanned(const hira_index_t* index, const void* new_k, const void* new_v,
+                        int64_t k_head_stride, int64_t v_head_stride, int32_t token_base,
+                        int32_t* status, uint64_t* scan, void* stream);
+
 /* Query preparation for a decode step: q_hat[qh] = q[qh] / ||q[qh]|| in fp32 and
  * logit_scale[qh] = ||q[qh]|| * sm_scale, i.e. the unit query the tree bound assumes and the
  * `scaling` that turns emitted scores into attention logits (searcher/cpu.py:58-63).
@@ -247,14 +268,16 @@ int hira_prepare_query(const void* q, int32_t dtype, int32_t n_qheads, int32_t d
  * folding the three calls into one saves the caller two trips through its FFI.
  *   q [n_qheads][dim] raw queries in `q_dtype`;  tau [n_qheads] on the scale of q_hat . k;
  *   q_hat [n_qheads][dim], logit_scale [n_qheads]: scratch, left holding the prepared query;
- *   idx/score/count, workspace, out, out_ml, queued_*: as in hira_search / hira_sparse_attn. */
+ *   idx/score/count, workspace, out, out_ml, queued_*: as in hira_search / hira_sparse_attn;
+ *   scan_key, scan_key_stride, scan_out: as in hira_search_scan, or NULL, 0, NULL. */
 int hira_decode_attention(const hira_index_t* index, const void* q, int32_t q_dtype, float sm_scale,
                           const float* tau, const int32_t* q2kv, int32_t n_qheads, int32_t max_group,
                           int32_t flags, int32_t tile_parents, float* q_hat, float* logit_scale,
                           int32_t* idx, float* score, int32_t* count,
                           const void* queued_k, const void* queued_v, int32_t n_queued,
                           int64_t queued_head_stride, int32_t n_splits, float* workspace,
-                          float* out, float* out_ml, void* stream);
+                          float* out, float* out_ml,
+                          const void* scan_key, int64_t scan_key_stride, uint64_t* scan_out, void* stream);
 
 /* Exact k-th largest of the scores in a compacted search output (run
  * hira_search with HIRA_LEAF_CANDIDATES, tau = -inf and scaling = NULL first).

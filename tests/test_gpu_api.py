@@ -304,3 +304,35 @@ def test_active_bound_skips_empty_capacity_without_changing_results(levels):
         assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
     # the split of the tile range over CTAs differs, so the output may differ in the last bits
     assert torch.allclose(out_b, out_f, rtol=1e-5, atol=1e-6) and torch.equal(kth_b, kth_f)
+
+
+@pytest.mark.parametrize("levels", [2, 3])
+def test_scanned_update_through_the_public_classes(levels):
+    """hira_decode_attention(append_key=k) + update(k, v, scanned=True) leaves the same index and
+    the same attention output as the plain decode_attention + update."""
+    from hira_b200.cache import CacheOutput
+    h, hq, n, d, bf = 2, 4, 1024, 64, 8
+    keys, vals = _keys(h, n, d, 51), _keys(h, n, d, 52)
+    a = CUDAIndexer(levels, 1, bf, max_context=n + 64, seed=3).build(keys, vals)
+    b = CUDAIndexer(levels, 1, bf, max_context=n + 64, seed=3).build(keys, vals)
+    more_k, more_v = _keys(h, 20, d, 53), _keys(h, 20, d, 54)
+    tau = torch.full((hq,), 0.1, device="cuda")
+    empty = torch.empty((1, h, 0, d), device="cuda")
+    ca = CacheOutput(queued_keys=empty, queued_values=empty, prefill_keys=None, prefill_values=None, indexer=a,
+                     searcher=CUDASearcher(bf))
+    cb = CacheOutput(queued_keys=empty, queued_values=empty, prefill_keys=None, prefill_values=None, indexer=b,
+                     searcher=CUDASearcher(bf))
+    for i in range(20):
+        q = _query(hq, d, 60 + i)
+        k, v = more_k[:, :, i:i + 1], more_v[:, :, i:i + 1]
+        oa = hira_decode_attention(q, ca, threshold=tau)
+        a.update(k, v)
+        ob = hira_decode_attention(q, cb, threshold=tau, append_key=k)
+        b.update(k, v, scanned=True)
+        assert torch.equal(oa, ob)
+    a.check_status(), b.check_status()
+    for name in a.state.ARRAYS:
+        x, y = getattr(a.state, name), getattr(b.state, name)
+        assert x is None and y is None or torch.equal(x, y), name
+    with pytest.raises(ValueError):
+        b.update(more_k[:, :, :1], more_v[:, :, :1], scanned=True)      # no search scanned for this key

@@ -182,6 +182,58 @@ def test_append_with_and_without_workspace_agree():
     assert_index_equal(b, ox, "append without workspace")
 
 
+SCAN_CASES = [
+    # h, n, d, bf, depth, dtype, group, steps
+    (2, 256, 32, 8, 2, torch.float32, 1, 30),
+    (2, 500, 64, 8, 3, torch.float32, 2, 40),
+    (3, 4096, 128, 32, 3, torch.bfloat16, 4, 40),
+    (2, 2048, 128, 32, 3, torch.bfloat16, 8, 20),     # two 4-head chunks per kv head: only the first scans
+    (1, 100, 128, 4, 3, torch.bfloat16, 1, 50),       # many parents per tile (the gate loop beyond the staged rows)
+    (2, 700, 256, 16, 3, torch.float32, 2, 20),
+]
+
+
+@pytest.mark.parametrize("h,n,d,bf,depth,dtype,group,steps", SCAN_CASES)
+def test_search_with_fused_parent_scan_equals_search_then_append(h, n, d, bf, depth, dtype, group, steps):
+    """search + append against search-with-scan + append-from-scan on twin indexes, key after key:
+    the same keys are selected and the indexes stay bit-identical to the oracle's."""
+    a, ox, keys, vals = build_both(h, n, d, bf, depth, dtype, seed=71, spare=(steps + 1) * bf)
+    b, _, _, _ = build_both(h, n, d, bf, depth, dtype, seed=71, spare=(steps + 1) * bf)
+    new_k = make_keys(h, steps, d, 72, dtype)
+    new_v = make_keys(h, steps, d, 73, dtype, normalize=False)
+    hq = h * group
+    q = make_queries(hq, d, seed=74)
+    tau = torch.full((hq,), 0.15, device="cuda")
+    flags = L.HIRA_GATE_GE | L.HIRA_LEAF_GE
+    ca, cb = S.alloc_compact(a, hq), S.alloc_compact(b, hq)
+    scan = S.new_scan_slots(b)
+    for i in range(steps):
+        k1, v1 = new_k[:, i:i + 1].contiguous(), new_v[:, i:i + 1].contiguous()
+        S.search(a, q, tau, flags=flags, compact=ca)
+        S.append(a, k1, v1)
+        S.search(b, q, tau, flags=flags, compact=cb, scan_key=new_k[:, i], scan_out=scan)
+        S.append_scanned(b, new_k[:, i:i + 1], new_v[:, i:i + 1], scan)       # strided views are fine
+        O.append(ox, k1, v1)
+        if i % 7 == 0 or i == steps - 1:
+            torch.cuda.synchronize()
+            la, lb = ca.to_lists(), cb.to_lists()
+            for x, y in zip(la, lb):
+                assert torch.equal(x[0], y[0]) and torch.equal(x[1], y[1])
+    torch.cuda.synchronize()
+    assert bool((scan == -1).all())                    # every slot was consumed and reset
+    assert int(a.status.item()) == 0 and int(b.status.item()) == 0
+    assert_index_equal(a, ox, "search then append")
+    assert_index_equal(b, ox, "search with scan, append from scan")
+
+
+def test_fused_scan_rejects_explicit_head_map():
+    st, _, _, _ = build_both(2, 256, 32, 8, 2, torch.float32, seed=75, spare=16)
+    q = make_queries(2, 32, seed=76)
+    with pytest.raises(ValueError):
+        S.search(st, q, torch.zeros(2, device="cuda"), q2kv=torch.tensor([1, 0], dtype=torch.int32, device="cuda"),
+                 want_compact=True, scan_key=make_keys(2, 1, 32, 77)[:, 0], scan_out=S.new_scan_slots(st))
+
+
 def test_append_capacity_status():
     h, n, d, bf = 1, 64, 32, 8
     st, ox, keys, vals = build_both(h, n, d, bf, 2, torch.float32, seed=5, spare=2)

@@ -452,15 +452,14 @@ search_kernel(const SearchParams P) {
                 s_npass = n;
                 s_dense = dense;
             }
-            if (do_scan) {  // nearest parent of the tile -> nearest of the head
-                unsigned long long best = wl < SEARCH_GROUPS ? s_scan[wl] : ~0ull;
+        } else if (warp == 1 && do_scan) {  // meanwhile: nearest parent of the tile -> nearest of the head
+            unsigned long long best = wl < SEARCH_GROUPS ? s_scan[wl] : ~0ull;
 #pragma unroll
-                for (int sft = 16; sft >= 1; sft >>= 1) {
-                    const unsigned long long o = __shfl_xor_sync(0xffffffffu, best, sft);
-                    best = o < best ? o : best;
-                }
-                if (wl == 0 && best != ~0ull) atomicMin(P.scan_out + h, best);
+            for (int sft = 16; sft >= 1; sft >>= 1) {
+                const unsigned long long o = __shfl_xor_sync(0xffffffffu, best, sft);
+                best = o < best ? o : best;
             }
+            if (wl == 0 && best != ~0ull) atomicMin(P.scan_out + h, best);
         }
         __syncthreads();
         const int npass = s_npass;

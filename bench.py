@@ -366,7 +366,7 @@ def run_ours(args):
                    "sharding": f"kv_head x{world}", "l2": "inputs>L2 (keys per GPU >> 126 MB)",
                    "gate": "ge", "leaf": "ge"},
         "e2e": {"value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]},
-        "gpu_launches": args.steps * (4 if fused else 5),   # search, sparse_attn, merge, [append_scan,] append
+        "gpu_launches": args.steps * (1 + (1 if n_splits == 1 else 2) + (1 if fused else 2)),   # search, sparse_attn[, merge][, append_scan], append
         "roofline": {"bound": "hbm", "kernel": "search_kernel", "achieved": achieved, "peak": peak,
                      "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": (SEARCH_DRAM_BYTES_PER_GROUP_AT_CTX * n_groups if ctx == CTX else None),

@@ -33,6 +33,8 @@ struct AttnParams {
     const void* queued_k;
     const void* queued_v;
     float* ws;
+    float* out;     // with one split the kernel writes the normalised output (and out_ml) itself
+    float* out_ml;
     int n_heads, n_qheads, group, dim, vdim, n_tiles, tile_rows, n_splits, n_queued;
     int n_tiles_active;  // tiles that can hold keys (<= n_tiles, the stride of `count`)
     long long cap_children;
@@ -244,6 +246,21 @@ sparse_attn_kernel(const AttnParams P) {
     }
     if (lane == 0) s_red[hw] = l;
     __syncthreads();
+    if (P.n_splits == 1) {
+        // the only partial of this head: what the merge would compute, written directly
+        float L = 0.f;
+        for (int w = 0; w < ATTN_HW; ++w) L += s_red[w];
+        for (int d = tid; d < P.vdim; d += ATTN_THREADS) {
+            float s = 0.f;
+            for (int w = 0; w < ATTN_HW; ++w) s += s_out[(size_t)w * P.vdim + d];
+            P.out[(size_t)qh * P.vdim + d] = L > 0.f ? s / L : 0.f;
+        }
+        if (tid == 0 && P.out_ml) {
+            P.out_ml[2 * qh] = m;
+            P.out_ml[2 * qh + 1] = L;
+        }
+        return;
+    }
     float* ws = P.ws + ((size_t)qh * P.n_splits + split) * (P.vdim + 2);
     for (int d = tid; d < P.vdim; d += ATTN_THREADS) {
         float s = 0.f;
@@ -355,6 +372,7 @@ extern "C" int hira_sparse_attn(const hira_index_t* ix, const float* q, const fl
     P.values = ix->values; P.q = q; P.scaling = scaling; P.q2kv = q2kv;
     P.idx = idx; P.score = score; P.count = count;
     P.queued_k = queued_k; P.queued_v = queued_v; P.ws = workspace;
+    P.out = out; P.out_ml = out_ml;
     P.n_heads = ix->n_heads; P.n_qheads = n_qheads;
     P.group = q2kv ? 1 : n_qheads / ix->n_heads;
     P.dim = ix->dim; P.vdim = ix->vdim;
@@ -370,6 +388,7 @@ extern "C" int hira_sparse_attn(const hira_index_t* ix, const float* q, const fl
     else if (ix->dtype == HIRA_F32 && ix->vdtype == HIRA_BF16) rc = launch_attn<float, __nv_bfloat16>(P, s);
     else rc = launch_attn<__nv_bfloat16, float>(P, s);
     if (rc != HIRA_OK) return rc;
+    if (n_splits == 1) return HIRA_OK;  // the attention kernel wrote `out` itself
     const long long pstride = ix->vdim + 2;
     merge_kernel<<<n_qheads, 128, 0, s>>>(workspace + 2, workspace, pstride, pstride * n_splits, pstride,
                                           pstride * n_splits, n_splits, ix->vdim, 0, out, out_ml);

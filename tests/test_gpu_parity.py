@@ -45,6 +45,7 @@ SEARCH_CASES = [
     (1, 640, 128, 4, 3, torch.float32, 12),
     (2, 700, 256, 10, 3, torch.float32, 4),
     (1, 300, 64, 1, 2, torch.float32, 2),
+    (1, 6000, 64, 48, 3, torch.bfloat16, 2),      # three 16-parent tiles per grandparent (not a power of two)
 ]
 FLAG_CASES = [
     L.HIRA_GATE_GT | L.HIRA_LEAF_CANDIDATES,

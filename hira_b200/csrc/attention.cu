@@ -18,8 +18,8 @@ namespace hira {
 
 constexpr int ATTN_THREADS = 128;
 constexpr int ATTN_HW = ATTN_THREADS / GROUP;  // 8-lane groups: one value row per group per step
-constexpr int ATTN_CHUNK = 2048;  // list entries staged in shared memory (>= rows of one search tile)
-constexpr int ATTN_UNROLL = 4;
+constexpr int ATTN_LIST = 1024;   // (slot, logit) entries per staging list; there are two lists
+constexpr int ATTN_TB = 32;       // tiles whose counts are fetched and prefix-summed together
 constexpr int QUEUE_FLAG = 0x40000000;
 
 struct AttnParams {
@@ -41,6 +41,26 @@ struct AttnParams {
     long long queued_head_stride;
 };
 
+__device__ __forceinline__ void attn_cp_async_16(uint32_t smem_addr, const void* gmem_src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(smem_addr), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void attn_cp_async_4(uint32_t smem_addr, const void* gmem_src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_addr), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void attn_cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void attn_cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+// value rows in flight per 8-lane group: the ring of one CTA is ATTN_THREADS * 16 B * pieces * depth
+template <typename TV, int NVCH>
+struct GatherRing {
+    static constexpr int TPP = (int)(sizeof(TV) / 2);       // 16-byte pieces per 8-element chunk
+    static constexpr int PIECES = NVCH * TPP;               // 16-byte pieces per thread per row
+    static constexpr int STAGE_BYTES = ATTN_THREADS * 16 * PIECES;
+    static constexpr int DEPTH = STAGE_BYTES <= 4096 ? 6 : (STAGE_BYTES <= 8192 ? 3 : 2);  // 24 KB: five CTAs per SM
+    static constexpr int BYTES = STAGE_BYTES * DEPTH;
+};
+
 template <typename TV, int NVCH>
 __device__ __forceinline__ void accumulate_row(float (&acc)[NVCH][8], const RawChunk<TV> (&raw)[NVCH], float p) {
 #pragma unroll
@@ -55,14 +75,14 @@ __device__ __forceinline__ void accumulate_row(float (&acc)[NVCH][8], const RawC
 template <typename TK, typename TV, int NCH, int NVCH>
 __global__ void __launch_bounds__(ATTN_THREADS)
 sparse_attn_kernel(const AttnParams P) {
-    __shared__ int s_idx[ATTN_CHUNK];
-    __shared__ float s_logit[ATTN_CHUNK];
-    __shared__ int s_cnt[ATTN_THREADS];
-    __shared__ int s_off[ATTN_THREADS + 1];
+    __shared__ int s_idx[2][ATTN_LIST];
+    __shared__ float s_logit[2][ATTN_LIST];
+    __shared__ int s_cnt[2][ATTN_TB];
+    __shared__ int s_off[2][ATTN_TB + 1];
     __shared__ float s_red[ATTN_HW];
     __shared__ float s_bcast;
-    __shared__ int s_end;
-    extern __shared__ __align__(16) float s_out[];  // [ATTN_HW][vdim]
+    extern __shared__ __align__(16) float s_out[];  // [ATTN_HW][vdim] at the end; the gather ring before
+    using Ring = GatherRing<TV, NVCH>;
 
     const int tid = threadIdx.x;
     const int lane = tid & (GROUP - 1);
@@ -83,9 +103,8 @@ sparse_attn_kernel(const AttnParams P) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
 
-    int fill = 0;
-
-    auto flush = [&]() {
+    // online-softmax step over one staged list: block maximum, rescale, gather + accumulate
+    auto flush = [&](const int* s_idx, const float* s_logit, int fill) {
         __syncthreads();
         // block max of the staged logits
         float mx = -CUDART_INF_F;
@@ -109,92 +128,141 @@ sparse_attn_kernel(const AttnParams P) {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) acc[i][e] *= alpha;
             m = new_m;
-            for (int base = 0; base < fill; base += ATTN_HW * ATTN_UNROLL) {
-                RawChunk<TV> raw[ATTN_UNROLL][NVCH];
-                float p[ATTN_UNROLL];
+            // Value rows through a private ring of asynchronous 16-byte copies: each thread keeps
+            // DEPTH-1 rows of its group in flight ahead of the one it accumulates, and only reads
+            // the pieces it copied itself, so the gather is a continuous stream without barriers.
+            const uint32_t ring_s = (uint32_t)__cvta_generic_to_shared(s_out) + tid * 16;
+            const unsigned char* ring_g = reinterpret_cast<const unsigned char*>(s_out) + tid * 16;
+            const int n_rounds = (fill + ATTN_HW - 1) / ATTN_HW;  // uniform over the CTA
+            auto issue = [&](int k) {
+                const int e = k * ATTN_HW + hw;
+                if (k < n_rounds && e < fill) {
+                    const int id = s_idx[e];
+                    const TV* row = (id & QUEUE_FLAG)
+                        ? reinterpret_cast<const TV*>(P.queued_v) + (size_t)h * P.queued_head_stride + (size_t)(id & ~QUEUE_FLAG) * P.vdim
+                        : values + (size_t)id * P.vdim;
+                    const uint32_t dst = ring_s + (uint32_t)(k % Ring::DEPTH) * Ring::STAGE_BYTES;
 #pragma unroll
-                for (int u = 0; u < ATTN_UNROLL; ++u) {
-                    const int e = base + u * ATTN_HW + hw;
-                    p[u] = 0.f;
-                    const TV* row = nullptr;
-                    if (e < fill) {
-                        const int id = s_idx[e];
-                        p[u] = __expf(s_logit[e] - m);
-                        if (id & QUEUE_FLAG)
-                            row = reinterpret_cast<const TV*>(P.queued_v) + (size_t)h * P.queued_head_stride +
-                                  (size_t)(id & ~QUEUE_FLAG) * P.vdim;
-                        else
-                            row = values + (size_t)id * P.vdim;
-                    }
-#pragma unroll
-                    for (int i = 0; i < NVCH; ++i) {
-                        const int c = lane + GROUP * i;
-                        if (row != nullptr && c * 8 < P.vdim) raw[u][i] = load_chunk_stream<TV>(row, c);
-                        else raw[u][i] = zero_chunk<TV>();
+                    for (int pc = 0; pc < Ring::PIECES; ++pc) {
+                        const int c = lane + GROUP * (pc / Ring::TPP);
+                        if (c * 8 < P.vdim)
+                            attn_cp_async_16(dst + pc * (ATTN_THREADS * 16),
+                                             reinterpret_cast<const char*>(row) + (size_t)c * 8 * sizeof(TV) + (pc % Ring::TPP) * 16);
                     }
                 }
+                attn_cp_async_commit();
+            };
 #pragma unroll
-                for (int u = 0; u < ATTN_UNROLL; ++u) {
-                    accumulate_row<TV, NVCH>(acc, raw[u], p[u]);
-                    l += p[u];
+            for (int k = 0; k < Ring::DEPTH - 1; ++k) issue(k);
+            for (int k = 0; k < n_rounds; ++k) {
+                issue(k + Ring::DEPTH - 1);
+                attn_cp_async_wait<Ring::DEPTH - 1>();
+                const int e = k * ATTN_HW + hw;
+                if (e < fill) {  // uniform inside the group
+                    const float p = __expf(s_logit[e] - m);
+                    const unsigned char* src = ring_g + (size_t)(k % Ring::DEPTH) * Ring::STAGE_BYTES;
+                    RawChunk<TV> raw[NVCH];
+#pragma unroll
+                    for (int i = 0; i < NVCH; ++i) {
+                        if ((lane + GROUP * i) * 8 < P.vdim) {
+                            if constexpr (sizeof(TV) == 2) {
+                                raw[i].a = *reinterpret_cast<const uint4*>(src + i * (ATTN_THREADS * 16));
+                            } else {
+                                raw[i].a = *reinterpret_cast<const float4*>(src + (2 * i) * (ATTN_THREADS * 16));
+                                raw[i].b = *reinterpret_cast<const float4*>(src + (2 * i + 1) * (ATTN_THREADS * 16));
+                            }
+                        } else {
+                            raw[i] = zero_chunk<TV>();
+                        }
+                    }
+                    accumulate_row<TV, NVCH>(acc, raw, p);
+                    l += p;
                 }
             }
         }
+        attn_cp_async_wait<0>();  // also the copies other stages slipped into the ring's groups
         __syncthreads();
-        fill = 0;
     };
 
     // ---- emitted children of this split's tiles -------------------------------
-    // The per-tile counts of a batch of tiles are fetched together and prefix-summed, then
-    // the warps copy the tiles' (slot, logit) segments into the staging list side by side:
-    // two memory latencies per batch instead of two per tile.
-    for (int tb = t0; tb < t1; tb += ATTN_THREADS) {
-        const int nb = min(ATTN_THREADS, t1 - tb);
-        const int my_cnt = tid < nb ? P.count[(size_t)qh * P.n_tiles + tb + tid] : 0;
-        __syncthreads();
-        s_cnt[tid] = my_cnt;
-        // inclusive scan over the warp, then over the warp totals
-        int v = my_cnt;
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-            const int o = __shfl_up_sync(0xffffffffu, v, d);
-            if (wl >= d) v += o;
+    // A three-stage software pipeline over blocks of ATTN_TB tiles, all by asynchronous copies
+    // into shared memory: (A) the tile counts of block b+2, (B) the (slot, logit) entries of
+    // the next list (block b+1, or the next ATTN_LIST entries of a block that emitted more),
+    // (C) maximum + gather of the current list.  A and B ride in the copy groups of C's value
+    // ring, so while the value rows of one list stream in, the next list arrives as well.
+    const int nblk = (t1 - t0 + ATTN_TB - 1) / ATTN_TB;
+    auto fetch_counts = [&](int b) {  // A
+        if (b < nblk && tid < ATTN_TB) {
+            const int t = t0 + b * ATTN_TB + tid;
+            if (t < t1) attn_cp_async_4((uint32_t)__cvta_generic_to_shared(&s_cnt[b & 1][tid]), P.count + (size_t)qh * P.n_tiles + t);
+            else s_cnt[b & 1][tid] = 0;
         }
-        if (wl == 31) s_off[ATTN_THREADS - 8 + warp] = v;   // parked in the tail of s_off until combined
-        __syncthreads();
-        int wbase = 0;
-        for (int w = 0; w < warp; ++w) wbase += s_off[ATTN_THREADS - 8 + w];
-        __syncthreads();
-        s_off[tid + 1] = wbase + v;
-        if (tid == 0) s_off[0] = 0;
-        __syncthreads();
-        int b0 = 0;
-        while (b0 < nb) {
-            // largest e with s_off[e] - s_off[b0] <= room left in the staging list
-            if (tid == 0) {
-                int e = b0;
-                const int room = ATTN_CHUNK - fill;
-                while (e < nb && s_off[e + 1] - s_off[b0] <= room) ++e;
-                s_end = e;
+    };
+    auto scan_counts = [&](int b) {   // prefix sums of a block whose counts have landed (warp 0)
+        if (warp == 0) {
+            const int c = s_cnt[b & 1][wl];
+            int v = c;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int o = __shfl_up_sync(0xffffffffu, v, d);
+                if (wl >= d) v += o;
             }
-            __syncthreads();
-            const int e = s_end;
-            if (e == b0) {  // the next tile does not fit: drain the list first (a tile never exceeds the list)
-                flush();
-                continue;
+            s_off[b & 1][wl + 1] = v;
+            if (wl == 0) s_off[b & 1][0] = 0;
+        }
+    };
+    auto fetch_entries = [&](int b, int sub, int buf) {  // B
+        const int* off = s_off[b & 1];
+        const int v0 = sub * ATTN_LIST;
+        const int n = min(ATTN_LIST, off[ATTN_TB] - v0);
+        for (int i = tid; i < n; i += ATTN_THREADS) {
+            const int v = v0 + i;
+            int lo = 0;  // the tile of entry v: the last one whose prefix is <= v
+#pragma unroll
+            for (int step = ATTN_TB / 2; step >= 1; step >>= 1)
+                if (off[lo + step] <= v) lo += step;
+            const size_t at = (size_t)qh * P.cap_children + (size_t)(t0 + b * ATTN_TB + lo) * P.tile_rows + (size_t)(v - off[lo]);
+            attn_cp_async_4((uint32_t)__cvta_generic_to_shared(&s_idx[buf][i]), P.idx + at);
+            attn_cp_async_4((uint32_t)__cvta_generic_to_shared(&s_logit[buf][i]), P.score + at);
+        }
+    };
+    if (nblk > 0) {
+        fetch_counts(0);
+        attn_cp_async_commit();
+        attn_cp_async_wait<0>();
+        __syncthreads();
+        scan_counts(0);
+        fetch_counts(1);
+        __syncthreads();
+        fetch_entries(0, 0, 0);
+        attn_cp_async_commit();
+        attn_cp_async_wait<0>();
+        __syncthreads();
+        int blk = 0, sub = 0, buf = 0;
+        while (blk < nblk) {  // every test below is uniform over the CTA
+            const int total = s_off[blk & 1][ATTN_TB];
+            const int n = min(ATTN_LIST, total - sub * ATTN_LIST);
+            int next_blk = blk, next_sub = sub + 1;
+            if ((sub + 1) * ATTN_LIST >= total) {
+                next_blk = blk + 1;
+                next_sub = 0;
             }
-            for (int t = b0 + warp; t < e; t += ATTN_THREADS / 32) {
-                const int c = s_cnt[t];
-                const int o = fill + s_off[t] - s_off[b0];
-                const size_t base = (size_t)qh * P.cap_children + (size_t)(tb + t) * P.tile_rows;
-                for (int i = wl; i < c; i += 32) {
-                    s_idx[o + i] = P.idx[base + i];
-                    s_logit[o + i] = P.score[base + i];
-                }
+            if (next_blk != blk && next_blk < nblk) {
+                scan_counts(next_blk);       // its counts landed before the last barrier
+                __syncthreads();
+                fetch_counts(next_blk + 1);  // into the buffer of block `blk`, whose prefix sums exist
             }
-            fill += s_off[e] - s_off[b0];
-            b0 = e;
-            __syncthreads();
+            if (next_blk < nblk) fetch_entries(next_blk, next_sub, buf ^ 1);
+            if (n > 0) {
+                flush(s_idx[buf], s_logit[buf], n);
+            } else {
+                attn_cp_async_commit();
+                attn_cp_async_wait<0>();
+                __syncthreads();
+            }
+            blk = next_blk;
+            sub = next_sub;
+            buf ^= 1;
         }
     }
 
@@ -206,8 +274,8 @@ sparse_attn_kernel(const AttnParams P) {
         const TK* qk = reinterpret_cast<const TK*>(P.queued_k) + (size_t)h * P.queued_head_stride;
         int j0 = 0;
         while (j0 < P.n_queued) {
-            if (fill == ATTN_CHUNK) flush();
-            const int n = min(P.n_queued - j0, ATTN_CHUNK - fill);
+            const int fill = 0;
+            const int n = min(P.n_queued - j0, ATTN_LIST);
             for (int b = 0; b < n; b += ATTN_HW) {  // uniform trip count
                 const int j = b + hw;
                 Acc2 a2{0.f, 0.f};
@@ -224,15 +292,14 @@ sparse_attn_kernel(const AttnParams P) {
                 }
                 const float d = group_sum(__fadd_rn(a2.e, a2.o));
                 if (lane == 0 && j < n) {
-                    s_idx[fill + j] = QUEUE_FLAG | (j0 + j);
-                    s_logit[fill + j] = __fmul_rn(d, scale);
+                    s_idx[0][fill + j] = QUEUE_FLAG | (j0 + j);
+                    s_logit[0][fill + j] = __fmul_rn(d, scale);
                 }
             }
-            fill += n;
+            flush(s_idx[0], s_logit[0], n);
             j0 += n;
         }
     }
-    if (fill > 0) flush();
 
     // ---- combine the groups ----------------------------------------------------
     __syncthreads();
@@ -312,17 +379,31 @@ __global__ void merge_kernel(const float* __restrict__ part_o, const float* __re
     }
 }
 
-template <typename TK, typename TV>
-static int launch_attn(const AttnParams& P, cudaStream_t s) {
+template <typename TK, typename TV, int NCH, int NVCH>
+static int launch_attn_n(const AttnParams& P, cudaStream_t s) {
+    auto kern = sparse_attn_kernel<TK, TV, NCH, NVCH>;
     dim3 grid((unsigned)P.n_splits, (unsigned)P.n_qheads);
-    const size_t smem = (size_t)ATTN_HW * P.vdim * sizeof(float);
-    const bool k2 = P.dim > 128, v2 = P.vdim > 128;   // chunks per lane: 2 up to 128 elements, else 4
-    if (!k2 && !v2) sparse_attn_kernel<TK, TV, 2, 2><<<grid, ATTN_THREADS, smem, s>>>(P);
-    else if (k2 && !v2) sparse_attn_kernel<TK, TV, 4, 2><<<grid, ATTN_THREADS, smem, s>>>(P);
-    else if (!k2 && v2) sparse_attn_kernel<TK, TV, 2, 4><<<grid, ATTN_THREADS, smem, s>>>(P);
-    else sparse_attn_kernel<TK, TV, 4, 4><<<grid, ATTN_THREADS, smem, s>>>(P);
+    size_t smem = (size_t)ATTN_HW * P.vdim * sizeof(float);   // the final combine, in the ring's place
+    if (smem < (size_t)GatherRing<TV, NVCH>::BYTES) smem = GatherRing<TV, NVCH>::BYTES;
+    if (smem + 20 * 1024 > 48 * 1024) {   // static shared memory (lists, counts) comes on top
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            set_error("hira_sparse_attn: cudaFuncSetAttribute(%zu B smem): %s", smem, cudaGetErrorString(e));
+            return HIRA_ERR_CUDA;
+        }
+    }
+    kern<<<grid, ATTN_THREADS, smem, s>>>(P);
     HIRA_CHECK_LAUNCH("hira_sparse_attn launch");
     return HIRA_OK;
+}
+
+template <typename TK, typename TV>
+static int launch_attn(const AttnParams& P, cudaStream_t s) {
+    const bool k2 = P.dim > 128, v2 = P.vdim > 128;   // chunks per lane: 2 up to 128 elements, else 4
+    if (!k2 && !v2) return launch_attn_n<TK, TV, 2, 2>(P, s);
+    if (k2 && !v2) return launch_attn_n<TK, TV, 4, 2>(P, s);
+    if (!k2 && v2) return launch_attn_n<TK, TV, 2, 4>(P, s);
+    return launch_attn_n<TK, TV, 4, 4>(P, s);
 }
 
 }  // namespace hira
@@ -360,8 +441,7 @@ extern "C" int hira_sparse_attn(const hira_index_t* ix, const float* q, const fl
                    n_qheads, n_splits);
     HIRA_CHECK_ARG(q2kv || n_qheads % ix->n_heads == 0, HIRA_ERR_SHAPE,
                    "hira_sparse_attn: n_qheads=%d not divisible by n_heads=%d and no q2kv given", n_qheads, ix->n_heads);
-    HIRA_CHECK_ARG(tile_parents >= 1 && (long long)tile_parents * ix->bf <= ATTN_CHUNK, HIRA_ERR_SHAPE,
-                   "hira_sparse_attn: tile of %d parents x bf %d exceeds %d rows", tile_parents, ix->bf, ATTN_CHUNK);
+    HIRA_CHECK_ARG(tile_parents >= 1, HIRA_ERR_SHAPE, "hira_sparse_attn: tile_parents=%d", tile_parents);
     HIRA_CHECK_ARG(n_queued >= 0, HIRA_ERR_SHAPE, "hira_sparse_attn: n_queued=%d", n_queued);
     if (n_queued > 0) {
         HIRA_CHECK_ARG(q && queued_k && queued_v, HIRA_ERR_ARG,

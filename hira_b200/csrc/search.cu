@@ -378,7 +378,6 @@ search_kernel(const SearchParams P) {
                 }
             }
         };
-#pragma unroll
         // sq - 2 x.c of a parent row against the new key: the score the append's nearest-parent
         // search minimises, in the same arithmetic (chunk order, 8-lane tree)
         auto scan_score = [&](const RawChunk<T> (&raw)[NCH], float sq) -> float {

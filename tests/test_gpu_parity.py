@@ -280,6 +280,51 @@ def test_sparse_attention_matches_oracle(h, n, d, bf, depth, dtype, group, n_que
     np.testing.assert_allclose(got_ml[:, 1], want_ml[:, 1], rtol=1e-4)
 
 
+@pytest.mark.parametrize("n_splits", [1, 2])
+def test_attention_over_every_key_equals_dense_softmax(n_splits):
+    """Keep-all threshold: every tile emits all its rows, so a block of tiles overflows the staging
+    list many times over (the chunked path), and the result must be plain softmax attention."""
+    h, n, d, bf, group = 2, 8192, 128, 32, 2
+    st, ox, keys, vals = build_both(h, n, d, bf, 3, torch.bfloat16, seed=43)
+    hq = h * group
+    q = make_queries(hq, d, seed=7)
+    tau = torch.full((hq,), float("-inf"), device="cuda")
+    scaling = torch.full((hq,), 6.0, device="cuda")
+    _, compact = S.search(st, q, tau, scaling=scaling, flags=L.HIRA_GATE_GE | L.HIRA_LEAF_GE, want_compact=True)
+    out = S.sparse_attn(st, q, scaling, compact, n_splits=n_splits)
+    torch.cuda.synchronize()
+    assert int(compact.count.sum()) == hq * n
+    logits = torch.einsum("hnd,hgd->hgn", keys.double(), q.view(h, group, d).double()) * 6.0
+    want = torch.einsum("hgn,hnd->hgd", torch.softmax(logits, dim=-1), vals.double()).reshape(hq, d)
+    err = (out.double() - want).abs().max() / want.abs().max()
+    assert float(err) < 2e-3
+
+
+def test_decode_attention_entry_equals_the_three_calls():
+    h, n, d, bf, group = 2, 2048, 128, 32, 4
+    st, ox, keys, vals = build_both(h, n, d, bf, 3, torch.bfloat16, seed=44)
+    hq = h * group
+    g = torch.Generator().manual_seed(8)
+    q_raw = (torch.randn((hq, d), generator=g) * 3.0).cuda()
+    tau = torch.full((hq,), 0.12, device="cuda")
+    flags = L.HIRA_GATE_GE | L.HIRA_LEAF_GE
+    q_hat, ls = S.prepare_query(q_raw, d ** -0.5)
+    _, ca = S.search(st, q_hat, tau, scaling=ls, flags=flags, want_compact=True)
+    n_splits = S.attn_splits(st, hq, ca.tile_parents)
+    ws = torch.empty((hq * n_splits * (d + 2),), device="cuda")
+    out_a = S.sparse_attn(st, q_hat, ls, ca, n_splits=n_splits, workspace=ws)
+    cb = S.alloc_compact(st, hq)
+    qh2, ls2 = torch.empty_like(q_hat), torch.empty_like(ls)
+    out_b = torch.empty_like(out_a)
+    S.decode_attention(st, q_raw, d ** -0.5, tau, cb, qh2, ls2, flags=flags, n_splits=n_splits,
+                       workspace=torch.empty_like(ws), out=out_b)
+    torch.cuda.synchronize()
+    assert torch.equal(q_hat, qh2) and torch.equal(ls, ls2)
+    assert torch.equal(ca.count, cb.count) and torch.equal(out_a, out_b)
+    la, lb = ca.to_lists(), cb.to_lists()
+    assert all(torch.equal(x[0], y[0]) and torch.equal(x[1], y[1]) for x, y in zip(la, lb))
+
+
 def test_attention_with_nothing_selected_is_zero():
     st, ox, keys, vals = build_both(1, 512, 128, 16, 3, torch.bfloat16, seed=1)
     q = make_queries(2, 128, seed=2)

@@ -265,8 +265,10 @@ def run_ours(args):
     scanned_frac = rows_read / float(n_groups * ctx)
     setup_s = time.time() - t_setup
 
-    # fused: the search scores the parent rows it reads against the key appended right after,
-    # so the append needs no parent scan of its own (four kernels per step instead of five)
+    # fused: the search scores the parent rows it reads against the key appended right after, so
+    # the append needs no parent scan of its own.  With the append running beside the attention
+    # (below) the separate scan is mostly hidden anyway: at batch 16 both ways take the same time,
+    # at the per-GPU share of an 8-GPU run the fused one is 4 % faster (--unfused switches back).
     fused = not args.unfused
     scan = S.new_scan_slots(st)
 
@@ -282,11 +284,42 @@ def run_ours(args):
         else:
             S.append(st, new_k[i].unsqueeze(1), new_v[i].unsqueeze(1))
 
-    def step(i: int):
+    # The append touches neither the compacted lists nor the value rows the attention reads, so
+    # it runs beside the attention on a second stream; the next search waits for both.
+    side = None if args.serial else torch.cuda.Stream(device=dev)
+
+    def step(i: int, ev=None):
         q_hat, tau, lscale, _ = qsets[i % N_QUERY_SETS]
+        main = torch.cuda.current_stream()
+        if ev:
+            ev[0].record()
         search_step(i, q_hat, tau, lscale)
+        if ev:
+            ev[1].record()
+        if side is None:
+            S.sparse_attn(st, q_hat, lscale, compact, n_splits=n_splits, workspace=ws, out=out)
+            if ev:
+                ev[2].record()
+                ev[3].record()
+            append_step(i)
+            if ev:
+                ev[4].record()
+            return
+        searched = torch.cuda.Event()
+        searched.record(main)
+        with torch.cuda.stream(side):
+            side.wait_event(searched)
+            if ev:
+                ev[3].record(side)
+            append_step(i)
+            if ev:
+                ev[4].record(side)
+            appended = torch.cuda.Event()
+            appended.record(side)
         S.sparse_attn(st, q_hat, lscale, compact, n_splits=n_splits, workspace=ws, out=out)
-        append_step(i)
+        if ev:
+            ev[2].record()
+        main.wait_event(appended)
 
     def barrier():
         if dist is not None:
@@ -295,7 +328,7 @@ def run_ours(args):
 
     for i in range(args.warmup):
         step(i)
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
     sampler = ClockSampler(local_rank)
     barrier()
     if rank == 0:
@@ -305,22 +338,14 @@ def run_ours(args):
     host_t0 = time.time()
     t_start.record()
     for j in range(args.steps):
-        i = args.warmup + j
-        q_hat, tau, lscale, _ = qsets[i % N_QUERY_SETS]
-        ev[j][0].record()
-        search_step(i, q_hat, tau, lscale)
-        ev[j][1].record()
-        S.sparse_attn(st, q_hat, lscale, compact, n_splits=n_splits, workspace=ws, out=out)
-        ev[j][2].record()
-        append_step(i)
-        ev[j][3].record()
+        step(args.warmup + j, ev[j])
     t_end.record()
     barrier()
     host_t1 = time.time()
     total_ms = t_start.elapsed_time(t_end)
     search_ms = statistics.mean(ev[j][0].elapsed_time(ev[j][1]) for j in range(args.steps))
     attn_ms = statistics.mean(ev[j][1].elapsed_time(ev[j][2]) for j in range(args.steps))
-    append_ms = statistics.mean(ev[j][2].elapsed_time(ev[j][3]) for j in range(args.steps))
+    append_ms = statistics.mean(ev[j][3].elapsed_time(ev[j][4]) for j in range(args.steps))
     status = int(st.status.item())
     if status:
         raise RuntimeError(f"index capacity exhausted during the bench (status {status})")
@@ -371,7 +396,9 @@ def run_ours(args):
                    "batch": batch, "kv_heads": H_KV, "q_heads": H_Q, "dim": DIM, "context": ctx, "levels": DEPTH,
                    "branching": BF, "keep_frac": KEEP_FRAC, "tau": "exact k-th largest score per query head, set up front",
                    "sharding": f"kv_head x{world}", "l2": "inputs>L2 (keys per GPU >> 126 MB)",
-                   "gate": "ge", "leaf": "ge"},
+                   "gate": "ge", "leaf": "ge",
+                   "step": ("search with the append's parent scan folded in" if fused else "search") + ", then sparse attention "
+                           + ("followed by" if side is None else "and, beside it on a second stream,") + " the 1-key append"},
         "e2e": {"value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]},
         "gpu_launches": args.steps * (1 + (1 if n_splits == 1 else 2) + (1 if fused else 2)),   # search, sparse_attn[, merge][, append_scan], append
         "roofline": {"bound": "hbm", "kernel": "search_kernel", "achieved": achieved, "peak": peak,
@@ -429,8 +456,21 @@ def run_e2e(args, st, qsets, n_groups, group, k2, dev, CUDAIndexer, CUDASearcher
                      searcher=searcher)
     taus = [qs[1] for qs in qsets]
 
+    side = None if args.serial else torch.cuda.Stream(device=dev)
+
     def one(i):
         q = h_q[i % nset].to(dev, non_blocking=True)
+        if side is not None:
+            # the new key / value rows are copied and appended on a second stream, beside the
+            # attention; the append starts when the step's search has finished
+            o = hira_decode_attention(q, co, threshold=taus[i % nset])
+            with torch.cuda.stream(side):
+                k = h_k[i % 4].to(dev, non_blocking=True)
+                v = h_v[i % 4].to(dev, non_blocking=True)
+            idx.update(k, v, stream=side)
+            h_out.copy_(o, non_blocking=True)
+            idx.wait_pending_update()                   # the step ends when the append has landed too
+            return
         # (the scan folded into the search, `append_key=` / `update(scanned=True)`, would put the
         # key's copy in front of the search: through host buffers the plain order is faster)
         o = hira_decode_attention(q, co, threshold=taus[i % nset])
@@ -634,6 +674,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-tc", action="store_true", help="build the index with the CUDA-core assignment")
     ap.add_argument("--dense", action="store_true", help="also time torch SDPA over the full cache")
+    ap.add_argument("--serial", action="store_true", help="append after the attention on one stream instead of beside it")
     ap.add_argument("--unfused", action="store_true",
                     help="separate parent scan in the append instead of the scan folded into the search")
     args = ap.parse_args()

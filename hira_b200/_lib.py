@@ -64,7 +64,7 @@ def _declare(lib):
     lib.hira_sparse_attn.argtypes = [IX, P, P, P, I32, I32, P, P, P, P, P, I32, I64, I32, P, P, P, P]
     lib.hira_decode_attention.restype = C.c_int
     lib.hira_decode_attention.argtypes = [IX, P, I32, C.c_float, P, P, I32, I32, I32, I32, P, P, P, P, P, P, P, I32, I64,
-                                          I32, P, P, P, P, I64, P, P]
+                                          I32, P, P, P, P, I64, P, P, P]
     lib.hira_search_scan.restype = C.c_int
     lib.hira_search_scan.argtypes = [IX, P, P, P, P, I32, I32, I32, P, P, P, P, P, P, I64, P, P]
     lib.hira_append_scanned.restype = C.c_int

@@ -86,6 +86,8 @@ def hira_decode_attention(query: torch.Tensor, cache_output, *, scaling: Optiona
     srch = _attn_searcher(searcher, gate)
     n_q = b * hq
     q2kv, max_group = srch._coerce_q2kv(q_head_to_kv, n_q, st.n_heads, st.device)
+    if hasattr(indexer, "wait_pending_update"):
+        indexer.wait_pending_update()                            # an update still running on a side stream
     st.active_parents = getattr(indexer, "active_parents", 0)   # empty capacity is not visited
     compact = srch._compact
     if compact is None or compact.idx.device != st.device or tuple(compact.idx.shape) != (n_q, st.cap_children):
@@ -117,7 +119,8 @@ def hira_decode_attention(query: torch.Tensor, cache_output, *, scaling: Optiona
             tau = tau.to(device=st.device, dtype=torch.float32).contiguous()
         S.decode_attention(st, q, sm_scale, tau, compact, bufs[0], bufs[1], q2kv=q2kv, max_group=max_group,
                            flags=srch.flags, queued_k=queued_k, queued_v=queued_v, n_splits=n_splits, workspace=ws,
-                           out=out, scan_key=scan_key, scan_out=scan_out)
+                           out=out, scan_key=scan_key, scan_out=scan_out,
+                           searched_event=indexer.searched_event() if hasattr(indexer, "searched_event") else None)
     else:
         q_hat, logit_scale = S.prepare_query(q, sm_scale, bufs[0], bufs[1])
         if threshold is None and threshold_method == "none":
@@ -134,6 +137,9 @@ def hira_decode_attention(query: torch.Tensor, cache_output, *, scaling: Optiona
             raise ValueError(f"threshold must have shape ({n_q},), got {tuple(tau.shape)}")
         S.search(st, q_hat, tau, scaling=logit_scale, q2kv=q2kv, max_group=max_group, flags=srch.flags,
                  compact=compact, scan_key=scan_key, scan_out=scan_out)
+        if hasattr(indexer, "searched_event"):
+            indexer.searched_event()
+            indexer._searched.record(torch.cuda.current_stream(st.device))
         S.sparse_attn(st, q_hat, logit_scale, compact, q2kv=q2kv, queued_k=queued_k, queued_v=queued_v,
                       n_splits=n_splits, workspace=ws, out=out)
     out = out.reshape(b, hq, 1, st.vdim)

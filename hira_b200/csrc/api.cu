@@ -66,7 +66,8 @@ extern "C" int hira_decode_attention(const hira_index_t* index, const void* q, i
                                      const void* queued_k, const void* queued_v, int32_t n_queued,
                                      int64_t queued_head_stride, int32_t n_splits, float* workspace,
                                      float* out, float* out_ml,
-                                     const void* scan_key, int64_t scan_key_stride, uint64_t* scan_out, void* stream) {
+                                     const void* scan_key, int64_t scan_key_stride, uint64_t* scan_out,
+                                     void* searched, void* stream) {
     HIRA_CHECK_ARG(index != nullptr, HIRA_ERR_ARG, "hira_decode_attention: index is NULL");
     HIRA_CHECK_ARG(q && q_hat && logit_scale, HIRA_ERR_ARG, "hira_decode_attention: q, q_hat and logit_scale must not be NULL");
     int rc = hira_prepare_query(q, q_dtype, n_qheads, index->dim, sm_scale, q_hat, logit_scale, stream);
@@ -80,6 +81,13 @@ extern "C" int hira_decode_attention(const hira_index_t* index, const void* q, i
                          nullptr, idx, score, count, nullptr, stream);
     }
     if (rc != HIRA_OK) return rc;
+    if (searched != nullptr) {
+        cudaError_t e = cudaEventRecord(reinterpret_cast<cudaEvent_t>(searched), reinterpret_cast<cudaStream_t>(stream));
+        if (e != cudaSuccess) {
+            hira::set_error("hira_decode_attention: cudaEventRecord: %s", cudaGetErrorString(e));
+            return HIRA_ERR_CUDA;
+        }
+    }
     return hira_sparse_attn(index, q_hat, logit_scale, q2kv, n_qheads, tile_parents, idx, score, count,
                             queued_k, queued_v, n_queued, queued_head_stride, n_splits, workspace, out, out_ml,
                             stream);

@@ -329,7 +329,7 @@ def prepare_query(q: torch.Tensor, sm_scale: float, q_hat=None, logit_scale=None
 def decode_attention(st: IndexState, q: torch.Tensor, sm_scale: float, tau: torch.Tensor, compact: CompactResult,
                      q_hat: torch.Tensor, logit_scale: torch.Tensor, *, q2kv=None, max_group: int = 0, flags: int = 0,
                      queued_k=None, queued_v=None, n_splits: int, workspace: torch.Tensor, out: torch.Tensor,
-                     out_ml=None, scan_key=None, scan_out=None):
+                     out_ml=None, scan_key=None, scan_out=None, searched_event=None):
     """prepare_query + search (compact) + sparse_attn in one library call.  q (H_q, D) fp32/bf16
     contiguous; everything else preallocated by the caller."""
     lib = L.load()
@@ -349,7 +349,7 @@ def decode_attention(st: IndexState, q: torch.Tensor, sm_scale: float, tau: torc
                                    n_queued, qstride, n_splits, L.ptr(workspace), L.ptr(out), L.ptr(out_ml),
                                    L.ptr(scan_key) if scan_out is not None else None,
                                    scan_key.stride(0) if scan_out is not None else 0, L.ptr(scan_out),
-                                   L.current_stream(st.device))
+                                   searched_event, L.current_stream(st.device))
     L.check(rc, "hira_decode_attention")
     compact.n_tiles_active = None if st.active_parents == 0 else -(-st.active_parents // compact.tile_parents)
     return out

@@ -56,6 +56,9 @@ class CUDAIndexer(BaseIndexer):
         self._snapshot = None     # (pinned copy of `used`, event, keys appended when it was taken)
         self._scan_slots = None   # nearest-parent results of a search that scanned for the next update
         self._scan_pending = False
+        self._searched = None     # event recorded right after the latest search of a decode step
+        self._searched_fresh = False
+        self._pending_append = None   # event of an update that ran on a caller's side stream
         self._pinned = None
         self._appended = 0        # keys appended since the build
         self._n_keys = 0
@@ -192,6 +195,23 @@ class CUDAIndexer(BaseIndexer):
             new_cap = max(need_p, st.cap_parents + max(1, st.cap_parents // 2))
         self.state = st.grown(new_cap)
 
+    # ---- updates beside the attention, on a second stream ---------------------
+    def searched_event(self) -> int:
+        """Handle (cudaEvent_t) of the event a decode step records right after its search; an
+        `update(..., stream=side)` that follows starts once that event has fired."""
+        if self._searched is None:
+            self._searched = torch.cuda.Event()
+            self._searched.record(torch.cuda.current_stream(self.state.device))   # creates the CUDA event
+        self._searched_fresh = True
+        return self._searched.cuda_event
+
+    def wait_pending_update(self):
+        """Makes the current stream wait for an update that is still running on a side stream.
+        The searcher and the decode step call this before they touch the index."""
+        if self._pending_append is not None:
+            torch.cuda.current_stream(self.state.device).wait_event(self._pending_append)
+            self._pending_append = None
+
     @torch.no_grad()
     def begin_scanned_update(self, key: torch.Tensor):
         """For the search that precedes `update(key, value, scanned=True)`: the key folded to
@@ -213,12 +233,34 @@ class CUDAIndexer(BaseIndexer):
         return k, self._scan_slots
 
     @torch.no_grad()
-    def update(self, new_keys: torch.Tensor, new_values: Optional[torch.Tensor] = None, scanned: bool = False):
+    def update(self, new_keys: torch.Tensor, new_values: Optional[torch.Tensor] = None, scanned: bool = False,
+               stream: Optional["torch.cuda.Stream"] = None):
         """new_keys (B, H, M, D), new_values optional (B, H, M, V) -- appended one after another.
         `scanned=True` (M == 1): the search that ran just before was given this key
-        (`hira_decode_attention(..., append_key=new_keys)`) and already found its nearest parent."""
+        (`hira_decode_attention(..., append_key=new_keys)`) and already found its nearest parent.
+        `stream`: run the append on this stream, beside the attention of the decode step that was
+        enqueued just before on the current stream: it starts when that step's search has finished
+        (the attention reads nothing the append writes).  `new_keys` / `new_values` must be ready
+        on `stream`; whoever touches the index next waits for the append (`wait_pending_update`)."""
         if self.state is None:
             raise ValueError("Indexer is not built")
+        if stream is not None:
+            cur = torch.cuda.current_stream(self.state.device)
+            if stream != cur:
+                if self._pending_append is not None:
+                    stream.wait_event(self._pending_append)
+                if self._searched is not None and self._searched_fresh:
+                    stream.wait_event(self._searched)
+                else:
+                    stream.wait_stream(cur)     # no decode step to hook on: after everything enqueued so far
+                self._searched_fresh = False
+                with torch.cuda.stream(stream):
+                    self.update(new_keys, new_values, scanned=scanned)
+                    done = torch.cuda.Event()
+                    done.record(stream)
+                self._pending_append = done
+                return self
+        self.wait_pending_update()
         assert new_values is None or new_keys.shape[:3] == new_values.shape[:3]
         if new_keys.ndim != 4:
             raise ValueError(f"new_keys must be (B, H, M, D), got {tuple(new_keys.shape)}")
@@ -293,6 +335,7 @@ class CUDAIndexer(BaseIndexer):
 
     def check_status(self):
         """Raises if an append ran out of pre-allocated slots (reads one word from the device)."""
+        self.wait_pending_update() if self.state is not None else None
         code = int(self.state.status.item())
         if code:
             raise RuntimeError(f"index capacity exhausted during update (status {code}); raise max_context")
@@ -300,6 +343,7 @@ class CUDAIndexer(BaseIndexer):
     @torch.no_grad()
     def rebuild(self):
         """Full rebuild over the keys currently stored (token order), e.g. every N decode steps."""
+        self.wait_pending_update() if self.state is not None else None
         st = self.state
         n = self._n_keys
         keys, values = S.export(st, n)
@@ -313,6 +357,7 @@ class CUDAIndexer(BaseIndexer):
 
     # ---- checkpoint ---------------------------------------------------------
     def state_dict(self) -> dict:
+        self.wait_pending_update() if self.state is not None else None
         d = self.state.state_dict()
         d["meta"].update(n_keys=self._n_keys, parents_bound=self._parents_bound, gp_bound=self._gp_bound)
         return d

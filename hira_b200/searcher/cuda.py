@@ -79,6 +79,8 @@ class CUDASearcher(BaseSearcher):
         st: S.IndexState = getattr(indexer, "state", None)
         if st is None:
             raise ValueError("Indexer is not built: missing children tensor.")
+        if hasattr(indexer, "wait_pending_update"):
+            indexer.wait_pending_update()                            # an update on a side stream
         st.active_parents = getattr(indexer, "active_parents", 0)   # empty capacity is not visited
         q = self._coerce_query(query, st.dim, st.device)
         hq = q.shape[0]

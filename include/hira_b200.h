@@ -269,7 +269,10 @@ int hira_prepare_query(const void* q, int32_t dtype, int32_t n_qheads, int32_t d
  *   q [n_qheads][dim] raw queries in `q_dtype`;  tau [n_qheads] on the scale of q_hat . k;
  *   q_hat [n_qheads][dim], logit_scale [n_qheads]: scratch, left holding the prepared query;
  *   idx/score/count, workspace, out, out_ml, queued_*: as in hira_search / hira_sparse_attn;
- *   scan_key, scan_key_stride, scan_out: as in hira_search_scan, or NULL, 0, NULL. */
+ *   scan_key, scan_key_stride, scan_out: as in hira_search_scan, or NULL, 0, NULL;
+ *   searched: optional cudaEvent_t recorded on `stream` right after the search kernel, so that an
+ *            append on another stream can start while the attention still runs (it must not start
+ *            earlier: the search reads what the append writes). */
 int hira_decode_attention(const hira_index_t* index, const void* q, int32_t q_dtype, float sm_scale,
                           const float* tau, const int32_t* q2kv, int32_t n_qheads, int32_t max_group,
                           int32_t flags, int32_t tile_parents, float* q_hat, float* logit_scale,
@@ -277,7 +280,8 @@ int hira_decode_attention(const hira_index_t* index, const void* q, int32_t q_dt
                           const void* queued_k, const void* queued_v, int32_t n_queued,
                           int64_t queued_head_stride, int32_t n_splits, float* workspace,
                           float* out, float* out_ml,
-                          const void* scan_key, int64_t scan_key_stride, uint64_t* scan_out, void* stream);
+                          const void* scan_key, int64_t scan_key_stride, uint64_t* scan_out,
+                          void* searched, void* stream);
 
 /* Exact k-th largest of the scores in a compacted search output (run
  * hira_search with HIRA_LEAF_CANDIDATES, tau = -inf and scaling = NULL first).

@@ -336,3 +336,35 @@ def test_scanned_update_through_the_public_classes(levels):
         assert x is None and y is None or torch.equal(x, y), name
     with pytest.raises(ValueError):
         b.update(more_k[:, :, :1], more_v[:, :, :1], scanned=True)      # no search scanned for this key
+
+
+def test_update_on_a_side_stream_beside_the_attention():
+    """update(..., stream=side) runs the append while the decode step's attention is still going;
+    index and attention output stay identical to the one-stream order, step after step."""
+    from hira_b200.cache import CacheOutput
+    h, hq, n, d, bf = 2, 4, 4096, 64, 16
+    keys, vals = _keys(h, n, d, 81), _keys(h, n, d, 82)
+    a = CUDAIndexer(3, 1, bf, max_context=n + 64, seed=5).build(keys, vals)
+    b = CUDAIndexer(3, 1, bf, max_context=n + 64, seed=5).build(keys, vals)
+    more_k, more_v = _keys(h, 30, d, 83).cpu().pin_memory(), _keys(h, 30, d, 84).cpu().pin_memory()
+    tau = torch.full((hq,), 0.1, device="cuda")
+    empty = torch.empty((1, h, 0, d), device="cuda")
+    ca = CacheOutput(queued_keys=empty, queued_values=empty, prefill_keys=None, prefill_values=None, indexer=a,
+                     searcher=CUDASearcher(bf))
+    cb = CacheOutput(queued_keys=empty, queued_values=empty, prefill_keys=None, prefill_values=None, indexer=b,
+                     searcher=CUDASearcher(bf))
+    side = torch.cuda.Stream()
+    for i in range(30):
+        q = _query(hq, d, 90 + i)
+        oa = hira_decode_attention(q, ca, threshold=tau)
+        a.update(more_k[:, :, i:i + 1].cuda(), more_v[:, :, i:i + 1].cuda())
+        ob = hira_decode_attention(q, cb, threshold=tau)
+        with torch.cuda.stream(side):
+            k = more_k[:, :, i:i + 1].to("cuda", non_blocking=True)
+            v = more_v[:, :, i:i + 1].to("cuda", non_blocking=True)
+        b.update(k, v, stream=side)
+        assert torch.equal(oa, ob)
+    a.check_status(), b.check_status()
+    for name in a.state.ARRAYS:
+        x, y = getattr(a.state, name), getattr(b.state, name)
+        assert x is None and y is None or torch.equal(x, y), name

@@ -15,7 +15,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libhira_b200.so"
 HIRA_OK = 0
 HIRA_ERR_ARG, HIRA_ERR_SHAPE, HIRA_ERR_DTYPE, HIRA_ERR_CAPACITY, HIRA_ERR_CUDA = -1, -2, -3, -4, -5
 HIRA_F32, HIRA_BF16 = 0, 1
-HIRA_STATUS_PARENTS_FULL, HIRA_STATUS_GP_FULL = 1, 2
+HIRA_STATUS_PARENTS_FULL, HIRA_STATUS_GP_FULL, HIRA_STATUS_ASSIGN_FAILED = 1, 2, 4
 HIRA_GATE_GT, HIRA_GATE_GE = 0x0, 0x1
 HIRA_LEAF_CANDIDATES, HIRA_LEAF_GE, HIRA_LEAF_GT = 0x0, 0x2, 0x4
 HIRA_TAU_SAMPLE_MAX, HIRA_TAU_SAMPLE_MEAN_TOPK, HIRA_TAU_SAMPLE_KTH = 0, 1, 2
@@ -86,7 +86,7 @@ def _declare(lib):
     lib.hira_build_workspace_bytes.restype = SZ
     lib.hira_build_workspace_bytes.argtypes = [IX, I32]
     lib.hira_build.restype = C.c_int
-    lib.hira_build.argtypes = [IX, P, P, I32, I64, I64, I32, P, P, I32, I32, P, SZ, P]
+    lib.hira_build.argtypes = [IX, P, P, I32, I64, I64, I32, P, P, I32, I32, P, P, SZ, P]
     lib.hira_recompute_radii.restype = C.c_int
     lib.hira_recompute_radii.argtypes = [IX, P]
     lib.hira_export.restype = C.c_int

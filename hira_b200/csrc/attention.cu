@@ -12,7 +12,7 @@
 // four rows in flight per thread; softmax is online in fp32.
 #include "common.cuh"
 #include <math_constants.h>
-#include <stdlib.h>
+#include <atomic>
 
 namespace hira {
 
@@ -180,7 +180,12 @@ sparse_attn_kernel(const AttnParams P) {
                 }
             }
         }
-        attn_cp_async_wait<0>();  // also the copies other stages slipped into the ring's groups
+        // The prefetches of the next list and of the next counts were issued without a group of
+        // their own: they ride in the ring's groups above.  When the ring did not run (every staged
+        // logit -inf or NaN) nothing has committed them yet, and wait_group only covers committed
+        // groups -- so commit here, unconditionally (an empty group costs nothing).
+        attn_cp_async_commit();
+        attn_cp_async_wait<0>();
         __syncthreads();
     };
 
@@ -415,12 +420,7 @@ extern "C" int hira_attn_default_splits(int32_t n_qheads, int32_t n_tiles) {
     // One wave of CTAs: five 128-thread CTAs fit per SM (96 registers), and a launch that is a
     // little over a whole number of waves pays for a nearly empty last one.  Measured: 64 query
     // heads 41 -> 34 us against the former 16 CTAs/SM target, 512 query heads unchanged.
-    static int factor = 0;   // CTAs per SM aimed for (HIRA_ATTN_SPLIT_FACTOR overrides, for tuning)
-    if (factor == 0) {
-        const char* e = getenv("HIRA_ATTN_SPLIT_FACTOR");
-        factor = e ? atoi(e) : 5;
-        if (factor < 1) factor = 5;
-    }
+    const int factor = 5;   // CTAs per SM aimed for
     int s = (factor * 148) / n_qheads;
     if (s > n_tiles) s = n_tiles;
     if (s > 64) s = 64;
@@ -447,6 +447,10 @@ extern "C" int hira_sparse_attn(const hira_index_t* ix, const float* q, const fl
         HIRA_CHECK_ARG(q && queued_k && queued_v, HIRA_ERR_ARG,
                        "hira_sparse_attn: q, queued_k and queued_v are required when n_queued > 0");
         HIRA_CHECK_ARG(n_queued < QUEUE_FLAG, HIRA_ERR_SHAPE, "hira_sparse_attn: n_queued too large");
+        // one head stride serves queued_k (rows of dim) and queued_v (rows of vdim)
+        HIRA_CHECK_ARG(ix->dim == ix->vdim, HIRA_ERR_SHAPE,
+                       "hira_sparse_attn: queued keys/values need dim == vdim (got %d and %d): the single "
+                       "queued_head_stride applies to both arrays", ix->dim, ix->vdim);
     }
     AttnParams P;
     P.values = ix->values; P.q = q; P.scaling = scaling; P.q2kv = q2kv;
@@ -503,7 +507,9 @@ static __device__ __align__(256) float g_attn_scratch[HIRA_NOALLOC_SCRATCH_FLOAT
 
 namespace {
 constexpr int kMaxDevices = 64;
-float* g_scratch_ptr[kMaxDevices];  // device address of g_attn_scratch per device, 0 = not looked up yet
+// device address of g_attn_scratch per device, null = not looked up yet.  Threads that race on
+// the first call of a device all store the same address; the atomics make that race benign.
+std::atomic<float*> g_scratch_ptr[kMaxDevices];
 
 // In host code `g_attn_scratch` names a host-side shadow of the symbol, not device
 // memory, so the address a kernel can use has to be asked for -- once per device,
@@ -515,16 +521,16 @@ int scratch_for_current_device(float** out) {
         hira::set_error("hira_sparse_attn_noalloc: cudaGetDevice failed or device index %d is out of range", dev);
         return HIRA_ERR_CUDA;
     }
-    if (g_scratch_ptr[dev] == nullptr) {
-        float* p = nullptr;
+    float* p = g_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
         e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_attn_scratch);
         if (e != cudaSuccess || p == nullptr) {
             hira::set_error("hira_sparse_attn_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
             return HIRA_ERR_CUDA;
         }
-        g_scratch_ptr[dev] = p;
+        g_scratch_ptr[dev].store(p, std::memory_order_release);
     }
-    *out = g_scratch_ptr[dev];
+    *out = p;
     return HIRA_OK;
 }
 }  // namespace

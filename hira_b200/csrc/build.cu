@@ -203,13 +203,25 @@ __global__ void gather_centres_kernel(const T* __restrict__ points, long long p_
     for (int e = 0; e < 8; ++e) w[e] = r[e];
 }
 
+// An assignment outside [0, k) -- the tensor-core kernel writes -1 for the points of a CTA whose
+// bounded barrier wait ran out -- must not reach the segment arithmetic below: the point goes to
+// centre 0 at distance 0 (so that every later index stays in range) and the caller is told through
+// the status word.
 __global__ void make_sort_keys_kernel(const int32_t* __restrict__ idx, const float* __restrict__ d2, int n, int k,
-                                      long long total, uint64_t* __restrict__ keys, uint32_t* __restrict__ vals) {
+                                      long long total, uint64_t* __restrict__ keys, uint32_t* __restrict__ vals,
+                                      int32_t* __restrict__ status) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const int h = (int)(i / n);
-    const uint64_t seg = (uint64_t)h * k + (uint32_t)idx[i];
-    keys[i] = (seg << 32) | (uint64_t)__float_as_uint(d2[i]);  // d2 >= 0: bits order like values
+    int c = idx[i];
+    float d = d2[i];
+    if (c < 0 || c >= k || !(d >= 0.f)) {
+        if (status) atomicOr(status, HIRA_STATUS_ASSIGN_FAILED);
+        c = 0;
+        d = 0.f;
+    }
+    const uint64_t seg = (uint64_t)h * k + (uint32_t)c;
+    keys[i] = (seg << 32) | (uint64_t)__float_as_uint(d);  // d >= 0: bits order like values
     vals[i] = (uint32_t)(i - (long long)h * n);
 }
 
@@ -218,8 +230,10 @@ __global__ void segment_starts_kernel(const uint64_t* __restrict__ keys, long lo
                                       int32_t* __restrict__ start) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i > total) return;
-    const long long cur = (i < total) ? (long long)(keys[i] >> 32) : n_seg;
-    const long long prev = (i == 0) ? -1 : (long long)(keys[i - 1] >> 32);
+    long long cur = (i < total) ? (long long)(keys[i] >> 32) : n_seg;
+    long long prev = (i == 0) ? -1 : (long long)(keys[i - 1] >> 32);
+    cur = cur > n_seg ? n_seg : cur;     // `start` has n_seg + 1 entries
+    prev = prev > n_seg ? n_seg : prev;
     for (long long s = prev + 1; s <= cur; ++s) start[s] = (int32_t)i;
 }
 
@@ -555,7 +569,7 @@ static BuildWs carve(const hira_index_t* ix, int n_keys) {
 template <typename T>
 static int build_level(int dtype, const T* points, long long p_head_stride, int n_heads, int n, int k, int bf,
                        int dim, const int32_t* cent_idx, int n_iters, int use_tc, T* cents, char* base,
-                       const BuildWs& w, int32_t* slot, int32_t* fill, cudaStream_t s) {
+                       const BuildWs& w, int32_t* slot, int32_t* fill, int32_t* status, cudaStream_t s) {
     const long long total = (long long)n_heads * n;
     const long long n_seg = (long long)n_heads * k;
     float* csq = reinterpret_cast<float*>(base + w.csq);
@@ -581,7 +595,7 @@ static int build_level(int dtype, const T* points, long long p_head_stride, int 
         int rc = run_assign(dtype, points, p_head_stride, cents, csq, n_heads, n, k, dim, use_tc, a_idx, a_d2, s);
         if (rc != HIRA_OK) return rc;
         const int blocks = (int)((total + 255) / 256);
-        make_sort_keys_kernel<<<blocks, 256, 0, s>>>(a_idx, a_d2, n, k, total, keys_in, vals_in);
+        make_sort_keys_kernel<<<blocks, 256, 0, s>>>(a_idx, a_d2, n, k, total, keys_in, vals_in, status);
         HIRA_CHECK_LAUNCH("sort keys launch");
         size_t cub_bytes = w.cub_bytes;
         cudaError_t e = cub::DeviceRadixSort::SortPairs(base + w.cub, cub_bytes, keys_in, keys_out, vals_in, vals_out,
@@ -609,7 +623,7 @@ template <typename T>
 static int build_impl(const hira_index_t* ix, const void* keys_v, const void* values, int n_keys,
                       long long k_head_stride, long long v_head_stride, int token_base, const int32_t* cent_idx1,
                       const int32_t* cent_idx2, int n_iters, int use_tc, char* base, const BuildWs& w,
-                      cudaStream_t s) {
+                      int32_t* status, cudaStream_t s) {
     const T* keys = reinterpret_cast<const T*>(keys_v);
     const int H = ix->n_heads, bf = ix->bf, dim = ix->dim;
     const int k1 = (n_keys + bf - 1) / bf;
@@ -643,12 +657,12 @@ static int build_impl(const hira_index_t* ix, const void* keys_v, const void* va
     int32_t* fill1 = reinterpret_cast<int32_t*>(base + w.fill1);
     int32_t* fill2 = reinterpret_cast<int32_t*>(base + w.fill2);
     int rc = build_level<T>(ix->dtype, keys, k_head_stride, H, n_keys, k1, bf, dim, cent_idx1, n_iters, use_tc,
-                            cents1, base, w, slot1, fill1, s);
+                            cents1, base, w, slot1, fill1, status, s);
     if (rc != HIRA_OK) return rc;
     const int32_t* slot2_used = nullptr;
     if (ix->depth == 3) {
         rc = build_level<T>(ix->dtype, cents1, (long long)k1 * dim, H, k1, k2, bf, dim, cent_idx2, n_iters, use_tc,
-                            cents2, base, w, slot2, fill2, s);
+                            cents2, base, w, slot2, fill2, status, s);
         if (rc != HIRA_OK) return rc;
         slot2_used = slot2;
         const int chunks = dim / 8;
@@ -702,7 +716,8 @@ extern "C" size_t hira_build_workspace_bytes(const hira_index_t* ix, int32_t n_k
 extern "C" int hira_build(const hira_index_t* ix, const void* keys, const void* values, int32_t n_keys,
                           int64_t k_head_stride, int64_t v_head_stride, int32_t token_base,
                           const int32_t* cent_idx1, const int32_t* cent_idx2, int32_t n_iters,
-                          int32_t use_tensor_cores, void* workspace, size_t workspace_bytes, void* stream) {
+                          int32_t use_tensor_cores, int32_t* status, void* workspace, size_t workspace_bytes,
+                          void* stream) {
     int rc = validate_index(ix, false);
     if (rc != HIRA_OK) return rc;
     HIRA_CHECK_ARG(n_keys >= 0, HIRA_ERR_SHAPE, "hira_build: n_keys=%d", n_keys);
@@ -724,9 +739,9 @@ extern "C" int hira_build(const hira_index_t* ix, const void* keys, const void* 
     char* base = reinterpret_cast<char*>(workspace);
     if (ix->dtype == HIRA_BF16)
         return build_impl<__nv_bfloat16>(ix, keys, values, n_keys, k_head_stride, v_head_stride, token_base, cent_idx1,
-                                         cent_idx2, n_iters, use_tensor_cores, base, w, s);
+                                         cent_idx2, n_iters, use_tensor_cores, base, w, status, s);
     return build_impl<float>(ix, keys, values, n_keys, k_head_stride, v_head_stride, token_base, cent_idx1, cent_idx2,
-                             n_iters, use_tensor_cores, base, w, s);
+                             n_iters, use_tensor_cores, base, w, status, s);
 }
 
 extern "C" int hira_recompute_radii(const hira_index_t* ix, void* stream) {

@@ -12,7 +12,6 @@
 // asynchronous copies, several rows in flight per thread; it is HBM-bound.
 #include "common.cuh"
 #include <math_constants.h>
-#include <stdlib.h>
 
 namespace hira {
 
@@ -801,15 +800,6 @@ static int launch_search(const SearchParams& P, int chunks, cudaStream_t stream)
     return launch_search_fd<T, GT, NCH, STAGES, MINB, false, RPI>(P, chunks, stream);
 }
 
-static int tuning_variant() {
-    static int v = -1;
-    if (v < 0) {
-        const char* e = getenv("HIRA_SEARCH_VARIANT");
-        v = e ? atoi(e) : 0;
-    }
-    return v;
-}
-
 template <typename T, int NCH>
 static int dispatch_gt(const SearchParams& P, int max_group, cudaStream_t stream) {
     int gt = 1;
@@ -818,16 +808,6 @@ static int dispatch_gt(const SearchParams& P, int max_group, cudaStream_t stream
     const int chunks = (max_group + gt - 1) / gt;
     constexpr bool BF = sizeof(T) == 2;
     constexpr int ST = BF ? (NCH == 2 ? 4 : 2) : 2;  // ring = ST * SEARCH_RPI * pieces * 4 KB
-    if constexpr (BF && NCH == 2) {
-      if (gt == 4) {
-        switch (tuning_variant()) {  // prefetch depth / residency of the headline shape
-            case 1: return launch_search<T, 4, NCH, 2, 4, 4>(P, chunks, stream);
-            case 2: return launch_search<T, 4, NCH, 2, 4, 2>(P, chunks, stream);
-            case 3: return launch_search<T, 4, NCH, 8, 4, 1>(P, chunks, stream);
-            default: return launch_search<T, 4, NCH, 4, 4>(P, chunks, stream);
-        }
-      }
-    }
     switch (gt) {
         case 1: return launch_search<T, 1, NCH, ST, 4>(P, chunks, stream);
         case 2: return launch_search<T, 2, NCH, ST, NCH == 4 ? 2 : 4>(P, chunks, stream);

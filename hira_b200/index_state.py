@@ -374,13 +374,14 @@ def build(st: IndexState, keys: torch.Tensor, values: Optional[torch.Tensor], *,
     n = keys.shape[1]
     if values is not None:
         assert values.is_contiguous() and values.dtype == st.vdtype
+    st.status.zero_()
     nbytes = int(lib.hira_build_workspace_bytes(st.struct, n))
     ws = torch.empty((max(nbytes, 1),), dtype=torch.uint8, device=st.device)
     rc = lib.hira_build(st.struct, L.ptr(keys), L.ptr(values), n, n * st.dim,
                         n * st.vdim if values is not None else 0, token_base, L.ptr(cent_idx1), L.ptr(cent_idx2),
-                        n_iters, 1 if use_tensor_cores else 0, L.ptr(ws), nbytes, L.current_stream(st.device))
+                        n_iters, 1 if use_tensor_cores else 0, L.ptr(st.status), L.ptr(ws), nbytes,
+                        L.current_stream(st.device))
     L.check(rc, "hira_build")
-    st.status.zero_()
 
 
 def recompute_radii(st: IndexState):

@@ -39,13 +39,14 @@ class CUDAIndexer(BaseIndexer):
 
     def __init__(self, num_levels, max_iterations: int, branching_factor: int, verbose: bool = False,
                  pad_value: float = DEFAULT_PAD_VALUE, *, max_context: Optional[int] = None,
-                 use_tensor_cores: bool = True, seed: int = 1234):
+                 reserve_worst_case: bool = False, use_tensor_cores: bool = True, seed: int = 1234):
         self.depth = num_levels if isinstance(num_levels, CUDAIndexer.DEPTH) else CUDAIndexer.DEPTH(num_levels)
         self.max_iterations = max_iterations
         self.branching_factor = int(branching_factor)
         self.verbose = verbose
         self.pad_value = pad_value
         self.max_context = max_context
+        self.reserve_worst_case = reserve_worst_case
         self.use_tensor_cores = use_tensor_cores
         self.seed = seed
         self.dim: int = 0
@@ -126,13 +127,20 @@ class CUDAIndexer(BaseIndexer):
         k1 = max(1, -(-n_keys // bf))
         if self.max_context is None:
             return k1
-        # room for max_context keys.  Worst case of the append rule: every appended key finds
+        # Room for max_context keys.  Worst case of the append rule: every appended key finds
         # its nearest parent full and opens a new parent -- and, with three levels, finds its
-        # nearest grandparent full too and opens a whole new grandparent block.
+        # nearest grandparent full too and opens a whole new grandparent block (bf^2 child
+        # slots: 512 KiB of bf16 keys and values at bf = 32, D = 128, per key and head).
+        # `reserve_worst_case` pre-allocates exactly that, so that `update` never reallocates;
+        # otherwise the reserve is what the appended keys need when they pack (one parent per bf
+        # keys, one grandparent per bf parents) plus a few blocks, and `_ensure_capacity` grows
+        # the arrays by half when the device counters show it running short.
         extra = max(self.max_context, n_keys) - n_keys
         if self.depth == CUDAIndexer.DEPTH.THREE_LEVELS:
-            return (-(-k1 // bf) + extra) * bf
-        return k1 + extra
+            spare = extra if self.reserve_worst_case else min(extra, -(-extra // (bf * bf)) + 8)
+            return (-(-k1 // bf) + spare) * bf
+        spare = extra if self.reserve_worst_case else min(extra, -(-extra // bf) + 8 * bf)
+        return k1 + spare
 
     @torch.no_grad()
     def build(self, keys: torch.Tensor, values: Optional[torch.Tensor] = None):
@@ -254,6 +262,9 @@ class CUDAIndexer(BaseIndexer):
                 else:
                     stream.wait_stream(cur)     # no decode step to hook on: after everything enqueued so far
                 self._searched_fresh = False
+                for t in (new_keys, new_values):      # allocated on another stream, consumed on this one
+                    if t is not None and t.is_cuda:
+                        t.record_stream(stream)
                 with torch.cuda.stream(stream):
                     self.update(new_keys, new_values, scanned=scanned)
                     done = torch.cuda.Event()
@@ -337,6 +348,9 @@ class CUDAIndexer(BaseIndexer):
         """Raises if an append ran out of pre-allocated slots (reads one word from the device)."""
         self.wait_pending_update() if self.state is not None else None
         code = int(self.state.status.item())
+        if code & 4:
+            raise RuntimeError("the tensor-core assignment of the build gave up on a bounded wait for some points "
+                               "(status bit HIRA_STATUS_ASSIGN_FAILED); rebuild with use_tensor_cores=False")
         if code:
             raise RuntimeError(f"index capacity exhausted during update (status {code}); raise max_context")
 
@@ -348,7 +362,8 @@ class CUDAIndexer(BaseIndexer):
         n = self._n_keys
         keys, values = S.export(st, n)
         b = self.__class__(self.depth, self.max_iterations, self.branching_factor, self.verbose, self.pad_value,
-                           max_context=self.max_context, use_tensor_cores=self.use_tensor_cores, seed=self.seed)
+                           max_context=self.max_context, reserve_worst_case=self.reserve_worst_case,
+                           use_tensor_cores=self.use_tensor_cores, seed=self.seed)
         b.build(keys.unsqueeze(0), None if values is None else values.unsqueeze(0))
         self.state, self._parents_bound, self._gp_bound = b.state, b._parents_bound, b._gp_bound
         self._snapshot = None

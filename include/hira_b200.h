@@ -45,9 +45,13 @@ extern "C" {
 #define HIRA_F32 0
 #define HIRA_BF16 1
 
-/* device status word bits written by hira_append */
+/* device status word bits written by hira_append and hira_build */
 #define HIRA_STATUS_PARENTS_FULL 1 /* no free parent slot left for an orphan key */
 #define HIRA_STATUS_GP_FULL 2      /* no free grandparent slot left              */
+#define HIRA_STATUS_ASSIGN_FAILED 4 /* hira_build: the tensor-core assignment gave up on a bounded
+                                       wait for some points (their hira_assign index is -1); the
+                                       build placed them under centre 0, so the index is valid but
+                                       of poor quality: rebuild with use_tensor_cores = 0 */
 
 /* search flags */
 #define HIRA_GATE_GT 0x0          /* keep node iff q.c + r >  tau (reference Triton kernels, kernels/triton_search_kernels.py:49,114,131) */
@@ -144,8 +148,9 @@ int hira_search(const hira_index_t* index, const float* q, const float* tau,
  * logits of queued keys are scaling * (q . k_queued) computed here.
  *
  *   queued_k/queued_v [n_heads][n_queued][dim|vdim] in index dtype/vdtype with
- *            row strides queued_head_stride (elements between heads); may be
- *            NULL when n_queued == 0
+ *            row strides queued_head_stride (elements between heads, the same for
+ *            both arrays: n_queued > 0 therefore requires dim == vdim, else
+ *            HIRA_ERR_SHAPE); may be NULL when n_queued == 0
  *   workspace: n_qheads * n_splits * (vdim + 2) floats of scratch
  *   out      [n_qheads][vdim] fp32, normalised attention output
  *   out_ml   [n_qheads][2] fp32 or NULL: (running max m, denominator l) so that
@@ -309,13 +314,14 @@ int hira_kth_score(const hira_index_t* index, int32_t n_qheads,
  *   radius 0, count 0, slot2token -1.
  *   use_tensor_cores: 1 = tcgen05 assignment GEMM when dtype is bf16 and the
  *          shapes allow it, 0 = CUDA-core fp32 assignment.
+ *   status: device int32 or NULL, OR-ed with HIRA_STATUS_ASSIGN_FAILED (see there).
  */
 size_t hira_build_workspace_bytes(const hira_index_t* index, int32_t n_keys);
 int hira_build(const hira_index_t* index, const void* keys, const void* values,
                int32_t n_keys, int64_t k_head_stride, int64_t v_head_stride,
                int32_t token_base, const int32_t* cent_idx1,
                const int32_t* cent_idx2, int32_t n_iters,
-               int32_t use_tensor_cores, void* workspace,
+               int32_t use_tensor_cores, int32_t* status, void* workspace,
                size_t workspace_bytes, void* stream);
 
 /* Radii recomputed from the layout (indexer/cuda.py:114-198): parent radius =
@@ -334,6 +340,8 @@ int hira_export(const hira_index_t* index, int32_t token_base, int32_t n_out,
  * torch.cdist + argmin at indexer/cuda.py:244-245): for each point the index
  * of the centroid minimising ||c||^2 - 2 x.c (ties -> lowest index) and that
  * minimum plus ||x||^2 clamped at 0 (squared distance).
+ *   With use_tensor_cores, a CTA whose bounded wait on its copy / MMA barriers runs out writes
+ *   out_idx = -1 (and distance 0) for its 128 points instead of hanging: check for it.
  *   points [n_heads][n][dim], cents [n_heads][k][dim] in `dtype` (dense);
  *   csq_scratch: n_heads*k floats of scratch (receives ||c||^2). */
 int hira_assign(const void* points, const void* cents, int32_t dtype,

@@ -225,7 +225,8 @@ def gen_cpu_search(out: Path):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    ap.add_argument("--ref", default=os.environ.get("HIRA_REFERENCE"), required="HIRA_REFERENCE" not in os.environ,
+                    help="path of the reference checkout (or set HIRA_REFERENCE)")
     ap.add_argument("--out", default=str(HERE))
     a = ap.parse_args()
     setup_reference(Path(a.ref))

@@ -270,7 +270,7 @@ def test_active_bound_skips_empty_capacity_without_changing_results(levels):
     from hira_b200.cache import CacheOutput
     h, hq, n, d, bf = 2, 4, 2048, 64, 8
     keys, vals = _keys(h, n, d, 41), _keys(h, n, d, 42)
-    ix = CUDAIndexer(levels, 1, bf, max_context=n + 4096).build(keys, vals)
+    ix = CUDAIndexer(levels, 1, bf, max_context=n + 4096, reserve_worst_case=True).build(keys, vals)
     more_k, more_v = _keys(h, 24, d, 43), _keys(h, 24, d, 44)
     for i in range(24):
         ix.update(more_k[:, :, i:i + 1], more_v[:, :, i:i + 1])

@@ -9,7 +9,6 @@ purpose: a run that stops at the first failure has then already run every other 
 """
 import ctypes as C
 
-import numpy as np
 import pytest
 import torch
 
@@ -57,10 +56,10 @@ def test_noalloc_attention_matches_workspace_attention_twice():
         rc, out, ml = _noalloc(st, q, scaling, compact, qk, qv, n_splits)
         torch.cuda.synchronize()
         assert rc == 0, L.load().hira_last_error()
-        a, b = out.cpu().numpy(), ref.cpu().numpy()
-        denom = np.abs(b).max(axis=-1, keepdims=True) + 1e-6
-        assert np.max(np.abs(a - b) / denom) < 2e-3, f"call {call}: outputs differ"
-        np.testing.assert_allclose(ml.cpu().numpy(), ml_ref.cpu().numpy(), rtol=1e-5, atol=1e-6)
+        # both entry points launch the same kernels in the same order; only the address of the
+        # partials differs, so the results are the same bits
+        assert torch.equal(out, ref), f"call {call}: outputs differ"
+        assert torch.equal(ml, ml_ref), f"call {call}: (max, denominator) differ"
 
 
 def test_noalloc_attention_rejects_oversized_requests():

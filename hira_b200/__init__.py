@@ -5,14 +5,14 @@ sparse attention) as hand-written CUDA for NVIDIA B200 behind the reference's Py
 """
 __version__ = "0.1.0"
 
-from .attention import hira_attention, hira_decode_attention, make_hira_attention, register_hira_attention
+from .attention import HiraDecodeStep, hira_attention, hira_decode_attention, make_hira_attention, register_hira_attention
 from .cache import (THRESHOLD_METHODS, CacheOutput, DeviceMode, HiraCache, HiraCacheLayer, HiraConfig,
                     sample_kth, sample_max, sample_mean_topk)
 from .indexer import BaseIndexer, CUDAIndexer
 from .searcher import BaseSearcher, CUDASearcher
 
 __all__ = [
-    "hira_attention", "hira_decode_attention", "make_hira_attention", "register_hira_attention", "THRESHOLD_METHODS", "CacheOutput", "DeviceMode", "HiraCache",
+    "HiraDecodeStep", "hira_attention", "hira_decode_attention", "make_hira_attention", "register_hira_attention", "THRESHOLD_METHODS", "CacheOutput", "DeviceMode", "HiraCache",
     "HiraCacheLayer", "HiraConfig", "sample_max", "sample_mean_topk", "sample_kth", "BaseIndexer",
     "CUDAIndexer", "BaseSearcher", "CUDASearcher",
 ]

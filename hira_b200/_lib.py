@@ -26,7 +26,8 @@ EXPORTED_SYMBOLS = [
     "hira_append_workspace_bytes",
     "hira_threshold", "hira_kth_score", "hira_prepare_query", "hira_build_workspace_bytes", "hira_build",
     "hira_recompute_radii", "hira_export", "hira_assign", "hira_sparse_attn_noalloc", "hira_decode_attention",
-    "hira_search_scan", "hira_append_scanned",
+    "hira_search_scan", "hira_append_scanned", "hira_step_events_create", "hira_step_events_destroy",
+    "hira_decode_step",
 ]
 NOALLOC_SCRATCH_FLOATS = 1 << 20
 
@@ -41,6 +42,20 @@ class HiraIndexStruct(C.Structure):
         ("parents", C.c_void_p), ("parent_radii", C.c_void_p), ("parent_sqnorm", C.c_void_p),
         ("child_counts", C.c_void_p), ("grand_parents", C.c_void_p), ("gp_radii", C.c_void_p),
         ("gp_sqnorm", C.c_void_p), ("gp_counts", C.c_void_p), ("used", C.c_void_p),
+    ]
+
+
+class HiraStepStruct(C.Structure):
+    """Mirror of hira_step_t."""
+    _fields_ = [
+        ("q_dev", C.c_void_p), ("k_dev", C.c_void_p), ("v_dev", C.c_void_p), ("q_hat", C.c_void_p),
+        ("logit_scale", C.c_void_p), ("tau", C.c_void_p), ("idx", C.c_void_p), ("score", C.c_void_p),
+        ("count", C.c_void_p), ("workspace", C.c_void_p), ("out_dev", C.c_void_p), ("scan", C.c_void_p),
+        ("status", C.c_void_p), ("append_ws", C.c_void_p), ("append_ws_bytes", C.c_size_t),
+        ("tau_samples", C.c_void_p), ("samples_head_stride", C.c_int64),
+        ("n_samples", C.c_int32), ("tau_method", C.c_int32), ("tau_k", C.c_int32),
+        ("n_splits", C.c_int32), ("tile_parents", C.c_int32), ("flags", C.c_int32),
+        ("ev_copied", C.c_void_p), ("ev_searched", C.c_void_p), ("ev_appended", C.c_void_p),
     ]
 
 
@@ -61,18 +76,25 @@ def _declare(lib):
     lib.hira_attn_default_splits.restype = C.c_int
     lib.hira_attn_default_splits.argtypes = [I32, I32]
     lib.hira_sparse_attn.restype = C.c_int
-    lib.hira_sparse_attn.argtypes = [IX, P, P, P, I32, I32, P, P, P, P, P, I32, I64, I32, P, P, P, P]
+    lib.hira_sparse_attn.argtypes = [IX, P, P, P, I32, I32, P, P, P, P, P, I32, I64, I32, P, P, P, I64, I64, P]
     lib.hira_decode_attention.restype = C.c_int
     lib.hira_decode_attention.argtypes = [IX, P, I32, C.c_float, P, P, I32, I32, I32, I32, P, P, P, P, P, P, P, I32, I64,
-                                          I32, P, P, P, P, I64, P, P, P]
+                                          I32, P, P, P, I64, I64, P, I64, P, P, P]
+    ST = C.POINTER(HiraStepStruct)
+    lib.hira_step_events_create.restype = C.c_int
+    lib.hira_step_events_create.argtypes = [ST]
+    lib.hira_step_events_destroy.restype = C.c_int
+    lib.hira_step_events_destroy.argtypes = [ST]
+    lib.hira_decode_step.restype = C.c_int
+    lib.hira_decode_step.argtypes = [IX, ST, P, I32, C.c_float, I32, P, P, P, P, P, P]
     lib.hira_search_scan.restype = C.c_int
     lib.hira_search_scan.argtypes = [IX, P, P, P, P, I32, I32, I32, P, P, P, P, P, P, I64, P, P]
     lib.hira_append_scanned.restype = C.c_int
     lib.hira_append_scanned.argtypes = [IX, P, P, I64, I64, I32, P, P, P]
     lib.hira_sparse_attn_noalloc.restype = C.c_int
-    lib.hira_sparse_attn_noalloc.argtypes = [IX, P, P, P, I32, I32, P, P, P, P, P, I32, I64, I32, P, P, P]
+    lib.hira_sparse_attn_noalloc.argtypes = [IX, P, P, P, I32, I32, P, P, P, P, P, I32, I64, I32, P, P, I64, I64, P]
     lib.hira_merge_partials.restype = C.c_int
-    lib.hira_merge_partials.argtypes = [P, P, I32, I32, I32, P, P, P]
+    lib.hira_merge_partials.argtypes = [P, P, I32, I32, I32, I64, I64, I64, I64, P, P, P]
     lib.hira_append.restype = C.c_int
     lib.hira_append.argtypes = [IX, P, P, I32, I64, I64, I32, P, P, SZ, P]
     lib.hira_append_workspace_bytes.restype = SZ

@@ -192,3 +192,62 @@ def register_hira_attention(hira_config=None, name: str = "hira"):
     except Exception:  # older transformers: no separate mask registry
         pass
     return name
+
+
+class HiraDecodeStep:
+    """One library call per decode step and layer, host buffers in and out (`hira_decode_step`):
+    the query is copied to the device, the threshold taken or found there, the index searched,
+    the selected keys attended, the output copied back, and the token's new key / value appended
+    beside all that on a second stream.  The Python classes above do the same in several calls
+    with device tensors; this is the path for a serving loop that holds its activations in
+    pinned host memory and wants no interpreter work between the launches.
+
+        step = HiraDecodeStep(indexer, n_qheads=B * H_q, threshold_method="sample_mean_topk")
+        step(q_host, out_host, k_host=k, v_host=v)          # (B*H_q, D), (B*H_q, V), (B*H_kv, D) ...
+        step.synchronize()                                   # out_host is ready, the key is indexed
+
+    The indexer must have been built with room for the appends (`max_context`): the step never
+    reallocates."""
+
+    def __init__(self, indexer, n_qheads: int, *, q_dtype: torch.dtype = torch.float32, gate: str = "ge",
+                 scaling: Optional[float] = None, threshold_method: str = "sample_mean_topk", sample_size: int = 1000,
+                 topk: int = 16, fused_scan: bool = False, side_stream: Optional["torch.cuda.Stream"] = None):
+        st: S.IndexState = indexer.state
+        if st is None:
+            raise ValueError("Indexer is not built")
+        self.indexer = indexer
+        flags = (L.HIRA_GATE_GE | L.HIRA_LEAF_GE) if gate == "ge" else (L.HIRA_GATE_GT | L.HIRA_LEAF_GT)
+        methods = {"sample_max": L.HIRA_TAU_SAMPLE_MAX, "sample_mean_topk": L.HIRA_TAU_SAMPLE_MEAN_TOPK,
+                   "sample_kth": L.HIRA_TAU_SAMPLE_KTH}
+        samples = _samples_for(indexer, sample_size) if threshold_method in methods else None
+        self._step = S.DecodeStep(st, n_qheads, q_dtype, flags=flags, fused_scan=fused_scan, tau_samples=samples,
+                                  tau_method=methods.get(threshold_method, L.HIRA_TAU_SAMPLE_MEAN_TOPK),
+                                  tau_k=1 if samples is None else min(topk, samples.shape[1]))
+        self.sm_scale = float(scaling) if scaling is not None else st.dim ** -0.5
+        self.side = side_stream if side_stream is not None else torch.cuda.Stream(device=st.device)
+
+    def __call__(self, q_host: torch.Tensor, out_host: torch.Tensor, *, threshold: Optional[torch.Tensor] = None,
+                 k_host: Optional[torch.Tensor] = None, v_host: Optional[torch.Tensor] = None):
+        ix = self.indexer
+        st = ix.state
+        if st is not self._step.st:
+            raise RuntimeError("the index was reallocated since this step was created: build it with max_context")
+        ix.wait_pending_update()
+        if k_host is not None:
+            need_g, need_p = ix._gp_bound + 1, ix._parents_bound + 1
+            if (st.depth == 3 and need_g > st.cap_gp) or (st.depth == 2 and need_p > st.cap_parents):
+                ix._tighten_bounds()
+                raise RuntimeError("no pre-allocated room left for this append: raise max_context (or rebuild)")
+            ix._parents_bound += 1          # the append may open a new parent and a new grandparent
+            ix._gp_bound += 1
+        st.active_parents = ix.active_parents
+        self._step.run(q_host, out_host, sm_scale=self.sm_scale, tau=threshold, k_host=k_host, v_host=v_host,
+                       side_stream=self.side)
+        if k_host is not None:
+            ix._n_keys += 1
+            ix._appended += 1
+            if ix._snapshot is not None or ix._appended % ix.BOUND_REFRESH_EVERY == 0:
+                ix._tighten_bounds()
+
+    def synchronize(self):
+        torch.cuda.current_stream(self.indexer.state.device).synchronize()

@@ -39,6 +39,7 @@ struct AttnParams {
     int n_tiles_active;  // tiles that can hold keys (<= n_tiles, the stride of `count`)
     long long cap_children;
     long long queued_head_stride;
+    long long out_stride, ml_stride;  // elements between the heads' rows of out / out_ml
 };
 
 __device__ __forceinline__ void attn_cp_async_16(uint32_t smem_addr, const void* gmem_src) {
@@ -325,11 +326,11 @@ sparse_attn_kernel(const AttnParams P) {
         for (int d = tid; d < P.vdim; d += ATTN_THREADS) {
             float s = 0.f;
             for (int w = 0; w < ATTN_HW; ++w) s += s_out[(size_t)w * P.vdim + d];
-            P.out[(size_t)qh * P.vdim + d] = L > 0.f ? s / L : 0.f;
+            P.out[(size_t)qh * P.out_stride + d] = L > 0.f ? s / L : 0.f;
         }
         if (tid == 0 && P.out_ml) {
-            P.out_ml[2 * qh] = m;
-            P.out_ml[2 * qh + 1] = L;
+            P.out_ml[(size_t)qh * P.ml_stride] = m;
+            P.out_ml[(size_t)qh * P.ml_stride + 1] = L;
         }
         return;
     }
@@ -355,7 +356,7 @@ __global__ void merge_kernel(const float* __restrict__ part_o, const float* __re
                              long long o_part_stride, long long o_head_stride,
                              long long ml_part_stride, long long ml_head_stride,
                              int n_parts, int vdim, int normalised, float* __restrict__ out,
-                             float* __restrict__ out_ml) {
+                             float* __restrict__ out_ml, long long out_stride, long long out_ml_stride) {
     const int qh = blockIdx.x;
     float M = -CUDART_INF_F;
     for (int s = 0; s < n_parts; ++s)
@@ -376,11 +377,11 @@ __global__ void merge_kernel(const float* __restrict__ part_o, const float* __re
                 o += w * part_o[s * o_part_stride + qh * o_head_stride + d];
             }
         }
-        out[(size_t)qh * vdim + d] = L > 0.f ? o / L : 0.f;
+        out[(size_t)qh * out_stride + d] = L > 0.f ? o / L : 0.f;
     }
     if (out_ml && threadIdx.x == 0) {
-        out_ml[2 * qh] = M;
-        out_ml[2 * qh + 1] = L;
+        out_ml[(size_t)qh * out_ml_stride] = M;
+        out_ml[(size_t)qh * out_ml_stride + 1] = L;
     }
 }
 
@@ -432,7 +433,8 @@ extern "C" int hira_sparse_attn(const hira_index_t* ix, const float* q, const fl
                                 const int32_t* idx, const float* score, const int32_t* count,
                                 const void* queued_k, const void* queued_v, int32_t n_queued,
                                 int64_t queued_head_stride, int32_t n_splits, float* workspace,
-                                float* out, float* out_ml, void* stream) {
+                                float* out, float* out_ml, int64_t out_head_stride, int64_t ml_head_stride,
+                                void* stream) {
     int rc = validate_index(ix, true);
     if (rc != HIRA_OK) return rc;
     HIRA_CHECK_ARG(idx && score && count && workspace && out, HIRA_ERR_ARG,
@@ -466,6 +468,11 @@ extern "C" int hira_sparse_attn(const hira_index_t* ix, const float* q, const fl
     P.n_splits = n_splits; P.n_queued = n_queued;
     P.cap_children = (long long)ix->cap_parents * ix->bf;
     P.queued_head_stride = queued_head_stride;
+    HIRA_CHECK_ARG((out_head_stride == 0 || out_head_stride >= ix->vdim) && (ml_head_stride == 0 || ml_head_stride >= 2),
+                   HIRA_ERR_SHAPE, "hira_sparse_attn: out_head_stride=%lld / ml_head_stride=%lld too small",
+                   (long long)out_head_stride, (long long)ml_head_stride);
+    P.out_stride = out_head_stride ? out_head_stride : ix->vdim;
+    P.ml_stride = ml_head_stride ? ml_head_stride : 2;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (ix->dtype == HIRA_BF16 && ix->vdtype == HIRA_BF16) rc = launch_attn<__nv_bfloat16, __nv_bfloat16>(P, s);
     else if (ix->dtype == HIRA_F32 && ix->vdtype == HIRA_F32) rc = launch_attn<float, float>(P, s);
@@ -475,19 +482,26 @@ extern "C" int hira_sparse_attn(const hira_index_t* ix, const float* q, const fl
     if (n_splits == 1) return HIRA_OK;  // the attention kernel wrote `out` itself
     const long long pstride = ix->vdim + 2;
     merge_kernel<<<n_qheads, 128, 0, s>>>(workspace + 2, workspace, pstride, pstride * n_splits, pstride,
-                                          pstride * n_splits, n_splits, ix->vdim, 0, out, out_ml);
+                                          pstride * n_splits, n_splits, ix->vdim, 0, out, out_ml, P.out_stride,
+                                          P.ml_stride);
     HIRA_CHECK_LAUNCH("hira_sparse_attn merge launch");
     return HIRA_OK;
 }
 
 extern "C" int hira_merge_partials(const float* part_o, const float* part_ml, int32_t n_parts,
-                                   int32_t n_qheads, int32_t vdim, float* out, float* out_ml, void* stream) {
+                                   int32_t n_qheads, int32_t vdim, int64_t o_part_stride, int64_t o_head_stride,
+                                   int64_t ml_part_stride, int64_t ml_head_stride, float* out, float* out_ml,
+                                   void* stream) {
     HIRA_CHECK_ARG(part_o && part_ml && out, HIRA_ERR_ARG, "hira_merge_partials: NULL argument");
     HIRA_CHECK_ARG(n_parts >= 1 && n_qheads >= 1 && vdim >= 1, HIRA_ERR_SHAPE,
                    "hira_merge_partials: n_parts=%d n_qheads=%d vdim=%d", n_parts, n_qheads, vdim);
+    if (o_head_stride == 0) o_head_stride = vdim;
+    if (o_part_stride == 0) o_part_stride = (int64_t)n_qheads * o_head_stride;
+    if (ml_head_stride == 0) ml_head_stride = 2;
+    if (ml_part_stride == 0) ml_part_stride = (int64_t)n_qheads * ml_head_stride;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    merge_kernel<<<n_qheads, 128, 0, s>>>(part_o, part_ml, (long long)n_qheads * vdim, vdim,
-                                          (long long)n_qheads * 2, 2, n_parts, vdim, 1, out, out_ml);
+    merge_kernel<<<n_qheads, 128, 0, s>>>(part_o, part_ml, o_part_stride, o_head_stride, ml_part_stride,
+                                          ml_head_stride, n_parts, vdim, 1, out, out_ml, vdim, 2);
     HIRA_CHECK_LAUNCH("hira_merge_partials launch");
     return HIRA_OK;
 }
@@ -540,7 +554,7 @@ extern "C" int hira_sparse_attn_noalloc(const hira_index_t* ix, const float* q, 
                                         const int32_t* idx, const float* score, const int32_t* count,
                                         const void* queued_k, const void* queued_v, int32_t n_queued,
                                         int64_t queued_head_stride, int32_t n_splits, float* out, float* out_ml,
-                                        void* stream) {
+                                        int64_t out_head_stride, int64_t ml_head_stride, void* stream) {
     HIRA_CHECK_ARG(ix != nullptr, HIRA_ERR_ARG, "hira_sparse_attn_noalloc: index is NULL");
     HIRA_CHECK_ARG(n_qheads >= 1 && n_splits >= 1 && ix->vdim >= 1, HIRA_ERR_SHAPE,
                    "hira_sparse_attn_noalloc: n_qheads=%d n_splits=%d vdim=%d", n_qheads, n_splits, ix->vdim);
@@ -556,5 +570,6 @@ extern "C" int hira_sparse_attn_noalloc(const hira_index_t* ix, const float* q, 
     // every (query head, split) slot of the scratch that the merge reads is written by the
     // attention kernel of this same call first, so nothing has to be cleared
     return hira_sparse_attn(ix, q, scaling, q2kv, n_qheads, tile_parents, idx, score, count, queued_k, queued_v,
-                            n_queued, queued_head_stride, n_splits, scratch, out, out_ml, stream);
+                            n_queued, queued_head_stride, n_splits, scratch, out, out_ml, out_head_stride,
+                            ml_head_stride, stream);
 }

@@ -223,6 +223,8 @@ def attn_splits(st: IndexState, hq: int, tp: Optional[int] = None) -> int:
 
 def sparse_attn(st: IndexState, q, scaling, compact: CompactResult, *, q2kv=None, queued_k=None, queued_v=None,
                 n_splits: Optional[int] = None, workspace=None, out=None, out_ml=None):
+    """`out` / `out_ml` may be strided views (rows of a packed (H_q, 2 + V) message): only the
+    last dimension has to be contiguous."""
     lib = L.load()
     hq = q.shape[0]
     n_splits = n_splits or attn_splits(st, hq, compact.tile_parents)
@@ -243,17 +245,21 @@ def sparse_attn(st: IndexState, q, scaling, compact: CompactResult, *, q2kv=None
                               L.ptr(compact.idx), L.ptr(compact.score), L.ptr(compact.count),
                               L.ptr(queued_k) if n_queued else None, L.ptr(queued_v) if n_queued else None,
                               n_queued, qstride, n_splits, L.ptr(workspace), L.ptr(out), L.ptr(out_ml),
-                              L.current_stream(dev))
+                              out.stride(0), out_ml.stride(0) if out_ml is not None else 0, L.current_stream(dev))
     L.check(rc, "hira_sparse_attn")
     return out
 
 
 def merge_partials(part_o, part_ml, out=None, out_ml=None):
+    """part_o (n_parts, H_q, V), part_ml (n_parts, H_q, 2): any strides with a contiguous last
+    dimension (e.g. two views of one gathered (n_parts, H_q, 2 + V) buffer)."""
     lib = L.load()
     n_parts, hq, vdim = part_o.shape
+    assert part_o.stride(2) == 1 and part_ml.stride(2) == 1
     if out is None:
         out = torch.empty((hq, vdim), dtype=torch.float32, device=part_o.device)
-    rc = lib.hira_merge_partials(L.ptr(part_o), L.ptr(part_ml), n_parts, hq, vdim, L.ptr(out), L.ptr(out_ml),
+    rc = lib.hira_merge_partials(L.ptr(part_o), L.ptr(part_ml), n_parts, hq, vdim, part_o.stride(0), part_o.stride(1),
+                                 part_ml.stride(0), part_ml.stride(1), L.ptr(out), L.ptr(out_ml),
                                  L.current_stream(part_o.device))
     L.check(rc, "hira_merge_partials")
     return out
@@ -347,6 +353,7 @@ def decode_attention(st: IndexState, q: torch.Tensor, sm_scale: float, tau: torc
                                    L.ptr(compact.idx), L.ptr(compact.score), L.ptr(compact.count),
                                    L.ptr(queued_k) if n_queued else None, L.ptr(queued_v) if n_queued else None,
                                    n_queued, qstride, n_splits, L.ptr(workspace), L.ptr(out), L.ptr(out_ml),
+                                   out.stride(0), out_ml.stride(0) if out_ml is not None else 0,
                                    L.ptr(scan_key) if scan_out is not None else None,
                                    scan_key.stride(0) if scan_out is not None else 0, L.ptr(scan_out),
                                    searched_event, L.current_stream(st.device))
@@ -410,3 +417,67 @@ def assign(points: torch.Tensor, cents: torch.Tensor, use_tensor_cores: bool = F
                          1 if use_tensor_cores else 0, L.ptr(csq), L.ptr(idx), L.ptr(d2), L.current_stream(dev))
     L.check(rc, "hira_assign")
     return idx, d2
+
+
+class DecodeStep:
+    """Device scratch and events of `hira_decode_step` for one index: the whole decode step of a
+    layer (query copy, threshold, search, sparse attention, output copy and, beside them on a
+    second stream, the 1-key append) behind one library call with host buffers in and out."""
+
+    def __init__(self, st: IndexState, n_qheads: int, q_dtype: torch.dtype = torch.float32, *, flags: int,
+                 fused_scan: bool = False, tau_samples: Optional[torch.Tensor] = None,
+                 tau_method: int = L.HIRA_TAU_SAMPLE_MEAN_TOPK, tau_k: int = 16):
+        lib = L.load()
+        dev = st.device
+        self.st, self.n_qheads, self.q_dtype = st, n_qheads, q_dtype
+        tp = tile_parents(st)
+        self.compact = alloc_compact(st, n_qheads, tp)
+        # splits sized for the whole capacity: the bound on the slots in use moves from step to step
+        self.n_splits = int(lib.hira_attn_default_splits(n_qheads, n_tiles(st, tp)))
+        f32 = dict(dtype=torch.float32, device=dev)
+        self.q_dev = torch.empty((n_qheads, st.dim), dtype=q_dtype, device=dev)
+        self.k_dev = torch.empty((st.n_heads, st.dim), dtype=st.dtype, device=dev)
+        self.v_dev = torch.empty((st.n_heads, max(st.vdim, 1)), dtype=st.vdtype, device=dev)
+        self.q_hat = torch.empty((n_qheads, st.dim), **f32)
+        self.logit_scale = torch.empty((n_qheads,), **f32)
+        self.tau = torch.empty((n_qheads,), **f32)
+        self.workspace = torch.empty((n_qheads * self.n_splits * (st.vdim + 2),), **f32)
+        self.out_dev = torch.empty((n_qheads, st.vdim), **f32)
+        self.scan = new_scan_slots(st) if fused_scan else None
+        nbytes = int(lib.hira_append_workspace_bytes(st.struct, 1))
+        self.append_ws = torch.empty((max(nbytes, 1),), dtype=torch.uint8, device=dev) if nbytes else None
+        self.tau_samples = tau_samples
+        s = L.HiraStepStruct()
+        for name in ("q_dev", "k_dev", "v_dev", "q_hat", "logit_scale", "tau", "workspace", "out_dev", "scan",
+                     "append_ws", "tau_samples"):
+            setattr(s, name, L.ptr(getattr(self, name)))
+        s.idx, s.score, s.count = L.ptr(self.compact.idx), L.ptr(self.compact.score), L.ptr(self.compact.count)
+        s.status = L.ptr(st.status)
+        s.append_ws_bytes = nbytes
+        if tau_samples is not None:
+            assert tau_samples.dtype == st.dtype and tau_samples.is_contiguous() and tau_samples.shape[0] == st.n_heads
+            s.n_samples, s.samples_head_stride = tau_samples.shape[1], tau_samples.stride(0)
+        s.tau_method, s.tau_k = tau_method, tau_k
+        s.n_splits, s.tile_parents, s.flags = self.n_splits, tp, flags
+        self._struct = s
+        L.check(lib.hira_step_events_create(C.byref(s)), "hira_step_events_create")
+
+    def __del__(self):
+        try:
+            L.load().hira_step_events_destroy(C.byref(self._struct))
+        except Exception:
+            pass
+
+    def run(self, q_host: torch.Tensor, out_host: torch.Tensor, *, sm_scale: float, tau: Optional[torch.Tensor] = None,
+            k_host: Optional[torch.Tensor] = None, v_host: Optional[torch.Tensor] = None, side_stream=None):
+        """q_host (H_q, D), k_host (H_kv, D), v_host (H_kv, V), out_host (H_q, V) fp32: contiguous
+        (pinned) host tensors.  `tau` (H_q,) on the device, or None to find it from the samples."""
+        st = self.st
+        assert q_host.dtype == self.q_dtype and q_host.is_contiguous() and out_host.is_contiguous()
+        rc = L.load().hira_decode_step(st.struct, C.byref(self._struct), q_host.data_ptr(), L.dtype_code(self.q_dtype),
+                                       float(sm_scale), self.n_qheads, L.ptr(tau),
+                                       None if k_host is None else k_host.data_ptr(),
+                                       None if v_host is None else v_host.data_ptr(), out_host.data_ptr(),
+                                       L.current_stream(st.device),
+                                       None if side_stream is None else side_stream.cuda_stream)
+        L.check(rc, "hira_decode_step")

@@ -156,6 +156,9 @@ int hira_search(const hira_index_t* index, const float* q, const float* tau,
  *   out_ml   [n_qheads][2] fp32 or NULL: (running max m, denominator l) so that
  *            shards can be merged with hira_merge_partials
  *   n_splits: CTAs per query head (>= 1); use hira_attn_default_splits()
+ *   out_head_stride / ml_head_stride: floats between the rows of consecutive query heads in
+ *            out / out_ml (0 = dense: vdim and 2), so that both can be written straight into a
+ *            packed [n_qheads][2 + vdim] message of (m, l, out) rows
  */
 int hira_attn_default_splits(int32_t n_qheads, int32_t n_tiles);
 int hira_sparse_attn(const hira_index_t* index, const float* q,
@@ -165,7 +168,8 @@ int hira_sparse_attn(const hira_index_t* index, const float* q,
                      const int32_t* count, const void* queued_k,
                      const void* queued_v, int32_t n_queued,
                      int64_t queued_head_stride, int32_t n_splits,
-                     float* workspace, float* out, float* out_ml, void* stream);
+                     float* workspace, float* out, float* out_ml,
+                     int64_t out_head_stride, int64_t ml_head_stride, void* stream);
 
 /* hira_sparse_attn without a caller workspace.  No counterpart in the reference: it
  * exists for callers that cannot allocate device memory at this point -- a decode
@@ -188,14 +192,19 @@ int hira_sparse_attn_noalloc(const hira_index_t* index, const float* q,
                              const int32_t* count, const void* queued_k,
                              const void* queued_v, int32_t n_queued,
                              int64_t queued_head_stride, int32_t n_splits,
-                             float* out, float* out_ml, void* stream);
+                             float* out, float* out_ml, int64_t out_head_stride,
+                             int64_t ml_head_stride, void* stream);
 
 /* Log-sum-exp merge of partial softmax results (used across sequence shards
  * after an all-gather).  part_o [n_parts][n_qheads][vdim] holds NORMALISED
- * outputs, part_ml [n_parts][n_qheads][2] their (m, l).  Writes the normalised
- * merged output and optionally its (m, l). */
+ * outputs, part_ml [n_parts][n_qheads][2] their (m, l); the four strides (in
+ * floats; 0 = dense) let both point into one gathered buffer of packed
+ * [n_parts][n_qheads][2 + vdim] rows.  Writes the normalised merged output
+ * [n_qheads][vdim] and optionally its (m, l) [n_qheads][2]. */
 int hira_merge_partials(const float* part_o, const float* part_ml,
                         int32_t n_parts, int32_t n_qheads, int32_t vdim,
+                        int64_t o_part_stride, int64_t o_head_stride,
+                        int64_t ml_part_stride, int64_t ml_head_stride,
                         float* out, float* out_ml, void* stream);
 
 /* ------------------------------------------------------------------------- */
@@ -284,9 +293,55 @@ int hira_decode_attention(const hira_index_t* index, const void* q, int32_t q_dt
                           int32_t* idx, float* score, int32_t* count,
                           const void* queued_k, const void* queued_v, int32_t n_queued,
                           int64_t queued_head_stride, int32_t n_splits, float* workspace,
-                          float* out, float* out_ml,
+                          float* out, float* out_ml, int64_t out_head_stride, int64_t ml_head_stride,
                           const void* scan_key, int64_t scan_key_stride, uint64_t* scan_out,
                           void* searched, void* stream);
+
+/* One whole decode step of one layer from HOST buffers, in one call: the copy of the query to the
+ * device, query preparation, the threshold (given, or found on the device from the step's
+ * samples), search, sparse attention, the copy of the output back to the host and -- when k_host
+ * is given -- the 1-key-per-head append, whose host-to-device copies and kernels run on
+ * `side_stream` beside the query copy, the search's tail and the attention (it starts when the
+ * search has finished; the step ends, on `stream`, when both the output copy and the append are
+ * done).  It is the reference's per-token path cache/hira_cache.py:96-153 -> indexer.update,
+ * searcher.search (searcher/cuda.py:56-143) -> attention, without a host round trip between the
+ * launches.  Nothing is allocated; the caller owns the scratch in hira_step_t and creates its
+ * events once with hira_step_events_create.  q_host [n_qheads][dim] in q_dtype, k_host
+ * [n_heads][dim] / v_host [n_heads][vdim] in the index dtypes, out_host [n_qheads][vdim] fp32;
+ * use pinned host memory, or the copies serialise with the host.  Default head grouping only.
+ * The index's active_parents must cover the slots the append may open (see hira_index_t). */
+typedef struct hira_step {
+    void* q_dev;          /* [n_qheads][dim] in q_dtype                                        */
+    void* k_dev;          /* [n_heads][dim] index dtype: the appended key (NULL: never appends) */
+    void* v_dev;          /* [n_heads][vdim] values dtype                                      */
+    float* q_hat;         /* [n_qheads][dim]                                                   */
+    float* logit_scale;   /* [n_qheads]                                                        */
+    float* tau;           /* [n_qheads] scratch for a threshold found on the device, or NULL   */
+    int32_t* idx;         /* compacted search output, as in hira_search                        */
+    float* score;
+    int32_t* count;
+    float* workspace;     /* n_qheads * n_splits * (vdim + 2) floats                           */
+    float* out_dev;       /* [n_qheads][vdim]                                                  */
+    uint64_t* scan;       /* [n_heads] all bits set, or NULL.  Non-NULL folds the append's parent
+                             scan into the search (hira_search_scan): the search then waits for
+                             the key's copy                                                     */
+    int32_t* status;      /* device status word of the appends                                 */
+    void* append_ws;      /* optional hira_append workspace (scan == NULL)                     */
+    size_t append_ws_bytes;
+    const void* tau_samples;      /* [n_heads][n_samples][dim] index dtype, for tau_dev == NULL */
+    int64_t samples_head_stride;  /* elements between the heads' samples                        */
+    int32_t n_samples, tau_method, tau_k;   /* as in hira_threshold                             */
+    int32_t n_splits, tile_parents, flags;  /* as in hira_sparse_attn / hira_search             */
+    void* ev_copied;      /* cudaEvent_t, set by hira_step_events_create                       */
+    void* ev_searched;
+    void* ev_appended;
+} hira_step_t;
+int hira_step_events_create(hira_step_t* step);
+int hira_step_events_destroy(hira_step_t* step);
+int hira_decode_step(const hira_index_t* index, const hira_step_t* step, const void* q_host,
+                     int32_t q_dtype, float sm_scale, int32_t n_qheads, const float* tau_dev,
+                     const void* k_host, const void* v_host, float* out_host, void* stream,
+                     void* side_stream);
 
 /* Exact k-th largest of the scores in a compacted search output (run
  * hira_search with HIRA_LEAF_CANDIDATES, tau = -inf and scaling = NULL first).

@@ -24,33 +24,15 @@ import tempfile
 import types
 from pathlib import Path
 
-os.environ["TRITON_INTERPRET"] = "1"
+if "--gpu" not in sys.argv:
+    os.environ["TRITON_INTERPRET"] = "1"
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parents[1]
 
-FAISS_SHIM = '''
-import numpy as np
-class _Index:
-    def __init__(self, c): self.c = c
-    def search(self, x, k):
-        d = (x * x).sum(1)[:, None] - 2.0 * x @ self.c.T + (self.c * self.c).sum(1)[None, :]
-        i = d.argmin(1)
-        return d[np.arange(len(x)), i][:, None], i[:, None]
-class Kmeans:
-    def __init__(self, d, k, niter=1, verbose=False, gpu=False, seed=0, min_points_per_centroid=1):
-        self.d, self.k, self.niter, self.seed = d, k, niter, seed
-    def train(self, x):
-        rng = np.random.default_rng(self.seed)
-        c = x[rng.choice(len(x), self.k, replace=False)].copy()
-        for _ in range(self.niter):
-            a = _Index(c).search(x, 1)[1][:, 0]
-            for j in range(self.k):
-                m = a == j
-                if m.any(): c[j] = x[m].mean(0)
-        self.centroids = c.astype(np.float32)
-        self.index = _Index(self.centroids)
-'''
+# `faiss` for the reference's CPUIndexer: the Lloyd stand-in of oracle/cpu_index.py, so that the
+# restatement of CPUIndexer there can be pinned against the reference running the same k-means
+FAISS_SHIM = "from oracle.cpu_index import LloydKmeans as Kmeans\n"
 
 
 def setup_reference(ref: Path):
@@ -223,17 +205,202 @@ def gen_cpu_search(out: Path):
         print("wrote", name, "selected", int((outt != 0).sum()), "of", outt.numel())
 
 
+def gen_cpu_indexer_levels(out: Path):
+    """The reference CPUIndexer (build, then update) with the Lloyd stand-in as faiss: pins
+    oracle/cpu_index.py's restatement of everything around the k-means call."""
+    import numpy as np
+    import torch
+    from hira.indexer.cpu import CPUIndexer
+    H, n, D, bf, levels, m = 2, 600, 32, 8, 3, 20
+    rng = np.random.default_rng(77)
+    keys = rng.standard_normal((1, H, n, D)).astype(np.float32)
+    new_keys = rng.standard_normal((1, H, m, D)).astype(np.float32)
+    idx = CPUIndexer(num_levels=levels, branching_factor=bf, max_iterations=3).build(torch.from_numpy(keys))
+    rec = dict(H=H, n=n, D=D, bf=bf, num_levels=levels, max_iterations=3, keys=keys[0], new_keys=new_keys[0])
+
+    def dump(tag):
+        rec[f"{tag}_n_levels"] = len(idx.levels)
+        for l, lev in enumerate(idx.levels):
+            rec[f"{tag}_centers_{l}"] = lev.ball_centers.numpy().copy()
+            rec[f"{tag}_radii_{l}"] = lev.ball_radii.numpy().copy()
+            if lev.child2parent is not None:
+                rec[f"{tag}_c2p_{l}"] = lev.child2parent.numpy().copy()
+    dump("built")
+    idx.update(torch.from_numpy(new_keys))
+    dump("updated")
+    np.savez_compressed(out / "cpu_indexer_levels.npz", **rec)
+    print("wrote cpu_indexer_levels", [lev.size for lev in idx.levels])
+
+
+def _gate_guard_banded_tau(ox, q, q2kv, depth, start_tau, band):
+    """Per query head a threshold with no gate value q.c + r within `band` of it.  Even heads
+    start from `start_tau` (the workload's threshold: on this data every gate passes); odd heads
+    start from the median gate value of their parents, so that the gates do prune there."""
+    import numpy as np
+    tau = np.array(start_tau, np.float32).copy()
+    for qh in range(q.shape[0]):
+        h = int(q2kv[qh])
+        up, ug = int(ox.used[h, 0]), int(ox.used[h, 1])
+        from oracle import oracle as O
+        par = O.as_f32(ox.parents[h, :up]) if ox.parents.dtype != np.float32 else ox.parents[h, :up]
+        gv = [par @ q[qh] + ox.parent_radii[h, :up]]
+        if depth == 3:
+            gp = O.as_f32(ox.grand_parents[h, :ug]) if ox.grand_parents.dtype != np.float32 else ox.grand_parents[h, :ug]
+            gv.append(gp @ q[qh] + ox.gp_radii[h, :ug])
+        if qh % 2 == 1:
+            tau[qh] = np.float32(np.median(gv[0]))
+        gv = np.sort(np.concatenate(gv).astype(np.float64))
+        t = float(tau[qh])
+        while True:
+            i = np.searchsorted(gv, t)
+            near = [abs(gv[j] - t) for j in (i - 1, i) if 0 <= j < len(gv)]
+            if not near or min(near) > band:
+                break
+            t += band
+        tau[qh] = np.float32(t)
+    return tau
+
+
+def gen_triton_search_bf16(out: Path):
+    """The reference's Triton filters (interpreter) on bf16 keys of the decode workload's
+    distribution (RoPE + outlier channels, un-normalised), D = 128, branching 32."""
+    import numpy as np
+    import torch
+    from hira.kernels.triton_search_kernels import (three_level_filter_kernel_v1_batched,
+                                                    two_level_filter_kernel_batched)
+    from hira_b200 import workloads as W
+    from oracle import oracle as O
+    D, bf = 128, 32
+    for name, H, G, n, depth in (("search_triton_l2_bf16_d128_bf32", 1, 4, 2048, 2),
+                                 ("search_triton_l3_bf16_d128_bf32", 1, 4, 4096, 3)):
+        keys, vals = W.make_kv(H, n, 300 + depth, "cpu", dist="rope_outlier", dtype=torch.bfloat16)
+        k1 = n // bf
+        ox = O.OracleIndex(n_heads=H, dim=D, vdim=D, bf=bf, depth=depth, cap_parents=k1, dtype=O.HIRA_BF16,
+                           vdtype=O.HIRA_BF16)
+        c1 = W.random_centres(H, n, k1, 5, "cpu")
+        c2 = W.random_centres(H, k1, k1 // bf, 6, "cpu") if depth == 3 else None
+        O.build(ox, keys, vals, cent_idx1=c1, cent_idx2=c2)
+        hq = H * G
+        q = W.make_queries(hq, 9, "cpu", pos=n)
+        q = (q / q.norm(dim=-1, keepdim=True)).numpy()
+        q2kv = np.repeat(np.arange(H), G).astype(np.int64)
+        kf = keys.float().numpy()
+        sc = np.einsum("hgd,hnd->hgn", q.reshape(H, G, D), kf).reshape(hq, n)
+        tau0 = np.sort(sc, axis=-1)[:, n - max(1, n // 50)]          # keeps about 2 %
+        tau = _gate_guard_banded_tau(ox, q, q2kv, depth, tau0, 2e-3)
+        scaling = np.random.default_rng(3).uniform(0.5, 2.0, hq).astype(np.float32)
+        f32 = lambda a: torch.from_numpy(O.as_f32(a).copy())
+        K, P, R = f32(ox.children), f32(ox.parents), torch.from_numpy(ox.parent_radii)
+        qt, tt, st = torch.from_numpy(q), torch.from_numpy(tau), torch.from_numpy(scaling)
+        m = torch.from_numpy(q2kv)
+        outt = torch.zeros((hq, n), dtype=torch.float32)
+        if depth == 2:
+            two_level_filter_kernel_batched[(k1, hq)](
+                K_ptr=K, P_ptr=P, R_ptr=R, q_ptr=qt, q_head_to_kv_ptr=m, out_ptr=outt, t_ptr=tt, scaling_ptr=st,
+                K_h_stride=K.stride(0), K_row_stride=K.stride(1), P_h_stride=P.stride(0), P_row_stride=P.stride(1),
+                R_h_stride=R.stride(0), R_row_stride=R.stride(1), q_h_stride=qt.stride(0), q_d_stride=qt.stride(1),
+                out_h_stride=outt.stride(0), out_row_stride=outt.stride(1), t_h_stride=tt.stride(0),
+                scaling_h_stride=st.stride(0), q2kv_h_stride=m.stride(0), n_cols=D, BLOCK_C=bf, branching_factor=bf)
+        else:
+            P2, R2 = f32(ox.grand_parents), torch.from_numpy(ox.gp_radii)
+            three_level_filter_kernel_v1_batched[(P2.shape[1], hq)](
+                K_ptr=K, P1_ptr=P, R1_ptr=R, P2_ptr=P2, R2_ptr=R2, q_ptr=qt, q_head_to_kv_ptr=m, out_ptr=outt,
+                t_ptr=tt, scaling_ptr=st, K_h_stride=K.stride(0), K_row_stride=K.stride(1), P1_h_stride=P.stride(0),
+                P1_row_stride=P.stride(1), R1_h_stride=R.stride(0), R1_row_stride=R.stride(1),
+                P2_h_stride=P2.stride(0), P2_row_stride=P2.stride(1), R2_h_stride=R2.stride(0),
+                R2_row_stride=R2.stride(1), q_h_stride=qt.stride(0), q_d_stride=qt.stride(1),
+                out_h_stride=outt.stride(0), out_row_stride=outt.stride(1), t_h_stride=tt.stride(0),
+                scaling_h_stride=st.stride(0), q2kv_h_stride=m.stride(0), n_cols=D, branch=bf, BLOCK_C=bf)
+        rec = dict(H=H, n=n, D=D, bf=bf, depth=depth, cap_parents=ox.cap_parents, q=q, tau=tau, scaling=scaling,
+                   q2kv=q2kv.astype(np.int32), keys_bf16=keys.view(torch.int16).numpy(),
+                   cent_idx1=c1.numpy(), expected_mask=np.packbits(outt.numpy() != 0, axis=-1),
+                   expected_sum=outt.numpy().sum(axis=-1))
+        if depth == 3:
+            rec["cent_idx2"] = c2.numpy()
+        np.savez_compressed(out / f"{name}.npz", **rec)
+        print("wrote", name, "emitted", int((outt != 0).sum()), "of", outt.numel())
+
+
+def gen_gpu_reference_search(out: Path):
+    """ON A CUDA DEVICE: the reference's own CUDASearcher (its Triton kernels, compiled for the
+    GPU) on an index this library built from the cfg1 and cfg4 workloads -- 8 KV heads, bf16,
+    D = 128; 32,768 keys / branching 32 / 32 query heads and 131,072 keys / branching 64 / 64
+    query heads.  The reference searcher sees fp32 copies of the index arrays through an object
+    with the attribute names of its CUDAIndexer.  The data is generated on the device from
+    seeds; the fixture keeps checksums of it, the thresholds and the candidate bitmaps."""
+    import hashlib
+    import numpy as np
+    import torch
+    from hira.searcher.cuda import CUDASearcher as RefSearcher
+    from hira.indexer.cuda import CUDAIndexer as RefIndexer
+    from hira_b200 import _lib as L
+    from hira_b200 import index_state as S
+    from hira_b200 import workloads as W
+    from oracle import oracle as O
+    dev = torch.device("cuda", 0)
+    for tag, w in (("cfg1", W.CFG1), ("cfg4", W.CFG4)):
+        H, n, D, bf, G = w.kv_heads, w.context, W.DIM, w.branching, w.group
+        keys, vals, q = W.make_inputs(w, dev)
+        k1, k2 = n // bf, n // bf // bf
+        st = S.IndexState(n_heads=H, dim=D, vdim=D, bf=bf, depth=3, cap_parents=k1, dtype=torch.bfloat16,
+                          vdtype=torch.bfloat16, device=dev)
+        c1 = W.random_centres(H, n, k1, 7, dev)
+        c2 = W.random_centres(H, k1, k2, 8, dev)
+        S.build(st, keys, vals, cent_idx1=c1, cent_idx2=c2, n_iters=1, use_tensor_cores=False)
+        torch.cuda.synchronize()
+        hq = H * G
+        q_hat = (q / q.norm(dim=-1, keepdim=True)).contiguous()
+        ox = O.OracleIndex.from_arrays(st.state_dict())
+        sc = torch.einsum("hgd,hnd->hgn", q_hat.view(H, G, D), keys.float()).reshape(hq, n)
+        tau0 = torch.sort(sc, dim=-1).values[:, n - w.kth].cpu().numpy()
+        q2kv = np.repeat(np.arange(H), G)
+        tau = _gate_guard_banded_tau(ox, q_hat.cpu().numpy(), q2kv, 3, tau0, 2e-3)
+
+        class View:
+            pass
+        v = View()
+        v.children, v.parents = st.children.float(), st.parents.float()
+        v.parent_radii, v.grand_parents = st.parent_radii, st.grand_parents.float()
+        v.grand_parent_radii = st.gp_radii
+        v.branching_factor, v.depth = bf, RefIndexer.DEPTH.THREE_LEVELS
+        tt = torch.from_numpy(tau).to(dev)
+        dense = RefSearcher(block_c=bf).search(q_hat.view(1, hq, 1, D), tt, v)
+        torch.cuda.synchronize()
+        ref_mask = (dense != 0).cpu().numpy()
+        _, compact = S.search(st, q_hat, tt, flags=L.HIRA_GATE_GT | L.HIRA_LEAF_CANDIDATES, want_compact=True)
+        ours = np.zeros_like(ref_mask)
+        for qh, (slots, _) in enumerate(compact.to_lists()):
+            ours[qh, slots.numpy()] = True
+        sha = lambda t: hashlib.sha256(t.contiguous().view(torch.uint8).cpu().numpy().tobytes()).hexdigest()
+        rec = dict(H=H, n=n, D=D, bf=bf, G=G, tau=tau, keys_sha=sha(keys), children_sha=sha(st.children),
+                   q_sha=sha(q_hat), expected_mask=np.packbits(ref_mask, axis=-1),
+                   candidates=ref_mask.sum(axis=-1).astype(np.int64), equal_when_generated=bool((ours == ref_mask).all()))
+        np.savez_compressed(out / f"search_triton_gpu_{tag}.npz", **rec)
+        print("wrote", f"search_triton_gpu_{tag}", "candidates", int(ref_mask.sum()), "of", ref_mask.size,
+              "ours == reference:", rec["equal_when_generated"], "differing:", int((ours != ref_mask).sum()))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--ref", default=os.environ.get("HIRA_REFERENCE"), required="HIRA_REFERENCE" not in os.environ,
                     help="path of the reference checkout (or set HIRA_REFERENCE)")
     ap.add_argument("--out", default=str(HERE))
+    ap.add_argument("--gpu", action="store_true",
+                    help="run the reference's GPU searcher on a CUDA device (search_triton_gpu_*.npz only)")
     a = ap.parse_args()
-    setup_reference(Path(a.ref))
+    if a.gpu:
+        os.environ.pop("TRITON_INTERPRET", None)
+    setup_reference(Path(a.ref).resolve())
     out = Path(a.out)
+    out.mkdir(parents=True, exist_ok=True)
+    if a.gpu:
+        gen_gpu_reference_search(out)
+        return
     gen_append_and_radii(out)
     gen_triton_search(out)
+    gen_triton_search_bf16(out)
     gen_cpu_search(out)
+    gen_cpu_indexer_levels(out)
 
 
 if __name__ == "__main__":

@@ -368,3 +368,49 @@ def test_update_on_a_side_stream_beside_the_attention():
     for name in a.state.ARRAYS:
         x, y = getattr(a.state, name), getattr(b.state, name)
         assert x is None and y is None or torch.equal(x, y), name
+
+
+@pytest.mark.parametrize("levels,fused", [(3, False), (3, True), (2, False)])
+def test_decode_step_from_host_buffers_equals_the_separate_calls(levels, fused):
+    """HiraDecodeStep (one hira_decode_step call per token: host query in, host output out, the
+    append beside it on a second stream) against hira_decode_attention + update with device
+    tensors: same attention output, same index, step after step; also with the threshold found
+    on the device inside the step."""
+    from hira_b200 import HiraDecodeStep
+    from hira_b200.cache import CacheOutput
+    h, hq, n, d, bf = 2, 8, 4096, 128, 16
+    keys, vals = _keys(h, n, d, 111, torch.bfloat16), _keys(h, n, d, 112, torch.bfloat16)
+    a = CUDAIndexer(levels, 1, bf, max_context=n + 64, reserve_worst_case=True, seed=9).build(keys, vals)
+    b = CUDAIndexer(levels, 1, bf, max_context=n + 64, reserve_worst_case=True, seed=9).build(keys, vals)
+    steps = 12
+    more_k = _keys(h, steps, d, 113, torch.bfloat16)[0].transpose(0, 1).contiguous().cpu().pin_memory()   # (steps, h, d)
+    more_v = _keys(h, steps, d, 114, torch.bfloat16)[0].transpose(0, 1).contiguous().cpu().pin_memory()
+    tau = torch.full((hq,), 0.12, device="cuda")
+    empty = torch.empty((1, h, 0, d), dtype=torch.bfloat16, device="cuda")
+    ca = CacheOutput(queued_keys=empty, queued_values=empty, prefill_keys=None, prefill_values=None, indexer=a,
+                     searcher=CUDASearcher(bf))
+    step = HiraDecodeStep(b, hq, fused_scan=fused)
+    out_host = torch.empty((hq, d), dtype=torch.float32).pin_memory()
+    g = torch.Generator().manual_seed(5)
+    for i in range(steps):
+        q = torch.randn((hq, d), generator=g).pin_memory()
+        oa = hira_decode_attention(q.cuda().view(1, hq, 1, d), ca, threshold=tau)
+        a.update(more_k[i].cuda().view(1, h, 1, d), more_v[i].cuda().view(1, h, 1, d))
+        step(q, out_host, threshold=tau, k_host=more_k[i], v_host=more_v[i])
+        step.synchronize()
+        assert torch.allclose(oa.view(hq, d).cpu(), out_host, rtol=1e-5, atol=1e-6), i
+    a.check_status(), b.check_status()
+    for name in a.state.ARRAYS:
+        x, y = getattr(a.state, name), getattr(b.state, name)
+        assert x is None and y is None or torch.equal(x, y), name
+    # threshold found inside the step: equals sample_mean_topk on the same samples + the given-tau step
+    from hira_b200.attention.hira_attention import _samples_for
+    q = torch.randn((hq, d), generator=g).pin_memory()
+    q_hat = (q / q.norm(dim=-1, keepdim=True)).cuda()
+    tau2 = sample_mean_topk(_samples_for(b, 1000), q_hat, 16)
+    step(q, out_host)
+    step.synchronize()
+    got = out_host.clone()
+    step(q, out_host, threshold=tau2)
+    step.synchronize()
+    assert torch.equal(got, out_host)

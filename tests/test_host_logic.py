@@ -177,7 +177,17 @@ def _gloo_worker(rank, world, port, ret):
     po, pml = gather_partials(o.contiguous(), torch.stack([m, l], dim=1).contiguous())
     merged, _ = O.merge_partials(po.numpy(), pml.numpy())
     full = torch.softmax(logits, dim=1) @ vals
-    ret[rank] = float(np.abs(merged - full.numpy()).max())
+    err = float(np.abs(merged - full.numpy()).max())
+    # the same through the preallocated exchange buffer: the partials are written in place
+    # (strided views of this rank's slice), gathered in place, and read back through strides
+    from hira_b200.parallel import PartialsExchange
+    ex = PartialsExchange(hq, d, "cpu")
+    assert ex.world == world and ex.message_bytes == hq * (d + 2) * 4
+    ex.local_out.copy_(o)
+    ex.local_ml.copy_(torch.stack([m, l], dim=1))
+    buf = ex.all_gather()
+    merged2, _ = O.merge_partials(np.ascontiguousarray(buf[:, :, 2:].numpy()), np.ascontiguousarray(buf[:, :, :2].numpy()))
+    ret[rank] = max(err, float(np.abs(merged2 - full.numpy()).max()))
     dist.destroy_process_group()
 
 

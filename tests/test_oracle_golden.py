@@ -218,3 +218,231 @@ def test_cuda_matches_reference_fixtures(name):
         n = want.shape[1]
         assert np.array_equal(d[:, :n] != 0, want != 0)
         np.testing.assert_allclose(d[:, :n], want, atol=1e-5, rtol=1e-5)
+
+
+# ---------------------------------------------------------------------------------------
+# bf16 keys of the decode workload's distribution, D = 128, branching 32
+# ---------------------------------------------------------------------------------------
+BF16_FIXTURES = ["search_triton_l2_bf16_d128_bf32", "search_triton_l3_bf16_d128_bf32"]
+
+
+def bf16_fixture_index(rec):
+    """The fixture stores the bf16 keys and the initial centres; the oracle's (deterministic)
+    build lays the index out exactly as it did when the fixture was made."""
+    import torch
+    H, n, D, bf, depth = (int(rec[k]) for k in ("H", "n", "D", "bf", "depth"))
+    keys = torch.from_numpy(rec["keys_bf16"]).view(torch.bfloat16)
+    vals = torch.zeros_like(keys)
+    ox = O.OracleIndex(n_heads=H, dim=D, vdim=D, bf=bf, depth=depth, cap_parents=int(rec["cap_parents"]),
+                       dtype=O.HIRA_BF16, vdtype=O.HIRA_BF16)
+    O.build(ox, keys, vals, cent_idx1=rec["cent_idx1"], cent_idx2=rec["cent_idx2"] if depth == 3 else None)
+    return ox, keys, vals
+
+
+@pytest.mark.parametrize("name", BF16_FIXTURES)
+def test_blocked_search_matches_reference_triton_kernels_on_bf16_keys(name):
+    rec = load(name)
+    ox, _, _ = bf16_fixture_index(rec)
+    dense, keep = O.search(ox, rec["q"], rec["tau"], scaling=rec["scaling"], q2kv=rec["q2kv"],
+                           flags=O.GATE_GT | O.LEAF_CANDIDATES)
+    n = int(rec["n"])
+    want = np.unpackbits(rec["expected_mask"], axis=-1)[:, :n].astype(bool)
+    assert np.array_equal(keep[:, :n] != 0, want)
+    np.testing.assert_allclose(dense[:, :n].sum(axis=-1), rec["expected_sum"], rtol=1e-4)
+    per_head = want.sum(axis=-1)
+    assert per_head[0] == n and 0 < per_head[1] < n     # workload threshold: no pruning; median gate: some
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", BF16_FIXTURES)
+def test_cuda_matches_reference_triton_kernels_on_bf16_keys(name):
+    import torch
+    from hira_b200 import _lib as L
+    from hira_b200 import index_state as S
+    rec = load(name)
+    H, n, D, bf, depth = (int(rec[k]) for k in ("H", "n", "D", "bf", "depth"))
+    keys = torch.from_numpy(rec["keys_bf16"]).view(torch.bfloat16).cuda()
+    st = S.IndexState(n_heads=H, dim=D, vdim=D, bf=bf, depth=depth, cap_parents=int(rec["cap_parents"]),
+                      dtype=torch.bfloat16, vdtype=torch.bfloat16, device="cuda")
+    S.build(st, keys, torch.zeros_like(keys), cent_idx1=torch.from_numpy(rec["cent_idx1"]).cuda(),
+            cent_idx2=torch.from_numpy(rec["cent_idx2"]).cuda() if depth == 3 else None, use_tensor_cores=False)
+    q, tau = torch.from_numpy(rec["q"]).cuda(), torch.from_numpy(rec["tau"]).cuda()
+    _, compact = S.search(st, q, tau, scaling=torch.from_numpy(rec["scaling"]).cuda(),
+                          q2kv=torch.from_numpy(rec["q2kv"]).cuda(), flags=L.HIRA_GATE_GT | L.HIRA_LEAF_CANDIDATES,
+                          want_compact=True)
+    torch.cuda.synchronize()
+    want = np.unpackbits(rec["expected_mask"], axis=-1)[:, :n].astype(bool)
+    for qh, (slots, scores) in enumerate(compact.to_lists()):
+        assert np.array_equal(slots.numpy(), np.nonzero(want[qh])[0])
+        np.testing.assert_allclose(float(scores.sum()), rec["expected_sum"][qh], rtol=1e-4)
+
+
+# ---------------------------------------------------------------------------------------
+# the CPU index restatement (oracle/cpu_index.py) against the reference's CPUIndexer
+# ---------------------------------------------------------------------------------------
+def test_cpu_index_restatement_matches_reference_cpu_indexer():
+    from oracle import cpu_index as CI
+    rec = load("cpu_indexer_levels")
+    bf, nl, it = int(rec["bf"]), int(rec["num_levels"]), int(rec["max_iterations"])
+    levels = CI.build_levels(rec["keys"], nl, bf, it)
+
+    def check(tag):
+        assert len(levels) == int(rec[f"{tag}_n_levels"])
+        for l, lv in enumerate(levels):
+            assert np.array_equal(lv["centers"], rec[f"{tag}_centers_{l}"]), (tag, l)
+            np.testing.assert_allclose(lv["radii"], rec[f"{tag}_radii_{l}"], rtol=1e-6, atol=1e-6)
+            if lv["c2p"] is not None:
+                assert np.array_equal(lv["c2p"], rec[f"{tag}_c2p_{l}"]), (tag, l)
+            else:
+                assert f"{tag}_c2p_{l}" not in rec
+    check("built")
+    CI.update_levels(levels, rec["new_keys"], bf, it)
+    check("updated")
+    assert [lv["size"] for lv in levels] == [620, 77, 10]
+
+
+# ---------------------------------------------------------------------------------------
+# the reference's own compiled kernels, run live (oracle/_ref, built from its sources)
+# ---------------------------------------------------------------------------------------
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _two_level_omp():
+    import ctypes as C
+    so = ROOT / "oracle" / "_ref" / "libtwo_level_filter_omp.so"
+    if not so.exists():
+        pytest.skip("oracle/_ref/libtwo_level_filter_omp.so is not built (make -C oracle ref REF=...)")
+    lib = C.CDLL(str(so))
+    lib.two_level_filter_omp.restype = None
+    lib.two_level_filter_omp.argtypes = [C.c_void_p] * 5 + [C.c_int64] * 3 + [C.c_float, C.c_int32]
+    return lib
+
+
+def test_two_level_search_matches_reference_omp_kernel_at_cfg1_width():
+    """benchmark_area/cpu_bench/archive/two_level_filter_omp.cpp is the reference's CPU statement
+    of the Triton two-level rule (skip a parent when dot + r <= t, else write every child's
+    score).  Decode-workload keys, D = 128, branching 32, 32,768 keys of one head."""
+    import torch
+    from hira_b200 import workloads as W
+    lib = _two_level_omp()
+    n, D, bf = 32768, 128, 32
+    keys, vals = W.make_kv(1, n, 41, "cpu", dist="rope_outlier", dtype=torch.float32)
+    ox = O.OracleIndex(n_heads=1, dim=D, vdim=D, bf=bf, depth=2, cap_parents=n // bf)
+    O.build(ox, keys, vals, cent_idx1=W.random_centres(1, n, n // bf, 3, "cpu"))
+    q = W.make_queries(2, 8, "cpu", pos=n)
+    q = (q / q.norm(dim=-1, keepdim=True)).numpy()
+    gates = ox.parents[0] @ q.T + ox.parent_radii[0][:, None]            # (parents, 2)
+    for j, frac in enumerate((0.5, 0.9)):                               # thresholds inside the gate range
+        gv = np.sort(gates[:, j].astype(np.float64))
+        i = int(frac * len(gv))
+        while gv[i + 1] - gv[i] < 1e-3:
+            i += 1
+        t = np.float32(0.5 * (gv[i] + gv[i + 1]))
+        out = np.zeros(n, np.float32)
+        qj = np.ascontiguousarray(q[j])
+        lib.two_level_filter_omp(ox.children.ctypes.data, ox.parents.ctypes.data, ox.parent_radii.ctypes.data,
+                                 qj.ctypes.data, out.ctypes.data, n, n // bf, D, t, bf)
+        dense, keep = O.search(ox, qj[None], np.array([t], np.float32), q2kv=np.zeros(1, np.int32),
+                               flags=O.GATE_GT | O.LEAF_CANDIDATES)
+        assert np.array_equal(keep[0] != 0, out != 0)
+        assert 0 < (out != 0).sum() < n
+        np.testing.assert_allclose(dense[0], out, atol=2e-5, rtol=1e-5)
+
+
+def cfg0_case():
+    """BASELINE configuration 0 whole: fp32, 8 heads x 4,096 keys (per-channel scaled Gaussian),
+    one query per head, 2 levels of branching 64 with 10 k-means iterations; thresholds: the
+    exact 128th largest score per head (a key sits on it) and the midpoint below it."""
+    import torch
+    from hira_b200 import workloads as W
+    from oracle import cpu_index as CI
+    ext = CI.load_reference_kernel(ROOT)
+    if ext is None:
+        pytest.skip("oracle/_ref/hira_torch_ext_v3.so is not built (make -C oracle ref REF=...)")
+    w = W.CFG0
+    keys, vals, q = W.make_inputs(w, "cpu")
+    levels = CI.build_levels(keys.numpy(), w.levels, w.branching, 10)
+    q_hat = (q / q.norm(dim=-1, keepdim=True)).contiguous()
+    sc = torch.einsum("hd,hnd->hn", q_hat, keys)
+    srt = torch.sort(sc, dim=-1, descending=True).values
+    tau_exact = srt[:, w.kth - 1].contiguous()
+    tau_mid = W.guard_banded_tau(sc, w.kth)
+    return ext, levels, keys, vals, q_hat, sc, tau_exact, tau_mid
+
+
+def check_against_reference_cpu_kernel(search_blocked, slot2token, ext, levels, keys, q_hat, sc, tau_exact, tau_mid):
+    """search_blocked(tau) -> per query head (slots, scores) of the blocked index searched with
+    gate >=, leaf >=; compared with the reference kernel's dense token-order output."""
+    from oracle import cpu_index as CI
+    prepared = CI.searcher_inputs(levels)
+    hq = q_hat.shape[0]
+    # (1) midpoint threshold: the sets must be equal
+    want = CI.reference_search(ext, levels, q_hat, tau_mid, prepared=prepared).numpy()
+    got = search_blocked(tau_mid)
+    for qh in range(hq):
+        slots, scores = got[qh]
+        toks = slot2token[qh][slots]
+        assert sorted(toks.tolist()) == np.nonzero(want[qh])[0].tolist()
+        np.testing.assert_allclose(scores, want[qh][toks], atol=1e-4, rtol=1e-5)
+        assert len(toks) == 128
+    # (2) the exact 128th largest score: only keys whose score is within rounding of the
+    # threshold may differ (the reference kernel sums in compiler-chosen SIMD order)
+    want = CI.reference_search(ext, levels, q_hat, tau_exact, prepared=prepared).numpy()
+    got = search_blocked(tau_exact)
+    n_boundary = 0
+    for qh in range(hq):
+        toks = set(slot2token[qh][got[qh][0]].tolist())
+        ref = set(np.nonzero(want[qh])[0].tolist())
+        for t in toks ^ ref:
+            bound = 2.0 ** -20 * float(np.linalg.norm(keys[qh, t]))
+            assert abs(float(sc[qh, t]) - float(tau_exact[qh])) <= bound, (qh, t)
+            n_boundary += 1
+        assert 126 <= len(toks) <= 129
+    return n_boundary
+
+
+def test_cfg0_blocked_search_matches_reference_cpu_kernel():
+    from hira_b200.indexer.convert import blocked_from_levels
+    ext, levels, keys, vals, q_hat, sc, tau_exact, tau_mid = cfg0_case()
+    arrays = blocked_from_levels([lv["centers"] for lv in levels], [lv["radii"] for lv in levels],
+                                 [lv["c2p"] for lv in levels[:-1]], values=vals.numpy())
+    ox = O.OracleIndex.from_arrays(arrays)
+    assert [lv["size"] for lv in levels] == [4096, 64]
+
+    def search_blocked(tau):
+        dense, keep = O.search(ox, q_hat.numpy(), tau.numpy(), flags=O.GATE_GE | O.LEAF_GE)
+        return [(np.nonzero(keep[qh])[0], dense[qh][np.nonzero(keep[qh])[0]]) for qh in range(q_hat.shape[0])]
+    check_against_reference_cpu_kernel(search_blocked, ox.slot2token, ext, levels, keys.numpy(), q_hat, sc.numpy(),
+                                       tau_exact, tau_mid)
+
+
+@pytest.mark.gpu
+def test_cfg0_cuda_search_matches_reference_cpu_kernel():
+    import torch
+    from hira_b200 import _lib as L
+    from hira_b200 import index_state as S
+    from hira_b200.indexer.convert import blocked_from_levels
+    ext, levels, keys, vals, q_hat, sc, tau_exact, tau_mid = cfg0_case()
+    arrays = blocked_from_levels([lv["centers"] for lv in levels], [lv["radii"] for lv in levels],
+                                 [lv["c2p"] for lv in levels[:-1]], values=vals.numpy())
+    m = arrays["meta"]
+    st = S.IndexState(n_heads=m["n_heads"], dim=m["dim"], vdim=m["vdim"], bf=m["bf"], depth=m["depth"],
+                      cap_parents=m["cap_parents"], dtype=torch.float32, vdtype=torch.float32, device="cuda")
+    st.load_arrays(arrays)
+    qd = q_hat.cuda()
+
+    def search_blocked(tau):
+        _, compact = S.search(st, qd, tau.cuda(), flags=L.HIRA_GATE_GE | L.HIRA_LEAF_GE, want_compact=True)
+        torch.cuda.synchronize()
+        return [(a.numpy(), b.numpy()) for a, b in compact.to_lists()]
+    check_against_reference_cpu_kernel(search_blocked, arrays["slot2token"], ext, levels, keys.numpy(), q_hat,
+                                       sc.numpy(), tau_exact, tau_mid)
+    # attention over V of the selected keys (fp32): against softmax over exactly those tokens
+    scaling = torch.full((q_hat.shape[0],), 1.0, device="cuda")
+    _, compact = S.search(st, qd, tau_mid.cuda(), scaling=scaling, flags=L.HIRA_GATE_GE | L.HIRA_LEAF_GE,
+                          want_compact=True)
+    out = S.sparse_attn(st, qd, scaling, compact).cpu()
+    mask = sc >= tau_mid[:, None]
+    w = torch.softmax(torch.where(mask, sc, torch.full_like(sc, float("-inf"))).double(), dim=-1)
+    want = torch.einsum("hn,hnd->hd", w, vals.double()).float()
+    assert float((out - want).abs().max() / want.abs().max()) < 1e-5

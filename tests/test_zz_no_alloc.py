@@ -43,7 +43,7 @@ def _noalloc(st, q, scaling, compact, qk, qv, n_splits):
     rc = lib.hira_sparse_attn_noalloc(st.struct, L.ptr(q), L.ptr(scaling), None, hq, compact.tile_parents,
                                       L.ptr(compact.idx), L.ptr(compact.score), L.ptr(compact.count), L.ptr(qk),
                                       L.ptr(qv), qk.shape[1], qk.shape[1] * st.dim, n_splits, L.ptr(out), L.ptr(ml),
-                                      L.current_stream())
+                                      0, 0, L.current_stream())
     return rc, out, ml
 
 

@@ -2,29 +2,38 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload ("cfg2_b16_ctx131072"): Llama-3-8B-shaped GQA decode, batch 16, 32 query heads /
-8 KV heads, D = 128, bf16, context 131,072; keys/values N(0,1) with RoPE (base 500000)
-applied to the keys by position and 4 outlier channels x8; index 3 levels, branching 32;
-tau set per query head so that 2% of the keys survive (exact k-th largest score, computed
-once at set-up).  The (batch, kv_head) groups are independent and are partitioned across
-the N ranks (no collective on the data path); the timed value is the step time, max over
-ranks, so scaling is strong (the job is fixed).
+Headline workload ("cfg2_b16_ctx131072", hira_b200/workloads.py): Llama-3-8B-shaped GQA decode,
+batch 16, 32 query / 8 KV heads, D = 128, bf16, context 131,072; keys/values N(0,1) with RoPE
+(base 500000) by position on the keys and 4 outlier channels x8; index 3 levels, branching 32;
+tau per query head = the exact 2 % score, set up front.  The (batch, kv_head) groups are
+independent and are dealt to the N ranks (no collective on the data path); the timed value is the
+step time, max over ranks, so scaling is strong (the job is fixed).
 
-One JSON line on stdout from rank 0: `value` = device-timed step, `e2e` = the same step through
-the public classes with host buffers, `roofline` = the search kernel's algorithmic bytes over its
-CUDA-event time against the measured copy bandwidth, `cpu_baseline` = the CPU path on a sample.
-`--impl reference` times the reference's CPU path (its fused_tree_search_v3 kernel built
-from the reference sources into oracle/_ref, else the oracle port) on the host cores on a
-bounded sample of the same workload.
+One JSON line on stdout from rank 0:
+  value       device-timed step (CUDA events, inputs resident in HBM);
+  e2e         the same step through the one-call host-buffer entry (HiraDecodeStep ->
+              hira_decode_step): query and new key/value rows from pinned host memory, output
+              back to the host, every step; median of 5 repeats of the K-step loop;
+  roofline    the search kernel: algorithmic bytes (from the kernel's own counters) over its
+              CUDA-event time, against the measured copy bandwidth;
+  variants    the step with the threshold found on the device inside it (hira_threshold), the
+              search with and without the append's parent scan folded in;
+  dense_attention_us  torch SDPA over the same bf16 cache on the same GPU;
+  secondary   the other configurations: cfg1 (batch 1, 32k: latency regime), cfg3 (streaming
+              appends + rebuilds), cfg4 (sequence shards of 131,072 keys per GPU, NCCL all-gather
+              of the softmax partials + merge, checked against a one-rank recomputation);
+  cpu_baseline  the reference's CPU path on a bounded sample, on this box's host cores.
+`--impl reference` times the reference's CPU path: its fused_tree_search_v3 kernel (built from
+the reference sources into oracle/_ref; else the oracle port) driven exactly as its CPUSearcher
+drives it, on an index laid out as its CPUIndexer lays it out and updated as its `update` does
+(oracle/cpu_index.py restates both; the reference's Python sources do not travel to the GPU box).
 """
 from __future__ import annotations
 
 import argparse
 import json
-import math
 import os
 import statistics
-import subprocess
 import sys
 import time
 from pathlib import Path
@@ -33,19 +42,17 @@ ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-import numpy as np
 import torch
 
-WORKLOAD = "cfg2_b16_ctx131072"
-BATCH, H_KV, H_Q, DIM, CTX, BF, DEPTH = 16, 8, 32, 128, 131072, 32, 3
-KEEP_FRAC = 0.02
-ROPE_BASE = 500000.0
-OUTLIER_CHANNELS = (7, 42, 71, 110)
+from hira_b200 import workloads as W
+
+DIM = W.DIM
 N_QUERY_SETS = 4
-# DRAM bytes (read + write) of one search_kernel launch per (batch, kv head) group of 131,072 keys, from
-# an ncu capture of this bench at --batch 2 (16 groups: dram__bytes_read.sum 559.07 MB,
-# dram__bytes_write.sum 7.25 MB); traffic grows in proportion to the groups a launch covers.
-SEARCH_DRAM_BYTES_PER_GROUP_AT_CTX = (559.073280e6 + 7.247872e6) / 16
+E2E_REPEATS = 5
+# DRAM bytes (read + write) of one search_kernel launch per (batch, kv head) group of 131,072 keys,
+# from an ncu capture of this bench at --batch 2 (16 groups); traffic grows in proportion to the
+# groups a launch covers.  Keyed by kernel variant; None = not captured.
+SEARCH_DRAM_BYTES_PER_GROUP = {"bf16_stream": (559.073280e6 + 7.247872e6) / 16}
 
 
 def peaks():
@@ -54,47 +61,6 @@ def peaks():
         d = json.loads(p.read_text())
         return float(d["hbm_gbs"]), "measured"
     return 6650.0, "fallback"
-
-
-# ----------------------------------------------------------------------------------
-# synthetic data
-# ----------------------------------------------------------------------------------
-def rope_(x: torch.Tensor, positions: torch.Tensor):
-    """Llama half-rotation RoPE, in place on (..., L, D) with positions (L,)."""
-    d = x.shape[-1]
-    inv = 1.0 / (ROPE_BASE ** (torch.arange(0, d, 2, device=x.device, dtype=torch.float32) / d))
-    ang = positions.to(torch.float32)[:, None] * inv[None, :]
-    cos, sin = ang.cos(), ang.sin()
-    x1, x2 = x[..., : d // 2].float(), x[..., d // 2:].float()
-    r1 = x1 * cos - x2 * sin
-    r2 = x2 * cos + x1 * sin
-    x[..., : d // 2] = r1.to(x.dtype)
-    x[..., d // 2:] = r2.to(x.dtype)
-    return x
-
-
-def make_kv(n_groups: int, n: int, seed: int, device, first_pos: int = 0):
-    """keys, values (n_groups, n, D) bf16 on `device`, generated group by group."""
-    g = torch.Generator(device=device)
-    g.manual_seed(seed)
-    keys = torch.empty((n_groups, n, DIM), dtype=torch.bfloat16, device=device)
-    vals = torch.empty((n_groups, n, DIM), dtype=torch.bfloat16, device=device)
-    pos = torch.arange(first_pos, first_pos + n, device=device)
-    for i in range(n_groups):
-        k = torch.randn((n, DIM), generator=g, device=device, dtype=torch.float32)
-        rope_(k, pos)
-        k[:, list(OUTLIER_CHANNELS)] *= 8.0
-        keys[i] = k.to(torch.bfloat16)
-        vals[i] = torch.randn((n, DIM), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
-    return keys, vals
-
-
-def make_queries(n_qheads: int, seed: int, device, pos: int):
-    g = torch.Generator(device=device)
-    g.manual_seed(seed)
-    q = torch.randn((n_qheads, 1, DIM), generator=g, device=device, dtype=torch.float32)
-    rope_(q, torch.tensor([pos], device=device))
-    return q[:, 0, :].contiguous()
 
 
 # ----------------------------------------------------------------------------------
@@ -176,14 +142,433 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------------
+# one decode workload on this rank
+# ----------------------------------------------------------------------------------
+class DecodeBench:
+    """Index, buffers and device loop of one decode workload on one GPU: `n_groups`
+    (batch, kv head) groups of `ctx` keys each, `group` query heads per group."""
+
+    def __init__(self, w: W.Workload, n_groups: int, ctx: int, appends: int, dev, seed_offset: int = 0,
+                 use_tc: bool = True, exchange=None):
+        from hira_b200 import _lib as L
+        from hira_b200 import index_state as S
+        self.L, self.S, self.w, self.dev = L, S, w, dev
+        self.n_groups, self.ctx, self.bf, self.group = n_groups, ctx, w.branching, w.group
+        self.n_qheads = n_groups * w.group
+        bf = w.branching
+        t0 = time.time()
+        keys, vals = W.make_kv(n_groups, ctx, 1000 + w.seed + seed_offset, dev, dist=w.dist, dtype=w.dtype)
+        self.k1 = ctx // bf
+        self.k2 = -(-self.k1 // bf)
+        spare_gp = appends + 16   # worst case every appended key opens a new grandparent block
+        self.st = st = S.IndexState(n_heads=n_groups, dim=DIM, vdim=DIM, bf=bf, depth=w.levels,
+                                    cap_parents=(self.k2 + spare_gp) * bf, dtype=w.dtype, vdtype=w.dtype, device=dev)
+        cent1 = W.random_centres(n_groups, ctx, self.k1, 7 + seed_offset, dev)
+        cent2 = W.random_centres(n_groups, self.k1, self.k2, 8 + seed_offset, dev)
+        torch.cuda.synchronize()
+        t1 = time.time()
+        S.build(st, keys, vals, cent_idx1=cent1, cent_idx2=cent2, n_iters=1, use_tensor_cores=use_tc)
+        torch.cuda.synchronize()
+        self.build_s = time.time() - t1
+        # threshold samples: 1000 stored key rows per head (filled slots are the first ctx of a fresh build)
+        g = torch.Generator(device=dev)
+        g.manual_seed(99 + seed_offset)
+        pick = torch.randint(0, ctx, (1000,), generator=g, device=dev)
+        self.samples = keys[:, pick].contiguous()
+        del keys, vals, cent1, cent2
+        torch.cuda.empty_cache()
+        self.tp = S.tile_parents(st)
+        self.flags = L.HIRA_GATE_GE | L.HIRA_LEAF_GE
+        self.compact = S.alloc_compact(st, self.n_qheads, self.tp)
+        self.appended = 0
+        self._bound()
+        self.n_splits = S.attn_splits(st, self.n_qheads, self.tp)
+        self.ws = torch.empty((self.n_qheads * self.n_splits * (DIM + 2),), dtype=torch.float32, device=dev)
+        self.exchange = exchange
+        if exchange is not None:
+            self.out, self.out_ml = exchange.local_out, exchange.local_ml
+        else:
+            self.out, self.out_ml = torch.empty((self.n_qheads, DIM), dtype=torch.float32, device=dev), None
+        self.sm_scale = DIM ** -0.5
+        self.scan = S.new_scan_slots(st)
+        self.setup_s = time.time() - t0
+        self.qsets = []
+        self.new_k = self.new_v = None
+
+    def _bound(self):
+        # the host's bound on the parent slots in use: every append may open one grandparent block
+        self.st.active_parents = (self.k2 + self.appended) * self.bf
+
+    def make_queries(self, n_sets: int, seed: int, tau=None):
+        """Query sets (unit query, tau, logit scale, raw query); tau = exact w.keep score unless given."""
+        S, L = self.S, self.L
+        kk = torch.full((self.n_qheads,), max(1, int(round(self.w.keep * self.ctx))), dtype=torch.int32, device=self.dev)
+        neg_inf = torch.full((self.n_qheads,), float("-inf"), device=self.dev)
+        for i in range(n_sets):
+            q = W.make_queries(self.n_qheads, seed + 13 * i, self.dev, pos=self.ctx + i)
+            qn = q.norm(dim=-1)
+            q_hat = (q / qn[:, None]).contiguous()
+            if tau is None:
+                S.search(self.st, q_hat, neg_inf, flags=L.HIRA_GATE_GT | L.HIRA_LEAF_CANDIDATES, compact=self.compact, tp=self.tp)
+                t = S.kth_score(self.st, self.compact, kk).clone()
+            else:
+                t = tau
+            self.qsets.append((q_hat, t, (qn * self.sm_scale).contiguous(), q))
+
+    def make_new_keys(self, n: int, seed: int):
+        k, v = W.make_kv(self.n_groups, n, seed, self.dev, dist=self.w.dist, dtype=self.w.dtype, first_pos=self.ctx)
+        self.new_k, self.new_v = k.transpose(0, 1).contiguous(), v.transpose(0, 1).contiguous()   # (steps, groups, D)
+
+    def counters(self):
+        """Traffic counters of one search of query set 0 -> algorithmic bytes of the step."""
+        S = self.S
+        q_hat, tau, lscale, _ = self.qsets[0]
+        stats = S.new_stats(self.n_qheads, self.dev)
+        S.search(self.st, q_hat, tau, scaling=lscale, flags=self.flags, compact=self.compact, stats=stats, tp=self.tp)
+        torch.cuda.synchronize()
+        s = stats.to(torch.int64).sum(dim=0).tolist()
+        rows_read, parents_read, emitted = s[6], s[7], s[5]
+        e = 2 if self.w.dtype == torch.bfloat16 else 4
+        search_bytes = self.n_groups * self.k2 * (DIM * e + 4) + parents_read * (DIM * e + 8) + rows_read * DIM * e
+        attn_bytes = emitted * (DIM * e + 8) + self.n_qheads * DIM * 4
+        append_bytes = self.n_groups * ((self.k1 + self.k2) * (DIM * e + 4) + 2 * DIM * e)
+        return dict(search_bytes=search_bytes, attn_bytes=attn_bytes, append_bytes=append_bytes,
+                    scanned_fraction=rows_read / float(self.n_groups * self.ctx), selected_per_qhead=emitted / self.n_qheads)
+
+    # ---- the step ---------------------------------------------------------------------
+    def step(self, i: int, ev=None, *, fused=True, side=None, tau_in_step=False, append=True, nccl_ev=None):
+        S, L, st = self.S, self.L, self.st
+        q_hat, tau, lscale, _ = self.qsets[i % len(self.qsets)]
+        main = torch.cuda.current_stream()
+        self._bound()
+        if ev:
+            ev[0].record()
+        if tau_in_step:
+            tau = S.threshold(self.samples, q_hat, L.HIRA_TAU_SAMPLE_MEAN_TOPK, 16, out=self.tau_buf)
+        j = i % self.new_k.shape[0] if self.new_k is not None else 0
+        if fused and append:
+            S.search(st, q_hat, tau, scaling=lscale, flags=self.flags, compact=self.compact, tp=self.tp,
+                     scan_key=self.new_k[j], scan_out=self.scan)
+        else:
+            S.search(st, q_hat, tau, scaling=lscale, flags=self.flags, compact=self.compact, tp=self.tp)
+        if ev:
+            ev[1].record()
+
+        def do_append():
+            if fused:
+                S.append_scanned(st, self.new_k[j].unsqueeze(1), self.new_v[j].unsqueeze(1), self.scan)
+            else:
+                S.append(st, self.new_k[j].unsqueeze(1), self.new_v[j].unsqueeze(1))
+            self.appended += 1
+
+        def attend():
+            S.sparse_attn(st, q_hat, lscale, self.compact, n_splits=self.n_splits, workspace=self.ws, out=self.out,
+                          out_ml=self.out_ml)
+            if self.exchange is not None:
+                if nccl_ev:
+                    nccl_ev[0].record()
+                self.exchange.all_gather()
+                self.exchange.merge(out=self.merged)
+                if nccl_ev:
+                    nccl_ev[1].record()
+
+        if not append:
+            attend()
+            if ev:
+                ev[2].record()
+            return
+        if side is None:
+            attend()
+            if ev:
+                ev[2].record()
+                ev[3].record()
+            do_append()
+            if ev:
+                ev[4].record()
+            return
+        # The append touches neither the compacted lists nor the value rows the attention reads, so
+        # it runs beside the attention on a second stream; the next search waits for both.
+        self._searched.record(main)
+        with torch.cuda.stream(side):
+            side.wait_event(self._searched)
+            if ev:
+                ev[3].record(side)
+            do_append()
+            if ev:
+                ev[4].record(side)
+            self._appended_ev.record(side)
+        attend()
+        if ev:
+            ev[2].record()
+        main.wait_event(self._appended_ev)
+
+    def timed_loop(self, steps: int, warmup: int, barrier, first: int = 0, **kw):
+        """W warm-up steps, then K timed steps between barriers; returns ms totals (this rank)."""
+        self._searched, self._appended_ev = torch.cuda.Event(), torch.cuda.Event()
+        self.tau_buf = torch.empty((self.n_qheads,), dtype=torch.float32, device=self.dev)
+        if self.exchange is not None:
+            self.merged = torch.empty((self.n_qheads, DIM), dtype=torch.float32, device=self.dev)
+        for i in range(warmup):
+            self.step(first + i, **kw)
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(steps)]
+        nccl = [[torch.cuda.Event(enable_timing=True) for _ in range(2)] for _ in range(steps)] if self.exchange is not None else None
+        barrier()
+        t_start, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        host_t0 = time.time()
+        t_start.record()
+        for j in range(steps):
+            self.step(first + warmup + j, ev[j], nccl_ev=nccl[j] if nccl else None, **kw)
+        t_end.record()
+        barrier()
+        host_t1 = time.time()
+        has_append = kw.get("append", True)
+        res = dict(total_ms=t_start.elapsed_time(t_end), host=(host_t0, host_t1),
+                   search_ms=statistics.mean(ev[j][0].elapsed_time(ev[j][1]) for j in range(steps)),
+                   attn_ms=statistics.mean(ev[j][1].elapsed_time(ev[j][2]) for j in range(steps)),
+                   append_ms=statistics.mean(ev[j][3].elapsed_time(ev[j][4]) for j in range(steps)) if has_append else 0.0)
+        if nccl:
+            res["exchange_ms"] = statistics.mean(nccl[j][0].elapsed_time(nccl[j][1]) for j in range(steps))
+        status = int(self.st.status.item())
+        if status:
+            raise RuntimeError(f"index capacity exhausted during the bench (status {status})")
+        return res
+
+    def time_search_only(self, reps: int, fused: bool):
+        """Mean search time in us over `reps` launches (no append follows; the scan slot is reset)."""
+        S = self.S
+        q_hat, tau, lscale, _ = self.qsets[0]
+        self._bound()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        tot = 0.0
+        for r in range(reps + 2):
+            a.record()
+            if fused:
+                S.search(self.st, q_hat, tau, scaling=lscale, flags=self.flags, compact=self.compact, tp=self.tp,
+                         scan_key=self.new_k[0], scan_out=self.scan)
+            else:
+                S.search(self.st, q_hat, tau, scaling=lscale, flags=self.flags, compact=self.compact, tp=self.tp)
+            b.record()
+            if fused:
+                self.scan.fill_(-1)
+            torch.cuda.synchronize()
+            if r >= 2:
+                tot += a.elapsed_time(b)
+        return tot / reps * 1e3
+
+    def time_dense(self, reps: int = 5):
+        """torch SDPA over the whole cache of this rank (dense decode attention), same shapes, in ms."""
+        st = self.st
+        k = st.children[:, : self.ctx].unsqueeze(0)     # (1, groups, ctx, D) -- slot order is irrelevant for timing
+        v = st.values[:, : self.ctx].unsqueeze(0)
+        q = torch.randn((1, self.n_qheads, 1, DIM), device=self.dev, dtype=self.w.dtype)
+        f = torch.nn.functional.scaled_dot_product_attention
+        for _ in range(3):
+            f(q, k, v, enable_gqa=True)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            f(q, k, v, enable_gqa=True)
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps
+
+    def snapshot(self):
+        st = self.st
+        names = ("parents", "parent_radii", "parent_sqnorm", "child_counts", "grand_parents", "gp_radii", "gp_sqnorm",
+                 "gp_counts", "used")
+        return {n: getattr(st, n).clone() for n in names if getattr(st, n) is not None}, self.appended
+
+    def restore(self, snap):
+        arrays, appended = snap
+        for n, t in arrays.items():
+            getattr(self.st, n).copy_(t)
+        self.appended = appended
+
+
+def run_e2e(b: DecodeBench, steps: int, warmup: int, barrier, serial: bool):
+    """The step through the public host-buffer entry (HiraDecodeStep -> hira_decode_step): per step
+    the query and the new key/value rows come from pinned host memory and the attention output
+    goes back; the caller reads the result before the next token (stream synchronize per step).
+    Repeated E2E_REPEATS times from the same index state; returns the per-repeat ms per step."""
+    from hira_b200 import CUDAIndexer, HiraDecodeStep
+    st = b.st
+    idx = CUDAIndexer(b.w.levels, 1, b.bf)
+    idx.state, idx.num_heads, idx.dim = st, b.n_groups, DIM
+    snap = b.snapshot()
+    used = st.used.max(dim=0).values.tolist()
+    n_q = b.n_qheads
+    side = None if serial else torch.cuda.Stream(device=b.dev)
+    step = HiraDecodeStep(idx, n_q, q_dtype=torch.float32, threshold_method="none", side_stream=side)
+    if serial:
+        step.side = None
+    nset = len(b.qsets)
+    h_q = [qs[3].cpu().pin_memory() for qs in b.qsets]                  # (n_q, D) fp32 raw queries
+    h_k = b.new_k[:4].cpu().pin_memory()                                 # (4, groups, D)
+    h_v = b.new_v[:4].cpu().pin_memory()
+    h_out = torch.empty((n_q, DIM), dtype=torch.float32).pin_memory()
+    taus = [qs[1] for qs in b.qsets]
+    cur = torch.cuda.current_stream()
+
+    def one(i):
+        step(h_q[i % nset], h_out, threshold=taus[i % nset], k_host=h_k[i % 4], v_host=h_v[i % 4])
+        cur.synchronize()        # the caller reads the result before the next token
+
+    per_repeat = []
+    for _ in range(E2E_REPEATS):
+        b.restore(snap)
+        idx._parents_bound, idx._gp_bound = int(used[0]), int(used[1])
+        idx._snapshot, idx._appended = None, 0
+        for i in range(max(3, warmup)):
+            one(i)
+        barrier()
+        a, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(steps):
+            one(i)
+        e.record()
+        barrier()
+        per_repeat.append(a.elapsed_time(e) / steps)
+    if idx.state is not st:
+        raise RuntimeError("the index was reallocated during the end-to-end loop: capacity was mis-sized")
+    b.restore(snap)
+    h2d = h_q[0].numel() * 4 + h_k[0].numel() * 2 + h_v[0].numel() * 2
+    return {"per_repeat_ms": per_repeat, "h2d": h2d, "d2h": h_out.numel() * 4}
+
+
+# ----------------------------------------------------------------------------------
+# secondary workloads
+# ----------------------------------------------------------------------------------
+def secondary_cfg1(args, dev, barrier_local, peak):
+    """Configuration 1: batch 1, 8 KV / 32 query heads, 32,768 keys: the latency regime."""
+    w = W.CFG1
+    steps, warm = args.steps, args.warmup
+    b = DecodeBench(w, w.kv_heads, w.context, steps + warm + 8, dev, seed_offset=500, use_tc=not args.no_tc)
+    b.make_queries(N_QUERY_SETS, 250)
+    b.make_new_keys(steps + warm, 9100)
+    c = b.counters()
+    side = None if args.serial else torch.cuda.Stream(device=dev)
+    r = b.timed_loop(steps, warm, barrier_local, fused=True, side=side)
+    dense_ms = b.time_dense()
+    step_us = r["total_ms"] / steps * 1e3
+    ach = c["search_bytes"] / (r["search_ms"] * 1e-3) / 1e9
+    return {"workload": w.name, "step_us": step_us, "search_us": r["search_ms"] * 1e3, "sparse_attn_us": r["attn_ms"] * 1e3,
+            "append_us": r["append_ms"] * 1e3, "algorithmic_bytes": c["search_bytes"] + c["attn_bytes"] + c["append_bytes"],
+            "search_bytes": c["search_bytes"], "search_gbs": ach, "frac": ach / peak,
+            "scanned_fraction": c["scanned_fraction"], "dense_attention_us": dense_ms * 1e3, "build_ms": b.build_s * 1e3}
+
+
+def secondary_cfg3(args, dev):
+    """Configuration 3: streaming index update.  Prefix 65,536 keys per head, 8 KV heads, 4,096
+    single-key appends (incremental nearest-leaf assign + radius widen), full rebuild every 1,024."""
+    from hira_b200 import CUDAIndexer
+    from hira_b200 import index_state as S
+    w = W.CFG3
+    h, prefix, steps, every, bf = w.kv_heads, w.context, args.stream_steps, 1024, w.branching
+    keys, vals = W.make_kv(h, prefix + steps, 1300, dev, dist=w.dist, dtype=w.dtype)
+    ix = CUDAIndexer(3, 1, bf, max_context=prefix + every + 8, reserve_worst_case=True, use_tensor_cores=not args.no_tc)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ix.build(keys[None, :, :prefix], vals[None, :, :prefix])         # warm: allocations, first launches
+    e0.record()
+    ix.build(keys[None, :, :prefix], vals[None, :, :prefix])
+    e1.record()
+    torch.cuda.synchronize()
+    build_ms = e0.elapsed_time(e1)
+    append_us, rebuild_ms = [], []
+    pos = prefix
+    while pos < prefix + steps:
+        n = min(every, prefix + steps - pos)
+        e0.record()
+        for i in range(n):
+            S.append(ix.state, keys[:, pos + i:pos + i + 1].contiguous(), vals[:, pos + i:pos + i + 1].contiguous())
+        e1.record()
+        torch.cuda.synchronize()
+        append_us.append(e0.elapsed_time(e1) * 1e3 / n)
+        pos += n
+        ix._n_keys = pos
+        ix.check_status()
+        if pos < prefix + steps:
+            ix.max_context = pos + every + 8
+            e0.record()
+            ix.rebuild()
+            e1.record()
+            torch.cuda.synchronize()
+            rebuild_ms.append(e0.elapsed_time(e1))
+    e = 2
+    k1 = prefix // bf
+    append_bytes = h * ((k1 + k1 // bf) * (DIM * e + 4) + 2 * DIM * e)
+    return {"workload": w.name, "heads": h, "prefix": prefix, "appends": steps, "rebuild_every": every,
+            "append_us_per_step": statistics.mean(append_us), "append_us_by_window": append_us,
+            "append_algorithmic_bytes": append_bytes, "rebuild_ms": statistics.mean(rebuild_ms) if rebuild_ms else None,
+            "rebuilds": len(rebuild_ms), "initial_build_ms": build_ms,
+            "note": "append step = 8 heads, launch-latency bound (one small kernel pair per step)"}
+
+
+def secondary_cfg4(args, dev, rank, world, dist, barrier, peak):
+    """Configuration 4: sequence shards of 131,072 keys per GPU (context = N x 131,072), 64 query /
+    8 KV heads, branching 64; every rank searches its shard with the same threshold, the softmax
+    partials (m, l, out) are all-gathered over NCCL into a preallocated buffer and merged on the
+    device; the append goes to the last shard.  Rank 0 then recomputes all shards alone."""
+    from hira_b200 import index_state as S
+    from hira_b200.parallel import PartialsExchange
+    w = W.CFG4
+    steps, warm = args.steps, args.warmup
+    ex = PartialsExchange(w.q_heads, DIM, dev)
+    b = DecodeBench(w, w.kv_heads, w.context, steps + warm + 8, dev, seed_offset=700 + rank, use_tc=not args.no_tc,
+                    exchange=ex)
+    # the same query on every rank; one threshold for all shards: 2 % of shard 0 (identically distributed shards)
+    b.make_queries(1, 333)
+    tau = b.qsets[0][1]
+    if dist is not None:
+        dist.broadcast(tau, 0)
+    b.make_new_keys(steps + warm, 9200)
+    c = b.counters()
+    # check step: no append, merged output kept for the one-rank recomputation
+    b._searched, b._appended_ev = torch.cuda.Event(), torch.cuda.Event()
+    b.merged = torch.empty((w.q_heads, DIM), dtype=torch.float32, device=dev)
+    b.step(0, append=False)
+    torch.cuda.synchronize()
+    merged_dist = b.merged.clone()
+    last = rank == world - 1
+    r = b.timed_loop(steps, warm, barrier, fused=False, side=None, append=last)
+    t = torch.tensor([r["total_ms"], r["search_ms"], r["attn_ms"], r.get("exchange_ms", 0.0), r["append_ms"]],
+                     device=dev, dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, search_ms, attn_ms, exch_ms, append_ms = t.tolist()
+    check = None
+    if rank == 0:
+        # one-rank recomputation: every shard's index rebuilt here in turn, same kernels, one merge
+        buf = torch.zeros((world, w.q_heads, DIM + 2), dtype=torch.float32, device=dev)
+        q_hat, _, lscale, _ = b.qsets[0]
+        del b.st, b.compact
+        torch.cuda.empty_cache()
+        for r_ in range(world):
+            bb = DecodeBench(w, w.kv_heads, w.context, 8, dev, seed_offset=700 + r_, use_tc=not args.no_tc)
+            S.search(bb.st, q_hat, tau, scaling=lscale, flags=bb.flags, compact=bb.compact, tp=bb.tp)
+            S.sparse_attn(bb.st, q_hat, lscale, bb.compact, n_splits=bb.n_splits, workspace=bb.ws,
+                          out=buf[r_][:, 2:], out_ml=buf[r_][:, :2])
+            torch.cuda.synchronize()
+            del bb
+            torch.cuda.empty_cache()
+        alone = S.merge_partials(buf[:, :, 2:], buf[:, :, :2])
+        check = float((alone - merged_dist).abs().max() / alone.abs().max())
+    ach = c["search_bytes"] / (search_ms * 1e-3) / 1e9
+    return {"workload": w.name, "n_gpus": world, "context": w.context * world, "tokens_per_gpu": w.context,
+            "step_us": total_ms / steps * 1e3, "search_us": search_ms * 1e3, "sparse_attn_and_exchange_us": attn_ms * 1e3,
+            "exchange_us": exch_ms * 1e3, "append_us_last_shard": append_ms * 1e3,
+            "exchange": "NCCL all-gather of (m, l, out) rows into a preallocated buffer + merge kernel",
+            "exchange_bytes_per_gpu": ex.message_bytes, "algorithmic_bytes_per_gpu": c["search_bytes"] + c["attn_bytes"],
+            "search_gbs_per_gpu": ach, "frac": ach / peak, "scanned_fraction": c["scanned_fraction"],
+            "merged_vs_one_rank_max_rel_err": check}
+
+
+# ----------------------------------------------------------------------------------
 # our arm
 # ----------------------------------------------------------------------------------
 def run_ours(args):
     from hira_b200 import _lib as L
-    from hira_b200 import index_state as S
-    from hira_b200 import CUDAIndexer, CUDASearcher, hira_decode_attention
-    from hira_b200.cache import CacheOutput
-
+    w = W.CFG2
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -198,443 +583,217 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
     L.load()
 
-    batch, ctx = args.batch, args.ctx
-    total_groups = batch * H_KV
-    # kv heads are dealt to ranks (8 heads -> 1 per GPU at 8); every rank keeps all batch items
-    if H_KV % world != 0:
-        raise SystemExit(f"--gpus {world} must divide the {H_KV} KV heads")
-    kv_per_rank = H_KV // world
-    n_groups = batch * kv_per_rank
-    group = H_Q // H_KV
-    n_qheads = n_groups * group
-    steps_total = args.steps + args.warmup
-    spare_gp = 2 * steps_total + 16   # worst case every appended key opens a new grandparent block
-
-    t_setup = time.time()
-    keys, vals = make_kv(n_groups, ctx, seed=1000 + rank, device=dev)
-    k1 = ctx // BF
-    k2 = -(-k1 // BF)
-    st = S.IndexState(n_heads=n_groups, dim=DIM, vdim=DIM, bf=BF, depth=DEPTH, cap_parents=(k2 + spare_gp) * BF,
-                      dtype=torch.bfloat16, vdtype=torch.bfloat16, device=dev)
-    g = torch.Generator(device=dev)
-    g.manual_seed(7 + rank)
-    cent1 = torch.rand((n_groups, ctx), generator=g, device=dev).topk(k1, dim=1).indices.to(torch.int32).contiguous()
-    cent2 = torch.rand((n_groups, k1), generator=g, device=dev).topk(k2, dim=1).indices.to(torch.int32).contiguous()
-    torch.cuda.synchronize()
-    t0 = time.time()
-    S.build(st, keys, vals, cent_idx1=cent1, cent_idx2=cent2, n_iters=1, use_tensor_cores=not args.no_tc)
-    torch.cuda.synchronize()
-    build_s = time.time() - t0
-    del keys, vals, cent1, cent2
-    torch.cuda.empty_cache()
-
-    tp = S.tile_parents(st)
-    flags = L.HIRA_GATE_GE | L.HIRA_LEAF_GE
-    compact = S.alloc_compact(st, n_qheads, tp)
-    n_splits = S.attn_splits(st, n_qheads, tp)
-    ws = torch.empty((n_qheads * n_splits * (DIM + 2),), dtype=torch.float32, device=dev)
-    out = torch.empty((n_qheads, DIM), dtype=torch.float32, device=dev)
-
-    # query sets with their exact 2% thresholds (set-up, not timed)
-    sm_scale = DIM ** -0.5
-    qsets = []
-    kk = torch.full((n_qheads,), max(1, int(round(KEEP_FRAC * ctx))), dtype=torch.int32, device=dev)
-    neg_inf = torch.full((n_qheads,), float("-inf"), device=dev)
-    for i in range(N_QUERY_SETS):
-        q = make_queries(n_qheads, seed=50 + 13 * i + 1000 * rank, device=dev, pos=ctx + i)
-        qn = q.norm(dim=-1)
-        q_hat = (q / qn[:, None]).contiguous()
-        S.search(st, q_hat, neg_inf, flags=L.HIRA_GATE_GT | L.HIRA_LEAF_CANDIDATES, compact=compact, tp=tp)
-        tau = S.kth_score(st, compact, kk)
-        qsets.append((q_hat, tau.clone(), (qn * sm_scale).contiguous(), q))
-    new_k, new_v = make_kv(n_groups, steps_total, seed=9000 + rank, device=dev, first_pos=ctx)
-    new_k = new_k.transpose(0, 1).contiguous()   # (steps, groups, D)
-    new_v = new_v.transpose(0, 1).contiguous()
-
-    # traffic counters of one search (for the roofline numerator)
-    stats = torch.zeros((n_qheads, 8), dtype=torch.int32, device=dev)
-    S.search(st, qsets[0][0], qsets[0][1], scaling=qsets[0][2], flags=flags, compact=compact, stats=stats, tp=tp)
-    torch.cuda.synchronize()
-    s = stats.to(torch.int64).sum(dim=0).tolist()
-    rows_read, parents_read, emitted = s[6], s[7], s[5]
-    n_gp_rows = n_groups * k2
-    e = 2
-    search_bytes = n_gp_rows * (DIM * e + 4) + parents_read * (DIM * e + 4 + 4) + rows_read * DIM * e
-    attn_bytes = emitted * (DIM * e + 8) + n_qheads * DIM * 4
-    append_bytes = n_groups * ((k1 + k2) * (DIM * e + 4) + 2 * DIM * e)
-    scanned_frac = rows_read / float(n_groups * ctx)
-    setup_s = time.time() - t_setup
-
-    # fused: the search scores the parent rows it reads against the key appended right after, so
-    # the append needs no parent scan of its own.  With the append running beside the attention
-    # (below) the separate scan is mostly hidden anyway: at batch 16 both ways take the same time,
-    # at the per-GPU share of an 8-GPU run the fused one is 4 % faster (--unfused switches back).
-    fused = not args.unfused
-    scan = S.new_scan_slots(st)
-
-    def search_step(i, q_hat, tau, lscale):
-        if fused:
-            S.search(st, q_hat, tau, scaling=lscale, flags=flags, compact=compact, tp=tp, scan_key=new_k[i], scan_out=scan)
-        else:
-            S.search(st, q_hat, tau, scaling=lscale, flags=flags, compact=compact, tp=tp)
-
-    def append_step(i):
-        if fused:
-            S.append_scanned(st, new_k[i].unsqueeze(1), new_v[i].unsqueeze(1), scan)
-        else:
-            S.append(st, new_k[i].unsqueeze(1), new_v[i].unsqueeze(1))
-
-    # The append touches neither the compacted lists nor the value rows the attention reads, so
-    # it runs beside the attention on a second stream; the next search waits for both.
-    side = None if args.serial else torch.cuda.Stream(device=dev)
-
-    def step(i: int, ev=None):
-        q_hat, tau, lscale, _ = qsets[i % N_QUERY_SETS]
-        main = torch.cuda.current_stream()
-        if ev:
-            ev[0].record()
-        search_step(i, q_hat, tau, lscale)
-        if ev:
-            ev[1].record()
-        if side is None:
-            S.sparse_attn(st, q_hat, lscale, compact, n_splits=n_splits, workspace=ws, out=out)
-            if ev:
-                ev[2].record()
-                ev[3].record()
-            append_step(i)
-            if ev:
-                ev[4].record()
-            return
-        searched = torch.cuda.Event()
-        searched.record(main)
-        with torch.cuda.stream(side):
-            side.wait_event(searched)
-            if ev:
-                ev[3].record(side)
-            append_step(i)
-            if ev:
-                ev[4].record(side)
-            appended = torch.cuda.Event()
-            appended.record(side)
-        S.sparse_attn(st, q_hat, lscale, compact, n_splits=n_splits, workspace=ws, out=out)
-        if ev:
-            ev[2].record()
-        main.wait_event(appended)
-
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
-        step(i)
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(args.steps)]
+    batch, ctx = args.batch, args.ctx
+    # kv heads are dealt to ranks (8 heads -> 1 per GPU at 8); every rank keeps all batch items
+    if w.kv_heads % world != 0:
+        raise SystemExit(f"--gpus {world} must divide the {w.kv_heads} KV heads")
+    n_groups = batch * (w.kv_heads // world)
+    steps, warm = args.steps, args.warmup
+    tau_steps, tau_warm = min(steps, 10), 3
+    appends = (steps + warm) + (tau_steps + tau_warm) + 8
+    b = DecodeBench(w, n_groups, ctx, appends, dev, seed_offset=rank, use_tc=not args.no_tc)
+    b.make_queries(N_QUERY_SETS, 50 + 1000 * rank)
+    b.make_new_keys(steps + warm, 9000 + rank)
+    c = b.counters()
+    fused = not args.unfused
+    side = None if args.serial else torch.cuda.Stream(device=dev)
+
+    snap = b.snapshot()
     sampler = ClockSampler(local_rank)
-    barrier()
     if rank == 0:
         sampler.start()
-    t_start = torch.cuda.Event(enable_timing=True)
-    t_end = torch.cuda.Event(enable_timing=True)
-    host_t0 = time.time()
-    t_start.record()
-    for j in range(args.steps):
-        step(args.warmup + j, ev[j])
-    t_end.record()
-    barrier()
-    host_t1 = time.time()
-    total_ms = t_start.elapsed_time(t_end)
-    search_ms = statistics.mean(ev[j][0].elapsed_time(ev[j][1]) for j in range(args.steps))
-    attn_ms = statistics.mean(ev[j][1].elapsed_time(ev[j][2]) for j in range(args.steps))
-    append_ms = statistics.mean(ev[j][3].elapsed_time(ev[j][4]) for j in range(args.steps))
-    status = int(st.status.item())
-    if status:
-        raise RuntimeError(f"index capacity exhausted during the bench (status {status})")
+    r = b.timed_loop(steps, warm, barrier, fused=fused, side=side)
+    sampler.paused = True
+    # the step with the threshold found on the device inside it (sample_mean_topk over 1000 stored keys)
+    rt = b.timed_loop(tau_steps, tau_warm, barrier, first=steps + warm, fused=fused, side=side, tau_in_step=True)
+    stats = b.S.new_stats(b.n_qheads, dev)
+    b.S.search(b.st, b.qsets[0][0], b.tau_buf, scaling=b.qsets[0][2], flags=b.flags, compact=b.compact, stats=stats, tp=b.tp)
+    sel_tau = float(stats[:, 5].sum().item()) / b.n_qheads
+    b.restore(snap)
+    search_plain_us = b.time_search_only(5, fused=False)
+    search_scan_us = b.time_search_only(5, fused=True)
+    dense_ms = b.time_dense() if not args.no_dense else None
 
-    # dense attention over the full cache on the same shapes (torch SDPA), for context
-    dense_ms = None
-    if args.dense and rank == 0:
-        dense_ms = time_dense(st, n_groups, group, ctx, dev)
-
-    # ---- end to end through the public API with host buffers ----------------------------
-    sampler.paused = True        # the end-to-end loop is host-latency sensitive: no sampling thread beside it
-    e2e = run_e2e(args, st, qsets, n_groups, group, k2, dev, CUDAIndexer, CUDASearcher, CacheOutput,
-                  hira_decode_attention, barrier, new_k, new_v)
+    # ---- end to end through the host-buffer entry ------------------------------------------------
+    e2e = run_e2e(b, steps, warm, barrier, args.serial)
     sampler.paused = False
     if rank == 0:
         # an NVML query takes milliseconds, the timed region a few tens: run the step's search and
-        # attention again (untimed; no appends, so the index does not grow) until the sampler has
-        # seen the load for a quarter of a second.  Done last so that the heat it makes reaches no
-        # timed loop.
+        # attention again (untimed; no appends) until the sampler has seen the load for a quarter of
+        # a second.  Done after the timed loops so that the heat it makes reaches none of them.
         t_more = time.time()
         while time.time() - t_more < 0.25:
             for i in range(8):
-                q_hat, tau, lscale, _ = qsets[i % N_QUERY_SETS]
-                S.search(st, q_hat, tau, scaling=lscale, flags=flags, compact=compact, tp=tp)
-                S.sparse_attn(st, q_hat, lscale, compact, n_splits=n_splits, workspace=ws, out=out)
+                b.step(i, append=False)
             torch.cuda.synchronize()
-    clocks = sampler.stop((host_t0, host_t1)) if rank == 0 else None
+    clocks = sampler.stop(r["host"]) if rank == 0 else None
     barrier()
 
-    t = torch.tensor([total_ms, search_ms, attn_ms, append_ms, e2e["ms_per_step"]], device=dev, dtype=torch.float64)
+    e2e_ms = statistics.median(e2e["per_repeat_ms"])
+    t = torch.tensor([r["total_ms"], r["search_ms"], r["attn_ms"], r["append_ms"], e2e_ms, rt["total_ms"],
+                      min(e2e["per_repeat_ms"]), max(e2e["per_repeat_ms"]), search_plain_us, search_scan_us,
+                      dense_ms or 0.0], device=dev, dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, search_ms, attn_ms, append_ms, e2e_ms = t.tolist()
+    total_ms, search_ms, attn_ms, append_ms, e2e_ms, tau_total_ms, e2e_min, e2e_max, search_plain_us, search_scan_us, dense_max = t.tolist()
+    peak, peak_src = peaks()
+
+    # ---- secondary workloads -------------------------------------------------------------------
+    secondary = {}
+    if not args.no_secondary and (batch, ctx) == (w.batch, w.context):
+        del b.st, b.compact, b.ws
+        b = None
+        torch.cuda.empty_cache()
+        if rank == 0:
+            try:
+                secondary["cfg1"] = secondary_cfg1(args, dev, torch.cuda.synchronize, peak)
+            except Exception as ex:  # reported, never fatal for the headline
+                secondary["cfg1"] = {"error": repr(ex)}
+            torch.cuda.empty_cache()
+            try:
+                secondary["cfg3"] = secondary_cfg3(args, dev)
+            except Exception as ex:
+                secondary["cfg3"] = {"error": repr(ex)}
+            torch.cuda.empty_cache()
+        barrier()
+        secondary["cfg4"] = secondary_cfg4(args, dev, rank, world, dist, barrier, peak)
+        barrier()
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
-    ms_per_step = total_ms / args.steps
-    peak, peak_src = peaks()
-    achieved = search_bytes / (search_ms * 1e-3) / 1e9
-    step_bytes = search_bytes + attn_bytes + append_bytes
-    cpu = cpu_baseline_sample(args) if (world == 1 or rank == 0) and not args.no_cpu else None
+    ms_per_step = total_ms / steps
+    achieved = c["search_bytes"] / (search_ms * 1e-3) / 1e9
+    step_bytes = c["search_bytes"] + c["attn_bytes"] + c["append_bytes"]
+    cpu = cpu_baseline_sample(args) if not args.no_cpu else None
+    traffic = SEARCH_DRAM_BYTES_PER_GROUP.get(args.traffic_key)
     line = {
-        "metric": "decode_step_us", "value": ms_per_step * 1e3, "unit": "us", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong",
+        "metric": "decode_step_us", "value": ms_per_step * 1e3, "unit": "us", "n_gpus": world, "steps": steps,
+        "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD if (batch, ctx) == (BATCH, CTX) else f"b{batch}_ctx{ctx}",
-                   "batch": batch, "kv_heads": H_KV, "q_heads": H_Q, "dim": DIM, "context": ctx, "levels": DEPTH,
-                   "branching": BF, "keep_frac": KEEP_FRAC, "tau": "exact k-th largest score per query head, set up front",
-                   "sharding": f"kv_head x{world}", "l2": "inputs>L2 (keys per GPU >> 126 MB)",
-                   "gate": "ge", "leaf": "ge",
+        "config": {"workload": w.name if (batch, ctx) == (w.batch, w.context) else f"b{batch}_ctx{ctx}",
+                   "batch": batch, "kv_heads": w.kv_heads, "q_heads": w.q_heads, "dim": DIM, "context": ctx,
+                   "levels": w.levels, "branching": w.branching, "keep_frac": w.keep,
+                   "tau": "exact k-th largest score per query head, set up front (variants.tau_in_step: found in the step)",
+                   "sharding": f"kv_head x{world}", "l2": "inputs>L2 (keys per GPU >> 126 MB)", "gate": "ge", "leaf": "ge",
                    "step": ("search with the append's parent scan folded in" if fused else "search") + ", then sparse attention "
                            + ("followed by" if side is None else "and, beside it on a second stream,") + " the 1-key append"},
-        "e2e": {"value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"]},
-        "gpu_launches": args.steps * (1 + (1 if n_splits == 1 else 2) + (1 if fused else 2)),   # search, sparse_attn[, merge][, append_scan], append
+        "e2e": {"value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                "repeats": E2E_REPEATS, "min_us": e2e_min * 1e3, "max_us": e2e_max * 1e3,
+                "entry": "HiraDecodeStep -> hira_decode_step (one C call per step, host buffers)"},
+        "gpu_launches": steps * (2 + (1 if fused else 2)),   # search, sparse_attn (one split: no merge), [append_scan,] append
         "roofline": {"bound": "hbm", "kernel": "search_kernel", "achieved": achieved, "peak": peak,
                      "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": (SEARCH_DRAM_BYTES_PER_GROUP_AT_CTX * n_groups if ctx == CTX else None),
-                     "algorithmic_bytes_per_launch": search_bytes},
+                     "traffic": (traffic * n_groups if (traffic and ctx == w.context) else None),
+                     "algorithmic_bytes_per_launch": c["search_bytes"]},
         "breakdown_us": {"search": search_ms * 1e3, "sparse_attn": attn_ms * 1e3, "append": append_ms * 1e3},
+        "variants": {"tau_in_step": {"step_us": tau_total_ms / tau_steps * 1e3, "method": "sample_mean_topk, 1000 samples, top 16",
+                                     "selected_per_qhead": sel_tau, "steps": tau_steps},
+                     "search_plain_us": search_plain_us, "search_with_parent_scan_us": search_scan_us},
         "step_hbm": {"bytes": step_bytes, "achieved_gbs": step_bytes / (ms_per_step * 1e-3) / 1e9,
                      "frac_of_peak": step_bytes / (ms_per_step * 1e-3) / 1e9 / peak},
-        "scanned_fraction": scanned_frac, "selected_per_qhead": emitted / n_qheads,
-        "dense_attention_us": None if dense_ms is None else dense_ms * 1e3,
-        "build_s": build_s, "setup_s": setup_s, "clocks": clocks, "cpu_baseline": cpu,
+        "scanned_fraction": c["scanned_fraction"], "selected_per_qhead": c["selected_per_qhead"],
+        "dense_attention_us": None if dense_ms is None else dense_max * 1e3,
+        "vs_dense": None if dense_ms is None else dense_max / ms_per_step,
+        "secondary": secondary, "clocks": clocks, "cpu_baseline": cpu,
     }
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
 
 
-def time_dense(st, n_groups, group, ctx, dev):
-    """torch SDPA over the whole bf16 cache (dense decode attention), same shapes."""
-    k = st.children[:, :ctx].unsqueeze(0)            # (1, groups, ctx, D) -- slot order is irrelevant for timing
-    v = st.values[:, :ctx].unsqueeze(0)
-    q = torch.randn((1, n_groups * group, 1, DIM), device=dev, dtype=torch.bfloat16)
-    f = torch.nn.functional.scaled_dot_product_attention
-    for _ in range(3):
-        f(q, k, v, enable_gqa=True)
-    torch.cuda.synchronize()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for _ in range(5):
-        f(q, k, v, enable_gqa=True)
-    b.record()
-    torch.cuda.synchronize()
-    return a.elapsed_time(b) / 5
-
-
-def run_e2e(args, st, qsets, n_groups, group, k2, dev, CUDAIndexer, CUDASearcher, CacheOutput,
-            hira_decode_attention, barrier, new_k, new_v):
-    """The same step through the public classes, with host buffers: per step the query and
-    the new key/value rows come from pinned host memory and the attention output goes back."""
-    idx = CUDAIndexer(DEPTH, 1, BF)
-    idx.state, idx.num_heads, idx.dim = st, n_groups, DIM
-    used = st.used.max(dim=0).values.tolist()        # capacity was pre-allocated: start the host bounds here
-    idx._parents_bound, idx._gp_bound = int(used[0]), int(used[1])
-    searcher = CUDASearcher(BF)
-    n_q = n_groups * group
-    steps = args.steps
-    nset = len(qsets)
-    h_q = [qs[3].reshape(1, n_q, 1, DIM).cpu().pin_memory() for qs in qsets]       # fp32 queries
-    h_k = new_k[: 4].reshape(4, 1, n_groups, 1, DIM).cpu().pin_memory()
-    h_v = new_v[: 4].reshape(4, 1, n_groups, 1, DIM).cpu().pin_memory()
-    h_out = torch.empty((1, n_q, 1, DIM), dtype=torch.float32).pin_memory()
-    empty = torch.empty((1, n_groups, 0, DIM), dtype=torch.bfloat16, device=dev)
-    co = CacheOutput(queued_keys=empty, queued_values=empty, prefill_keys=None, prefill_values=None, indexer=idx,
-                     searcher=searcher)
-    taus = [qs[1] for qs in qsets]
-
-    side = None if args.serial else torch.cuda.Stream(device=dev)
-
-    def one(i):
-        q = h_q[i % nset].to(dev, non_blocking=True)
-        if side is not None:
-            # the new key / value rows are copied and appended on a second stream, beside the
-            # attention; the append starts when the step's search has finished
-            o = hira_decode_attention(q, co, threshold=taus[i % nset])
-            with torch.cuda.stream(side):
-                k = h_k[i % 4].to(dev, non_blocking=True)
-                v = h_v[i % 4].to(dev, non_blocking=True)
-            idx.update(k, v, stream=side)
-            h_out.copy_(o, non_blocking=True)
-            idx.wait_pending_update()                   # the step ends when the append has landed too
-            return
-        # (the scan folded into the search, `append_key=` / `update(scanned=True)`, would put the
-        # key's copy in front of the search: through host buffers the plain order is faster)
-        o = hira_decode_attention(q, co, threshold=taus[i % nset])
-        k = h_k[i % 4].to(dev, non_blocking=True)       # queued behind the attention: not on its critical path
-        v = h_v[i % 4].to(dev, non_blocking=True)
-        idx.update(k, v)
-        h_out.copy_(o, non_blocking=True)
-
-    for i in range(max(3, args.warmup)):
-        one(i)
-    barrier()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for i in range(steps):
-        one(i)
-        torch.cuda.current_stream().synchronize()   # the caller reads the result before the next token
-    b.record()
-    barrier()
-    if idx.state is not st:
-        raise RuntimeError("the index was reallocated during the end-to-end loop: capacity was mis-sized")
-    h2d = h_q[0].numel() * 4 + h_k[0].numel() * 2 + h_v[0].numel() * 2
-    return {"ms_per_step": a.elapsed_time(b) / steps, "h2d": h2d, "d2h": h_out.numel() * 4}
-
-
 # ----------------------------------------------------------------------------------
 # CPU side: the reference's kernel (oracle/_ref) or the oracle port, on a bounded sample
 # ----------------------------------------------------------------------------------
-def load_ref_ext():
-    so = ROOT / "oracle" / "_ref" / "hira_torch_ext_v3.so"
-    if not so.exists():
-        return None
-    try:
-        import importlib.util
-        spec = importlib.util.spec_from_file_location("hira_torch_ext_v3", str(so))
-        m = importlib.util.module_from_spec(spec)
-        spec.loader.exec_module(m)
-        return m
-    except Exception:
-        return None
+class CpuDecode:
+    """One batch item of the workload on the host cores, the way the reference's CPU classes run it:
+    CPUIndexer.build (k-means stand-in, see oracle/cpu_index.py), then per step
+    CPUSearcher(search_strategy="fused_v3").search -- which rebuilds its level tensors and CSR
+    adjacency whenever the number of keys changed, i.e. every step here (searcher/cpu.py:280-343) --
+    attention over the survivors (the reference ships none: fp32 torch softmax), and
+    CPUIndexer.update with the token's key (indexer/cpu.py:124-190)."""
 
+    def __init__(self, w: W.Workload, ctx: int):
+        from oracle import cpu_index as CI
+        from oracle import oracle as O
+        self.CI, self.O, self.w = CI, O, w
+        self.ext = CI.load_reference_kernel(ROOT)
+        torch.set_num_threads(os.cpu_count() or 1)
+        keys, vals = W.make_kv(w.kv_heads, ctx, 4242, "cpu", dist=w.dist, dtype=w.dtype)
+        self.vals = vals.float()
+        self.levels = CI.build_levels(keys.float().numpy(), w.levels, w.branching, 1)
+        self.group = w.group
+        hq = w.kv_heads * w.group
+        q = W.make_queries(hq, 99, "cpu", pos=ctx)
+        qn = q.norm(dim=-1)
+        self.q_hat = (q / qn[:, None]).contiguous()
+        sc = torch.einsum("hgd,hnd->hgn", self.q_hat.view(w.kv_heads, w.group, DIM), keys.float()).reshape(hq, ctx)
+        kth = max(1, int(round(w.keep * ctx)))
+        self.tau = sc.kthvalue(ctx - kth + 1, dim=1).values.contiguous()
+        self.scaling = (qn * DIM ** -0.5).contiguous()
+        nk, nv = W.make_kv(w.kv_heads, 64, 4343, "cpu", dist=w.dist, dtype=w.dtype, first_pos=ctx)
+        self.new_k, self.new_v = nk.float(), nv.float()
+        self.i = 0
+        self.kind = "reference" if self.ext is not None else "port"
+        self.cores = min(hq, os.cpu_count() or 1) if self.ext is not None else min(hq, O.num_threads())
 
-def cpu_sample_index(n_kv: int, ctx: int, seed: int):
-    """CPU-format index (the reference CPUIndexer's levels, indexer/cpu.py:48-122) for `n_kv`
-    heads of the workload: level sizes ctx, ctx/bf, ctx/bf^2; one Lloyd pass from random
-    centres stands in for faiss.Kmeans (not installed); radii by the triangle inequality
-    (indexer/cpu.py:263-311).  numpy/BLAS, set-up only."""
-    g = torch.Generator().manual_seed(seed)
-    pos = torch.arange(ctx)
-    keys = torch.randn((n_kv, ctx, DIM), generator=g)
-    for h in range(n_kv):
-        rope_(keys[h], pos)
-    keys[..., list(OUTLIER_CHANNELS)] *= 8.0
-    keys = keys.to(torch.bfloat16).float()
-    vals = torch.randn((n_kv, ctx, DIM), generator=g).to(torch.bfloat16).float()
-    centers, radii, c2p, sizes = [keys], [torch.zeros((n_kv, ctx))], [], [ctx]
-    size = ctx
-    for _ in range(DEPTH - 1):
-        size = size // BF
-        child = centers[-1]
-        n_child = child.shape[1]
-        cent = torch.empty((n_kv, size, DIM))
-        assign = torch.empty((n_kv, n_child), dtype=torch.long)
-        for h in range(n_kv):
-            init = child[h][torch.randperm(n_child, generator=g)[:size]]
-            a = torch.cdist(child[h], init).argmin(dim=1)
-            sums = torch.zeros((size, DIM)).index_add_(0, a, child[h])
-            cnt = torch.bincount(a, minlength=size).clamp_min(1).float()[:, None]
-            c = torch.where(torch.bincount(a, minlength=size)[:, None] > 0, sums / cnt, init)
-            cent[h] = c
-            assign[h] = torch.cdist(child[h], c).argmin(dim=1)
-        parent_for_child = cent.gather(1, assign.unsqueeze(-1).expand(-1, -1, DIM))
-        contrib = (child - parent_for_child).norm(dim=-1) + radii[-1]
-        r = torch.full((n_kv, size), float("-inf")).scatter_reduce_(1, assign, contrib, reduce="amax", include_self=True)
-        centers.append(cent)
-        radii.append(r)
-        c2p.append(assign)
-        sizes.append(size)
-    # CSR adjacency as CPUSearcher builds it (searcher/cpu.py:345-363)
-    offsets, children = [], []
-    for l in range(DEPTH - 1):
-        P = sizes[l + 1]
-        off = torch.empty((n_kv, P + 1), dtype=torch.long)
-        ch = torch.empty((n_kv, sizes[l]), dtype=torch.long)
-        for h in range(n_kv):
-            order = torch.argsort(c2p[l][h])
-            off[h, 0] = 0
-            off[h, 1:] = torch.bincount(c2p[l][h], minlength=P).cumsum(0)
-            ch[h] = order
-        offsets.append(off)
-        children.append(ch)
-    offsets.append(torch.empty(0, dtype=torch.long))
-    children.append(torch.empty(0, dtype=torch.long))
-    c2p.append(torch.empty(0, dtype=torch.long))
-    return dict(keys=keys, vals=vals, centers=centers, radii=radii, c2p=c2p, sizes=sizes, offsets=offsets,
-                children=children)
-
-
-def cpu_step_timer(n_kv: int, ctx: int, reps: int, warm: int):
-    """Times one decode step (search + attention over survivors + 1-key append) of the CPU
-    path for `n_kv` KV heads x (H_Q/H_KV) query heads each.  Returns (seconds per step, kind, cores)."""
-    from oracle import oracle as O
-    ext = load_ref_ext()
-    torch.set_num_threads(os.cpu_count() or 1)
-    ix = cpu_sample_index(n_kv, ctx, seed=4242)
-    group = H_Q // H_KV
-    hq = n_kv * group
-    g = torch.Generator().manual_seed(99)
-    q = torch.randn((hq, DIM), generator=g)
-    qn = q.norm(dim=-1)
-    q_hat = (q / qn[:, None]).contiguous()
-    keys = ix["keys"]
-    sc = torch.einsum("hgd,hnd->hgn", q_hat.view(n_kv, group, DIM), keys).reshape(hq, ctx)
-    kth = max(1, int(round(KEEP_FRAC * ctx)))
-    tau = sc.kthvalue(ctx - kth + 1, dim=1).values.contiguous()
-    scaling = (qn * DIM ** -0.5).contiguous()
-    q2kv = torch.arange(hq) // group
-    vals = ix["vals"]
-    new_k = torch.randn((n_kv, 1, DIM), generator=g)
-    state = {"keys": keys, "vals": vals}
-
-    def search():
-        if ext is not None:
-            return ext.fused_tree_search_v3(state["keys"], q_hat, tau, ix["centers"],
-                                            ix["radii"], ix["c2p"], ix["sizes"], ix["offsets"], ix["children"],
-                                            q2kv, scaling)
-        out, _ = O.search_csr([c.numpy() for c in ix["centers"]], [r.numpy() for r in ix["radii"]],
-                              [o.numpy() if o.numel() else None for o in ix["offsets"]],
-                              [c.numpy() if c.numel() else None for c in ix["children"]], ix["sizes"],
-                              q_hat.numpy(), tau.numpy(), scaling=scaling.numpy(), q2kv=q2kv.numpy())
+    def search(self):
+        CI, O = self.CI, self.O
+        prepared = CI.searcher_inputs(self.levels)          # recomputed: num_keys changed since the last step
+        if self.ext is not None:
+            return CI.reference_search(self.ext, self.levels, self.q_hat, self.tau, self.scaling, prepared=prepared)
+        cs, rs, c2ps, sizes, offs, chs = prepared
+        hq = self.q_hat.shape[0]
+        q2kv = (torch.arange(hq) // self.group).numpy()
+        out, _ = O.search_csr([c.numpy() for c in cs], [r.numpy() for r in rs],
+                              [o.numpy() if o.numel() else None for o in offs],
+                              [c.numpy() if c.numel() else None for c in chs], sizes, self.q_hat.numpy(),
+                              self.tau.numpy(), scaling=self.scaling.numpy(), q2kv=q2kv)
         return torch.from_numpy(out)
 
-    def one():
-        dense = search()                                   # (hq, ctx) logits, 0 where not selected
+    def step(self):
+        dense = self.search()                                   # (hq, n) logits, 0 where not selected
         outs = []
-        for qh in range(hq):                               # attention over the survivors (the reference has none)
+        for qh in range(dense.shape[0]):
             sel = dense[qh].nonzero().squeeze(1)
-            w = torch.softmax(dense[qh, sel], dim=0)
-            outs.append(w @ state["vals"][qh // group, sel])
-        # append as CPUIndexer.update does for one key: concatenate onto every level (indexer/cpu.py:158-181)
-        k_cat = torch.cat([state["keys"], new_k], dim=1)
-        v_cat = torch.cat([state["vals"], new_k], dim=1)
-        del k_cat, v_cat                                   # not kept: the next step searches the same index
+            wgt = torch.softmax(dense[qh, sel], dim=0)
+            outs.append(wgt @ self.vals[qh // self.group, sel])
+        j = self.i % self.new_k.shape[1]
+        self.CI.update_levels(self.levels, self.new_k[:, j:j + 1].numpy(), self.w.branching, 1)
+        self.vals = torch.cat([self.vals, self.new_v[:, j:j + 1]], dim=1)
+        self.i += 1
         return outs
 
+
+def cpu_time_steps(args, reps: int, warm: int):
+    cd = CpuDecode(W.CFG2, args.ctx)
     for _ in range(warm):
-        one()
+        cd.step()
     t0 = time.perf_counter()
     for _ in range(reps):
-        one()
-    dt = (time.perf_counter() - t0) / reps
-    cores = min(hq, os.cpu_count() or 1) if ext is not None else min(hq, O.num_threads())
-    return dt, ("reference" if ext is not None else "port"), cores
+        cd.step()
+    return (time.perf_counter() - t0) / reps, cd.kind, cd.cores
 
 
 def cpu_baseline_sample(args):
     """Bounded CPU sample: 1 of the batch items (8 KV heads x full context); scaled to the batch."""
+    w = W.CFG2
     try:
-        dt, kind, cores = cpu_step_timer(H_KV, args.ctx, reps=3, warm=1)
+        dt, kind, cores = cpu_time_steps(args, reps=3, warm=1)
     except Exception as ex:  # the baseline is reported, never required
-        return {"value": None, "unit": "us", "cores": 0, "kind": "port", "sample": f"failed: {ex}"}
+        return {"value": None, "unit": "us", "cores": 0, "kind": "port", "sample": f"failed: {ex!r}"}
     return {"value": dt * args.batch * 1e6, "unit": "us", "cores": cores, "kind": kind,
-            "sample": f"1 of {args.batch} batch items ({H_KV} kv heads x {args.ctx} keys, {H_Q} query heads) timed "
-                      f"{dt * 1e3:.1f} ms/step, x{args.batch}; index = numpy Lloyd stand-in for faiss k-means; "
-                      "search = reference fused_tree_search_v3" + ("" if kind == "reference" else " (oracle port)")}
+            "sample": f"1 of {args.batch} batch items ({w.kv_heads} kv heads x {args.ctx} keys, {w.q_heads} query heads) timed "
+                      f"{dt * 1e3:.1f} ms/step over 3 steps, x{args.batch}; index and per-step update as the reference "
+                      "CPUIndexer lays them out (k-means: numpy Lloyd stand-in for faiss); search = reference "
+                      "fused_tree_search_v3" + ("" if kind == "reference" else " (oracle port)") +
+                      " driven as its CPUSearcher drives it"}
 
 
 def run_reference(args):
@@ -642,20 +801,19 @@ def run_reference(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
-    reps = max(1, args.steps)
-    warm = max(1, min(args.warmup, 2))
-    reps = min(reps, 5)
-    dt, kind, cores = cpu_step_timer(H_KV, args.ctx, reps=reps, warm=warm)
+    w = W.CFG2
+    reps, warm = max(1, args.steps), max(1, args.warmup)
+    dt, kind, cores = cpu_time_steps(args, reps=reps, warm=warm)
     value = dt * args.batch * 1e6
-    sample = (f"each step = 1 of {args.batch} batch items ({H_KV} kv heads x {args.ctx} keys) on the host cores, "
-              f"x{args.batch}; {reps} steps timed")
+    sample = (f"each step = 1 of {args.batch} batch items ({w.kv_heads} kv heads x {args.ctx} keys) on the host cores, "
+              f"x{args.batch}; {reps} steps timed after {warm} warm-up steps")
     line = {
         "impl": "reference", "metric": "decode_step_us", "value": value, "unit": "us", "n_gpus": world,
         "steps": reps, "warmup": warm, "ms_per_step": value / 1e3, "higher_is_better": False, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD if (args.batch, args.ctx) == (BATCH, CTX) else f"b{args.batch}_ctx{args.ctx}",
-                   "batch": args.batch, "kv_heads": H_KV, "q_heads": H_Q, "dim": DIM, "context": args.ctx,
-                   "levels": DEPTH, "branching": BF, "keep_frac": KEEP_FRAC},
+        "config": {"workload": w.name if (args.batch, args.ctx) == (w.batch, w.context) else f"b{args.batch}_ctx{args.ctx}",
+                   "batch": args.batch, "kv_heads": w.kv_heads, "q_heads": w.q_heads, "dim": DIM, "context": args.ctx,
+                   "levels": w.levels, "branching": w.branching, "keep_frac": w.keep},
         "cpu_baseline": {"value": value, "unit": "us", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -669,14 +827,17 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=BATCH)
-    ap.add_argument("--ctx", type=int, default=CTX)
+    ap.add_argument("--batch", type=int, default=W.CFG2.batch)
+    ap.add_argument("--ctx", type=int, default=W.CFG2.context)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     ap.add_argument("--no-tc", action="store_true", help="build the index with the CUDA-core assignment")
-    ap.add_argument("--dense", action="store_true", help="also time torch SDPA over the full cache")
+    ap.add_argument("--no-dense", action="store_true", help="skip timing torch SDPA over the full cache")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the secondary workloads (cfg1, cfg3, cfg4)")
+    ap.add_argument("--stream-steps", type=int, default=4096, help="appends of the streaming workload (cfg3)")
     ap.add_argument("--serial", action="store_true", help="append after the attention on one stream instead of beside it")
     ap.add_argument("--unfused", action="store_true",
                     help="separate parent scan in the append instead of the scan folded into the search")
+    ap.add_argument("--traffic-key", default="bf16_stream", help=argparse.SUPPRESS)
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

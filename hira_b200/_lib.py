@@ -27,9 +27,11 @@ EXPORTED_SYMBOLS = [
     "hira_threshold", "hira_kth_score", "hira_prepare_query", "hira_build_workspace_bytes", "hira_build",
     "hira_recompute_radii", "hira_export", "hira_assign", "hira_sparse_attn_noalloc", "hira_decode_attention",
     "hira_search_scan", "hira_append_scanned", "hira_step_events_create", "hira_step_events_destroy",
-    "hira_decode_step",
+    "hira_decode_step", "hira_q8_refresh",
 ]
 NOALLOC_SCRATCH_FLOATS = 1 << 20
+SEARCH_STATS = 10     # uint32 counters per query head (HIRA_SEARCH_STATS)
+Q8_CHAN = 136         # floats per head in q8_chan_scale (HIRA_Q8_CHAN)
 
 
 class HiraIndexStruct(C.Structure):
@@ -42,6 +44,7 @@ class HiraIndexStruct(C.Structure):
         ("parents", C.c_void_p), ("parent_radii", C.c_void_p), ("parent_sqnorm", C.c_void_p),
         ("child_counts", C.c_void_p), ("grand_parents", C.c_void_p), ("gp_radii", C.c_void_p),
         ("gp_sqnorm", C.c_void_p), ("gp_counts", C.c_void_p), ("used", C.c_void_p),
+        ("children_q8", C.c_void_p), ("children_q8_meta", C.c_void_p), ("q8_chan_scale", C.c_void_p),
     ]
 
 
@@ -109,6 +112,8 @@ def _declare(lib):
     lib.hira_build_workspace_bytes.argtypes = [IX, I32]
     lib.hira_build.restype = C.c_int
     lib.hira_build.argtypes = [IX, P, P, I32, I64, I64, I32, P, P, I32, I32, P, P, SZ, P]
+    lib.hira_q8_refresh.restype = C.c_int
+    lib.hira_q8_refresh.argtypes = [IX, P]
     lib.hira_recompute_radii.restype = C.c_int
     lib.hira_recompute_radii.argtypes = [IX, P]
     lib.hira_export.restype = C.c_int

@@ -247,6 +247,18 @@ append_kernel(const AppendParams P) {
         }
         __syncthreads();  // all reads of the old state are done
 
+        // the int8 side copy of the new child row (dim == 128), by the 8 lanes of group 0; the row's
+        // values are those just stored (x holds the key in the index dtype's precision)
+        auto write_q8 = [&](int slot) {
+            if constexpr (NCH == 2) {
+                if (ix.children_q8 != nullptr) {
+                    const size_t at = (size_t)h * capC + slot;
+                    q8_write_row(x, ix.q8_chan_scale + (size_t)h * HIRA_Q8_CHAN,
+                                 reinterpret_cast<int8_t*>(ix.children_q8) + at * 128,
+                                 reinterpret_cast<float2*>(ix.children_q8_meta) + at, slot & 7, lane);
+                }
+            }
+        };
         // ---- warp 0 applies the insertion ---------------------------------------
         if (tid < 32) {
             const int token = P.token_base < 0 ? n_keys : P.token_base + key;
@@ -267,6 +279,7 @@ append_kernel(const AppendParams P) {
                         const int c = lane + GROUP * i;
                         if (c * 8 < dim) store_chunk(children + (size_t)slot * dim, c, x[i]);
                     }
+                    write_q8(slot);
                     if (values) {
 #pragma unroll
                         for (int i = 0; i < NVCH; ++i) {
@@ -304,6 +317,7 @@ append_kernel(const AppendParams P) {
                             if (new_gp) store_chunk(gps + (size_t)g_dst * dim, c, x[i]);
                         }
                     }
+                    write_q8(slot);
                     if (values) {
 #pragma unroll
                         for (int i = 0; i < NVCH; ++i) {

@@ -13,6 +13,7 @@
 // Every wait on an mbarrier is bounded; on a timeout the CTA writes index -1 for its points
 // and leaves in an orderly way (TMEM freed).  No TMA multicast is used.
 #include "common.cuh"
+#include "tc_common.cuh"
 
 #include <cuda.h>
 #include <math_constants.h>
@@ -25,7 +26,6 @@ constexpr int TC_K = 128;        // D
 constexpr int TC_BOX_K = 64;     // elements per 128-byte swizzle row
 constexpr int TC_BOX_BYTES = TC_BM * TC_BOX_K * 2;   // 16 KB
 constexpr int TC_THREADS = 160;      // 4 epilogue warps + 1 producer/MMA warp
-constexpr unsigned long long TC_WAIT_CYCLES = 400ull * 1000 * 1000;  // ~0.2 s
 
 struct TcSmem {
     // offsets in the 1024-byte aligned dynamic shared memory
@@ -36,47 +36,10 @@ struct TcSmem {
     static constexpr int TOTAL = TMEM_SLOT + 16;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    return ok != 0;
-}
-// bounded wait: false on timeout
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if ((unsigned long long)(clock64() - t0) > TC_WAIT_CYCLES) return false;
-    }
-    return true;
-}
-
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
         ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
-}
-
-// K-major operand tile, 128-byte swizzle: rows of 128 B, 8-row groups 1024 B apart
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((saddr & 0x3ffff) >> 4);        // start address
-    d |= (uint64_t)1 << 16;                          // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset between 8-row groups
-    d |= (uint64_t)1 << 46;                          // descriptor version (sm_100)
-    d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
-    return d;
 }
 
 // kind::f16, D = fp32, A = B = bf16, both K-major, M = 128, N = 128
@@ -89,9 +52,6 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a, uint64_t b
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
 }
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -103,10 +63,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
           "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr) : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
 // Warps 0-3 (128 threads) own the 128 TMEM lanes = the 128 points and run the arg-min

@@ -22,6 +22,7 @@
 
 namespace hira {
 
+int q8_refresh(const hira_index_t* ix, cudaStream_t s);
 int launch_assign_tc(const void* points, long long p_head_stride, const void* cents, const float* csq,
                      int n_heads, int n, int k, int dim, int32_t* out_idx, float* out_d2, cudaStream_t s);
 bool assign_tc_supported(int dtype, int n, int k, int dim);
@@ -701,7 +702,9 @@ static int build_impl(const hira_index_t* ix, const void* keys_v, const void* va
     set_used_kernel<<<(H + 127) / 128, 128, 0, s>>>(ix->used, H, ix->depth == 3 ? k2 * bf : k1,
                                                      ix->depth == 3 ? k2 : 0, n_keys);
     HIRA_CHECK_LAUNCH("set used launch");
-    return launch_radii<T>(ix, s);
+    rc = launch_radii<T>(ix, s);
+    if (rc != HIRA_OK) return rc;
+    return q8_refresh(ix, s);   // the int8 side copy of the children, when the index carries one
 }
 
 }  // namespace hira

@@ -380,6 +380,66 @@ __device__ __forceinline__ void load_vec(const T* v, float (&b)[NCH][8], int lan
     }
 }
 
+// ---------------------------------------------------------------------------
+// int8 side copy of a child row (D = 128), written by the 8 lanes of a group; see search_q8.cu.
+//   x        the lane's two chunks of the row in fp32 (values exactly as stored in the index)
+//   chan     per-channel scales s_i [128] followed by min_i s_i at [128]
+//   dst      the row's 128 bytes;  swz = slot & 7 permutes its 16-byte chunks
+//   meta     (step, err): k'_i = x_i / s_i, step = max |k'_i| / 127, k~_i = rint(k'_i / step),
+//            err >= ||k' - step k~||_2 + 2^-15 ||x||_2 / min_i s_i  (the second term covers the
+//            rounding of the canonical fp32 dot product for any query: ||q (.) s|| >= min s ||q||)
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void q8_write_row(const float (&x)[2][8], const float* __restrict__ chan, int8_t* dst,
+                                             float2* meta, int swz, int lane) {
+    float kp[2][8];
+    float amax = 0.f;
+    Acc2 nx{0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int c = lane + GROUP * i;
+        const float4 s0 = __ldg(reinterpret_cast<const float4*>(chan) + 2 * c);
+        const float4 s1 = __ldg(reinterpret_cast<const float4*>(chan) + 2 * c + 1);
+        const float sc[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            kp[i][e] = __fdiv_rn(x[i][e], sc[e]);
+            amax = fmaxf(amax, fabsf(kp[i][e]));
+        }
+        chunk_fma(nx, x[i], x[i]);
+    }
+    const unsigned gm = group_mask();
+    amax = fmaxf(amax, __shfl_xor_sync(gm, amax, 4));
+    amax = fmaxf(amax, __shfl_xor_sync(gm, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(gm, amax, 1));
+    const bool ok = amax > 0.f && amax < 3.0e38f;
+    const float step = ok ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    Acc2 ne{0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        float dlt[8];
+        uint32_t w[2] = {0u, 0u};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            float kq = ok ? rintf(__fdiv_rn(kp[i][e], step)) : 0.f;
+            kq = fminf(fmaxf(kq, -127.f), 127.f);
+            dlt[e] = __fmaf_rn(-kq, step, kp[i][e]);
+            w[e >> 2] |= ((uint32_t)(int)kq & 0xffu) << (8 * (e & 3));
+        }
+        chunk_fma(ne, dlt, dlt);
+        const int c = lane + GROUP * i;        // 8-element chunk of the row: half (c & 1) of 16-byte chunk c >> 1
+        const int off = (((c >> 1) ^ swz) << 4) + ((c & 1) << 3);
+        *reinterpret_cast<uint2*>(dst + off) = make_uint2(w[0], w[1]);
+    }
+    const float err2 = group_sum(__fadd_rn(ne.e, ne.o));
+    const float xsq = group_sum(__fadd_rn(nx.e, nx.o));
+    if (lane == 0) {
+        const float min_s = __ldg(chan + 128);
+        const float err = ok ? sqrtf(err2) * 1.001f + 3.1e-5f * sqrtf(xsq) / min_s
+                             : (amax > 0.f ? 3.0e38f : 0.f);    // a row that cannot be quantised is always a candidate
+        *meta = make_float2(step, err);
+    }
+}
+
 // non-negative floats order like their bit patterns
 __device__ __forceinline__ void atomic_max_nonneg(float* addr, float v) {
     atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));

@@ -1,0 +1,810 @@
+// Halfspace search with an int8 pre-filter on the tensor cores (D = 128, leaf rules >= / >).
+//
+// The streaming search kernel (search.cu) reads every child row of a kept parent in the
+// index dtype (256 B per bf16 key) and is instruction-issue bound on the dot products.  This
+// kernel reads a SIDE COPY of the children instead -- int8 rows of 128 B, quantised per row
+// after a per-channel rescale -- scores 128 rows at a time against the CTA's query heads
+// with tcgen05.mma (kind::i8, exact int32 accumulation in TMEM), and keeps as CANDIDATES the
+// rows whose score could reach the threshold given a rigorous bound on the quantisation
+// error.  Only the candidates (a few per cent) are then read in the index dtype and decided
+// by the canonical fp32 dot product, exactly as search.cu decides them: the emitted sets and
+// scores are bit-identical, the bytes per key roughly halve.
+//
+// Side copy (hira_index_t::children_q8, children_q8_meta, q8_chan_scale), per head:
+//   s_i   per-channel scale (rms of channel i over the stored keys), k'_i = k_i / s_i
+//   row   k~_i = rint(k'_i / step), step = max_i |k'_i| / 127, stored as int8 with the
+//         16-byte chunks of the row permuted for the 128-byte shared-memory swizzle
+//         (chunk j of slot r sits at chunk j ^ (r & 7)), so that a plain bulk copy of 128
+//         consecutive rows lands in the layout tcgen05.mma reads
+//   meta  (step, err) with err >= ||k' - step k~||_2 plus a share for the rounding of the
+//         canonical dot product
+// Query head: q' = q (.) s is split into two int8 terms, q' = c1 a1 + c2 a2 + r2.  Then
+//   q.k = step (c1 a1.k~ + c2 a2.k~) + step r2.k~ + q'.(k' - step k~)
+// and the last two terms are bounded by  B step + A err  (A = ||q'||, B = 127 ||r2||_1).
+//
+// Per CTA (one tile of <= 1024 child slots of one kv head, up to 4 query heads): warps 0-3
+// compute the gates exactly as search.cu does, then own the 128 TMEM lanes = the 128 rows of
+// a stage; lane 0 of warp 4 streams the needed 16 KB stages (+ 1 KB of meta) through a
+// 4-slot ring with cp.async.bulk (no multicast) and issues the MMAs.  Every mbarrier wait
+// is bounded; if one runs out the CTA falls back to treating every row of a kept parent as a
+// candidate, so the result is still exact.
+#include "common.cuh"
+#include "search_common.cuh"
+#include "tc_common.cuh"
+#include <math_constants.h>
+
+namespace hira {
+
+constexpr int Q8_DIM = 128;
+constexpr int Q8_STAGE_ROWS = 128;
+constexpr int Q8_STAGE_BYTES = Q8_STAGE_ROWS * Q8_DIM;    // 16 KB of int8 rows
+constexpr int Q8_META_BYTES = Q8_STAGE_ROWS * 8;          // (step, err) per row
+constexpr int Q8_SLOTS = 4;                               // stages in flight per CTA
+constexpr int Q8_MAX_STAGES = MAX_TILE_ROWS / Q8_STAGE_ROWS;   // 8
+constexpr int Q8_NCOL = 16;                               // accumulator columns per stage (N of the MMA)
+constexpr int Q8_TMEM_COLS = Q8_MAX_STAGES * Q8_NCOL;     // 128
+constexpr int Q8_THREADS = 160;                           // 4 worker warps + 1 producer/MMA warp
+constexpr int Q8_WORKERS = 128;
+constexpr int Q8_MAX_TP = 128;                            // parents per tile (bf >= 8)
+
+struct Q8Smem {   // offsets in the 1024-byte aligned dynamic shared memory
+    static constexpr int RING = 0;                                    // Q8_SLOTS stages of rows; later the candidates' scores
+    static constexpr int BQ = Q8_SLOTS * Q8_STAGE_BYTES;              // 16 x 128 int8 query terms (B operand)
+    static constexpr int META = BQ + 2048;                            // [Q8_MAX_STAGES][128] float2
+    static constexpr int CAND = META + Q8_MAX_STAGES * Q8_META_BYTES; // [1024] head masks
+    static constexpr int LIST = CAND + MAX_TILE_ROWS;                 // [1024] uint16 candidate rows, ascending
+    static constexpr int BAR = LIST + 2 * MAX_TILE_ROWS;              // full[Q8_SLOTS], done[Q8_MAX_STAGES], go
+    static constexpr int TMEM_SLOT = BAR + 8 * (Q8_SLOTS + Q8_MAX_STAGES + 1);
+    static constexpr int TOTAL = TMEM_SLOT + 16;
+};
+
+// kind::i8: D = int32, A = B = signed int8, both K-major, M = 128, N = 16
+constexpr uint32_t Q8_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(Q8_NCOL >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// plain (non-multicast) bulk copy global -> this CTA's shared memory, completion on an mbarrier
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void worker_sync() { asm volatile("bar.sync 1, %0;" ::"n"(Q8_WORKERS) : "memory"); }
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
+
+// block reductions over the 128 workers of GT values each (sum or max); every worker gets the results
+template <int GT, bool MAX>
+__device__ __forceinline__ void worker_reduce(float (&v)[GT], float (*s_red)[8], int warp, int wl) {
+#pragma unroll
+    for (int j = 0; j < GT; ++j) {
+#pragma unroll
+        for (int s = 16; s >= 1; s >>= 1) {
+            const float o = __shfl_xor_sync(0xffffffffu, v[j], s);
+            v[j] = MAX ? fmaxf(v[j], o) : v[j] + o;
+        }
+    }
+    worker_sync();   // s_red free again
+    if (wl == 0) {
+#pragma unroll
+        for (int j = 0; j < GT; ++j) s_red[warp][j] = v[j];
+    }
+    worker_sync();
+#pragma unroll
+    for (int j = 0; j < GT; ++j) {
+        const float a = s_red[0][j], b = s_red[1][j], c = s_red[2][j], d = s_red[3][j];
+        v[j] = MAX ? fmaxf(fmaxf(a, b), fmaxf(c, d)) : (a + b) + (c + d);
+    }
+}
+
+template <typename T, int GT, bool SCAN>
+__global__ void __launch_bounds__(Q8_THREADS, 3)
+search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const float2* __restrict__ k8_meta,
+                 const float* __restrict__ chan_scale) {
+    constexpr int NCH = 2;
+    constexpr int SEARCH_GROUPS = Q8_WORKERS / GROUP;  // 16
+    constexpr int PRE = 2;
+    extern __shared__ unsigned char q8_smem_raw[];
+    unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(q8_smem_raw) + 1023) & ~(uintptr_t)1023);
+    const uint32_t s_base = smem_u32(sm);
+    unsigned char* s_cand = sm + Q8Smem::CAND;
+    unsigned short* s_list = reinterpret_cast<unsigned short*>(sm + Q8Smem::LIST);
+    const float2* s_meta = reinterpret_cast<const float2*>(sm + Q8Smem::META);
+    uint32_t* s_cscore = reinterpret_cast<uint32_t*>(sm + Q8Smem::RING);   // after the last MMA: [candidate][GT]
+    const uint32_t bar_full = s_base + Q8Smem::BAR;                   // [Q8_SLOTS] stage landed
+    const uint32_t bar_done = bar_full + 8 * Q8_SLOTS;                // [Q8_MAX_STAGES] MMAs of the k-th stage complete
+    const uint32_t bar_go = bar_done + 8 * Q8_MAX_STAGES;             // gates known
+    volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(sm + Q8Smem::TMEM_SLOT);
+
+    __shared__ int s_pcount[Q8_MAX_TP];
+    __shared__ unsigned char s_pmask[Q8_MAX_TP], s_gpmask[Q8_MAX_TP];
+    __shared__ int s_qh[GT];
+    __shared__ float s_scale[GT], s_tau[GT];
+    __shared__ float s_qc[GT][4];   // c1, c2, A, B of each head
+    __shared__ float s_red[4][8];
+    __shared__ int s_nq, s_need, s_ncand, s_fail;
+    __shared__ uint32_t s_stat[GT][8];
+    __shared__ unsigned long long s_scan[SEARCH_GROUPS];
+    __shared__ __align__(16) float s_xkey[SCAN ? GROUP * NCH * 8 : 4];
+
+    const int TP = P.tile_parents;
+    const int bf = P.bf;
+    const int tile_rows = TP * bf;
+    const int tid = threadIdx.x;
+    const int lane = tid & (GROUP - 1);
+    const int grp = tid / GROUP;
+    const int warp = tid >> 5;
+    const int wl = tid & 31;
+    const bool worker = warp < 4;
+    const int chunk = blockIdx.x;
+    const int tile = blockIdx.y;
+    const int h = blockIdx.z;
+    const bool ge = P.flags & HIRA_GATE_GE;
+    const int leaf_mode = P.flags & (HIRA_LEAF_GE | HIRA_LEAF_GT);
+    const size_t cap_children = (size_t)P.cap_parents * bf;
+    const T* children = reinterpret_cast<const T*>(P.children) + (size_t)h * cap_children * P.dim;
+    const T* parents = reinterpret_cast<const T*>(P.parents) + (size_t)h * P.cap_parents * P.dim;
+
+    // ---- 1. query heads of this kv head handled by this CTA (as in search.cu) -------------
+    if (tid < GT * 8) (&s_stat[0][0])[tid] = 0;
+    int nq;
+    int qh_of[GT];
+    if (P.q2kv == nullptr) {
+        nq = P.group - chunk * GT;
+        nq = nq < 0 ? 0 : (nq > GT ? GT : nq);
+#pragma unroll
+        for (int j = 0; j < GT; ++j) qh_of[j] = h * P.group + chunk * GT + (j < nq ? j : 0);
+        if (tid < nq) s_qh[tid] = h * P.group + chunk * GT + tid;
+    } else {
+        if (warp == 0) {
+            int seen = 0;
+            for (int base = 0; base < P.n_qheads; base += 32) {
+                const int i = base + wl;
+                const bool m = (i < P.n_qheads) && (P.q2kv[i] == h);
+                const uint32_t b = __ballot_sync(0xffffffffu, m);
+                const int pos = seen + __popc(b & ((1u << wl) - 1u));
+                if (m && pos >= chunk * GT && pos < chunk * GT + GT) s_qh[pos - chunk * GT] = i;
+                seen += __popc(b);
+            }
+            if (wl == 0) {
+                int n = seen - chunk * GT;
+                s_nq = n < 0 ? 0 : (n > GT ? GT : n);
+            }
+        }
+        __syncthreads();
+        nq = s_nq;
+#pragma unroll
+        for (int j = 0; j < GT; ++j) qh_of[j] = s_qh[j < nq ? j : 0];
+    }
+    if (nq == 0) return;  // uniform over the CTA; nothing allocated yet
+
+    // ---- 0. barriers, tensor memory ----------------------------------------------------------
+    if (tid == 0) {
+        s_fail = 0;
+        s_need = 0;
+        s_ncand = 0;
+        for (int i = 0; i < Q8_SLOTS; ++i) mbar_init(bar_full + 8 * i, 1);
+        for (int i = 0; i < Q8_MAX_STAGES; ++i) mbar_init(bar_done + 8 * i, 1);
+        mbar_init(bar_go, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(s_base + Q8Smem::TMEM_SLOT), "r"(Q8_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *s_tmem;
+
+    const int tile_p0 = tile * TP;
+    const size_t tile_c0 = (size_t)tile_p0 * bf;
+    const int n_stage_tile = tile_rows / Q8_STAGE_ROWS;
+
+    if (!worker) {
+        // ======================= producer + MMA issuer (one thread) =========================
+        if (tid == Q8_WORKERS) {
+            bool failed = !mbar_wait(bar_go, 0);
+            const int need = failed ? 0 : *reinterpret_cast<volatile int*>(&s_need);
+            int order[Q8_MAX_STAGES];
+            int n = 0;
+#pragma unroll
+            for (int s = 0; s < Q8_MAX_STAGES; ++s)
+                if (s < n_stage_tile && ((need >> s) & 1)) order[n++] = s;
+            const int8_t* rows_g = k8 + ((size_t)h * cap_children + tile_c0) * Q8_DIM;
+            const float2* meta_g = k8_meta + (size_t)h * cap_children + tile_c0;
+            int issued = 0;
+            for (int k = 0; k < n && !failed; ++k) {
+                while (issued < n && issued < k + Q8_SLOTS) {
+                    // the slot held stage issued - Q8_SLOTS: free once its MMAs are complete
+                    if (issued >= Q8_SLOTS && !mbar_wait(bar_done + 8 * (issued - Q8_SLOTS), 0)) { failed = true; break; }
+                    const int slot = issued % Q8_SLOTS;
+                    const uint32_t full = bar_full + 8 * slot;
+                    mbar_expect_tx(full, Q8_STAGE_BYTES + Q8_META_BYTES);
+                    bulk_load(s_base + Q8Smem::RING + slot * Q8_STAGE_BYTES, rows_g + (size_t)order[issued] * Q8_STAGE_BYTES,
+                              Q8_STAGE_BYTES, full);
+                    bulk_load(s_base + Q8Smem::META + issued * Q8_META_BYTES, meta_g + (size_t)order[issued] * Q8_STAGE_ROWS,
+                              Q8_META_BYTES, full);
+                    ++issued;
+                }
+                if (failed) break;
+                const int slot = k % Q8_SLOTS;
+                if (!mbar_wait(bar_full + 8 * slot, (k / Q8_SLOTS) & 1)) { failed = true; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a0 = s_base + Q8Smem::RING + slot * Q8_STAGE_BYTES, b0 = s_base + Q8Smem::BQ;
+#pragma unroll
+                for (int ks = 0; ks < Q8_DIM / 32; ++ks)
+                    umma_i8(tmem + k * Q8_NCOL, umma_desc(a0 + ks * 32), umma_desc(b0 + ks * 32), Q8_IDESC, ks > 0 ? 1u : 0u);
+                umma_commit(bar_done + 8 * k);
+            }
+            if (failed) {
+                *reinterpret_cast<volatile int*>(&s_fail) = 1;
+                // let copies that may still be in flight land before the ring is reused (bounded)
+                for (int i = 0; i < issued && i < Q8_SLOTS; ++i) mbar_wait(bar_full + 8 * i, ((issued - 1 - i) / Q8_SLOTS) & 1);
+            }
+        }
+    } else {
+        // ================================ workers (128 threads) ================================
+        const int my_head = HeadReduce<GT>::head_of_lane(lane);
+        const bool head_on = my_head < nq;
+        const bool has_qn = false;   // this kernel is only launched for unit queries (qnorm == NULL)
+        const int used_parents = P.used[h * 4 + 0];
+        const int used_gp = P.used[h * 4 + 1];
+        const int g0 = P.tile_gp_shift >= 0 ? (tile >> P.tile_gp_shift)
+                                            : (P.tile_gp_shift == -1 ? tile * P.ng : div_bf(tile * TP, bf, P.bf_magic));
+        const int ng = P.ng;
+        int my_qh = qh_of[0];
+#pragma unroll
+        for (int j = 1; j < GT; ++j)
+            if (my_head == j) my_qh = qh_of[j];
+        const float my_tau = head_on ? P.tau[my_qh] : 0.f;
+        const float my_qn = 1.f;
+        if (tid < nq) {
+            s_scale[tid] = P.scaling ? P.scaling[s_qh[tid]] : 1.0f;
+            s_tau[tid] = P.tau[s_qh[tid]];
+        }
+        float qreg[GT][NCH][8];
+#pragma unroll
+        for (int j = 0; j < GT; ++j) {
+            if (j < nq) {
+                load_vec_f32<NCH>(P.q + (size_t)qh_of[j] * P.dim, qreg[j], lane, P.dim);
+            } else {
+#pragma unroll
+                for (int i = 0; i < NCH; ++i)
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) qreg[j][i][e] = 0.f;
+            }
+        }
+        // gate inputs, issued together (as in search.cu)
+        RawChunk<T> graw[NCH];
+        float grad = 0.f;
+        const bool gp_mine = P.depth == 3 && grp < ng && (g0 + grp) < P.cap_gp;
+        {
+            const T* gps = reinterpret_cast<const T*>(P.gps) + (size_t)h * P.cap_gp * P.dim;
+            load_row_raw<T, NCH>(graw, gps + (size_t)(g0 + grp) * P.dim, lane, P.dim, gp_mine);
+            if (gp_mine) grad = P.gp_radii[(size_t)h * P.cap_gp + g0 + grp];
+        }
+        RawChunk<T> praw[PRE][NCH];
+        float prad[PRE];
+        int pcnt[PRE], pgc[PRE];
+#pragma unroll
+        for (int u = 0; u < PRE; ++u) {
+            const int i = u * SEARCH_GROUPS + grp;
+            const int p = tile_p0 + i;
+            const bool in = (i < TP) && (p < P.cap_parents);
+            load_row_raw<T, NCH>(praw[u], parents + (size_t)p * P.dim, lane, P.dim, in);
+            prad[u] = in ? P.parent_radii[(size_t)h * P.cap_parents + p] : 0.f;
+            pcnt[u] = in ? P.child_counts[(size_t)h * P.cap_parents + p] : 0;
+            pgc[u] = (in && P.depth == 3) ? P.gp_counts[(size_t)h * P.cap_gp + g0 + div_bf(p - g0 * bf, bf, P.bf_magic)] : 0;
+        }
+        const bool do_scan = SCAN && chunk == 0;
+        float psq[PRE];
+        if (do_scan) {
+            if constexpr (SCAN) {
+                if (tid < GROUP) {
+                    float xk[NCH][8];
+                    load_vec<T, NCH>(reinterpret_cast<const T*>(P.scan_key) + (size_t)h * P.scan_key_stride, xk, lane, P.dim);
+#pragma unroll
+                    for (int ci = 0; ci < NCH; ++ci)
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) s_xkey[(lane * NCH + ci) * 8 + e] = xk[ci][e];
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < PRE; ++u) {
+                const int p = tile_p0 + u * SEARCH_GROUPS + grp;
+                psq[u] = (u * SEARCH_GROUPS + grp < TP && p < P.cap_parents) ? P.parent_sqnorm[(size_t)h * P.cap_parents + p] : 0.f;
+            }
+        }
+        unsigned long long scan_best = ~0ull;
+        // candidate masks start empty (rows of stages that are not scored stay so)
+        reinterpret_cast<uint2*>(s_cand)[tid] = make_uint2(0u, 0u);
+
+        // ---- 2. the query heads as two int8 terms each (B operand of the MMA) ----------------
+        {
+            const float cs = chan_scale[(size_t)h * HIRA_Q8_CHAN + tid];   // worker t owns channel t
+            float qp[GT], v[GT];
+#pragma unroll
+            for (int j = 0; j < GT; ++j) {
+                qp[j] = j < nq ? P.q[(size_t)qh_of[j] * P.dim + tid] * cs : 0.f;
+                v[j] = fabsf(qp[j]);
+            }
+            worker_reduce<GT, true>(v, s_red, warp, wl);
+            float c1[GT], a1[GT], r1[GT];
+#pragma unroll
+            for (int j = 0; j < GT; ++j) {
+                c1[j] = v[j] > 0.f ? v[j] / 127.0f : 1.0f;
+                a1[j] = fminf(fmaxf(rintf(qp[j] / c1[j]), -127.f), 127.f);
+                r1[j] = __fmaf_rn(-a1[j], c1[j], qp[j]);
+                v[j] = fabsf(r1[j]);
+            }
+            worker_reduce<GT, true>(v, s_red, warp, wl);
+            float c2[GT], a2[GT], l1[GT], sq[GT];
+#pragma unroll
+            for (int j = 0; j < GT; ++j) {
+                c2[j] = v[j] > 0.f ? v[j] / 127.0f : 1.0f;
+                a2[j] = fminf(fmaxf(rintf(r1[j] / c2[j]), -127.f), 127.f);
+                l1[j] = fabsf(__fmaf_rn(-a2[j], c2[j], r1[j]));
+                sq[j] = qp[j] * qp[j];
+            }
+            worker_reduce<GT, false>(l1, s_red, warp, wl);
+            worker_reduce<GT, false>(sq, s_red, warp, wl);
+            // B operand: row n = 2 * head + term, 128 int8, 16-byte chunks swizzled by the row; rows of
+            // absent heads are zero
+            const int ch16 = tid >> 4, byte = tid & 15;
+#pragma unroll
+            for (int n = 0; n < Q8_NCOL; ++n) {
+                float val = 0.f;
+                if (n < 2 * GT) val = (n & 1) ? a2[n >> 1] : a1[n >> 1];
+                const int off = (n >> 3) * 1024 + (n & 7) * 128 + ((ch16 ^ (n & 7)) << 4) + byte;
+                reinterpret_cast<signed char*>(sm + Q8Smem::BQ)[off] = (signed char)(int)val;
+            }
+            if (tid < GT) {
+                const int j = tid;
+                const float A = sqrtf(sq[j]) * 1.001f;
+                s_qc[j][0] = c1[j];
+                s_qc[j][1] = c2[j];
+                s_qc[j][2] = A;
+                // |r2 . k~| <= ||r2||_1 * 127, plus the rounding of the split itself
+                s_qc[j][3] = 127.0f * l1[j] * 1.001f + A * (127.0f * 11.32f * 3.9e-6f);
+            }
+            // the generic-proxy writes of the B operand must be visible to the tensor core
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        }
+
+        bool tile_empty;
+        if (P.depth == 3) tile_empty = g0 >= used_gp;
+        else tile_empty = tile_p0 >= used_parents;
+        const uint32_t allmask = (1u << nq) - 1u;
+
+        if (!tile_empty) {
+            // ---- 3a. grandparent gate ----------------------------------------------------
+            if (P.depth == 3) {
+                const T* gps = reinterpret_cast<const T*>(P.gps) + (size_t)h * P.cap_gp * P.dim;
+                for (int i0 = 0; i0 < ng; i0 += SEARCH_GROUPS) {
+                    const int i = i0 + grp;
+                    const int g = g0 + i;
+                    const bool valid = (i < ng) && (g < used_gp);
+                    float d, r;
+                    if (i0 == 0) {
+                        d = gate_dot_raw<T, GT, NCH>(graw, qreg, lane);
+                        r = grad;
+                    } else {
+                        d = gate_dot<T, GT, NCH>(gps + (size_t)g * P.dim, qreg, lane, P.dim, valid);
+                        r = valid ? P.gp_radii[(size_t)h * P.cap_gp + g] : 0.f;
+                    }
+                    const bool keep = valid && head_on && gate_keep(d, r, my_qn, has_qn, my_tau, ge);
+                    const uint32_t b = __ballot_sync(0xffffffffu, keep);
+                    const uint32_t m = head_mask_from_ballot<GT>(b, tid);
+                    if (lane == 0 && i < ng) {
+                        s_gpmask[i] = (unsigned char)m;
+                        if (valid && P.stats && tile_p0 == g0 * bf) {
+                            for (int jj = 0; jj < nq; ++jj) {
+                                atomicAdd(&s_stat[jj][0], 1u);
+                                if ((m >> jj) & 1u) atomicAdd(&s_stat[jj][1], 1u);
+                            }
+                        }
+                    }
+                }
+            }
+            worker_sync();
+
+            // ---- 3b. parent gate -----------------------------------------------------------
+            auto gate_parent = [&](int i0, float d, float r, int cnt, int gc, float scan_s) {
+                const int i = i0 + grp;
+                const int p = tile_p0 + i;
+                const bool in = (i < TP) && (p < P.cap_parents);
+                bool valid = in;
+                uint32_t gm = allmask;
+                if (in) {
+                    if (P.depth == 3) {
+                        const int g = g0 + div_bf(p - g0 * bf, bf, P.bf_magic);
+                        valid = (g < used_gp) && ((p - g * bf) < gc);
+                        gm = s_gpmask[g - g0];
+                    } else {
+                        valid = p < used_parents;
+                    }
+                }
+                if (do_scan && valid) {
+                    const unsigned long long key = ((unsigned long long)order_key(scan_s) << 32) | (uint32_t)p;
+                    if (key < scan_best) scan_best = key;
+                }
+                const bool work = valid && gm != 0;
+                const bool keep = work && head_on && ((gm >> my_head) & 1u) && gate_keep(d, r, my_qn, has_qn, my_tau, ge);
+                const uint32_t b = __ballot_sync(0xffffffffu, keep);
+                const uint32_t m = head_mask_from_ballot<GT>(b, tid);
+                if (lane == 0 && i < TP) {
+                    cnt = valid ? (cnt > bf ? bf : cnt) : 0;
+                    s_pmask[i] = (unsigned char)m;
+                    s_pcount[i] = cnt;
+                    if (work && P.stats) {
+                        atomicAdd(&s_stat[0][7], 1u);
+                        if (m != 0) atomicAdd(&s_stat[0][6], (uint32_t)cnt);
+                        for (int jj = 0; jj < nq; ++jj) {
+                            if ((gm >> jj) & 1u) atomicAdd(&s_stat[jj][2], 1u);
+                            if ((m >> jj) & 1u) {
+                                atomicAdd(&s_stat[jj][3], 1u);
+                                atomicAdd(&s_stat[jj][4], (uint32_t)cnt);
+                            }
+                        }
+                    }
+                }
+            };
+            auto scan_score = [&](const RawChunk<T> (&raw)[NCH], float sqn) -> float {
+                if constexpr (SCAN) {
+                    Acc2 acc{0.f, 0.f};
+#pragma unroll
+                    for (int ci = 0; ci < NCH; ++ci) {
+                        float a[8], xk[8];
+                        to_float(raw[ci], a);
+                        const float4 x0 = *reinterpret_cast<const float4*>(&s_xkey[(lane * NCH + ci) * 8]);
+                        const float4 x1 = *reinterpret_cast<const float4*>(&s_xkey[(lane * NCH + ci) * 8 + 4]);
+                        xk[0] = x0.x; xk[1] = x0.y; xk[2] = x0.z; xk[3] = x0.w;
+                        xk[4] = x1.x; xk[5] = x1.y; xk[6] = x1.z; xk[7] = x1.w;
+                        chunk_fma(acc, a, xk);
+                    }
+                    const float d = group_sum(__fadd_rn(acc.e, acc.o));
+                    return __fsub_rn(sqn, __fmul_rn(2.0f, d));
+                } else {
+                    return 0.f;
+                }
+            };
+#pragma unroll
+            for (int u = 0; u < PRE; ++u) {
+                if (u * SEARCH_GROUPS < TP) {
+                    float ss = 0.f;
+                    if (do_scan) ss = scan_score(praw[u], psq[u]);
+                    gate_parent(u * SEARCH_GROUPS, gate_dot_raw<T, GT, NCH>(praw[u], qreg, lane), prad[u], pcnt[u], pgc[u], ss);
+                }
+            }
+            for (int i0 = PRE * SEARCH_GROUPS; i0 < TP; i0 += SEARCH_GROUPS) {
+                const int p = tile_p0 + i0 + grp;
+                const bool in = (i0 + grp < TP) && (p < P.cap_parents);
+                const float d = gate_dot<T, GT, NCH>(parents + (size_t)p * P.dim, qreg, lane, P.dim, in);
+                const float r = in ? P.parent_radii[(size_t)h * P.cap_parents + p] : 0.f;
+                const int cnt = in ? P.child_counts[(size_t)h * P.cap_parents + p] : 0;
+                const int gc = (in && P.depth == 3) ? P.gp_counts[(size_t)h * P.cap_gp + g0 + div_bf(p - g0 * bf, bf, P.bf_magic)] : 0;
+                float ss = 0.f;
+                if (do_scan) {
+                    RawChunk<T> raw[NCH];
+                    load_row_raw<T, NCH>(raw, parents + (size_t)p * P.dim, lane, P.dim, in);
+                    ss = scan_score(raw, in ? P.parent_sqnorm[(size_t)h * P.cap_parents + p] : 0.f);
+                }
+                gate_parent(i0, d, r, cnt, gc, ss);
+            }
+            if (do_scan && lane == 0) s_scan[grp] = scan_best;
+            worker_sync();
+
+            // ---- 4. stages that hold rows of a kept parent; nearest parent of the tile -------
+            if (tid < n_stage_tile) {
+                const int p_lo = div_bf(tid * Q8_STAGE_ROWS, bf, P.bf_magic);
+                int p_hi = div_bf(tid * Q8_STAGE_ROWS + Q8_STAGE_ROWS - 1, bf, P.bf_magic);
+                p_hi = p_hi >= TP ? TP - 1 : p_hi;
+                bool any = false;
+                for (int i = p_lo; i <= p_hi; ++i) {
+                    // rows of parent i inside this stage that are filled
+                    const int first = i * bf > tid * Q8_STAGE_ROWS ? 0 : tid * Q8_STAGE_ROWS - i * bf;
+                    any = any || (s_pmask[i] != 0 && s_pcount[i] > first);
+                }
+                if (any) atomicOr(&s_need, 1 << tid);
+            } else if (warp == 1 && do_scan) {
+                unsigned long long best = wl < SEARCH_GROUPS ? s_scan[wl] : ~0ull;
+#pragma unroll
+                for (int sft = 16; sft >= 1; sft >>= 1) {
+                    const unsigned long long o = __shfl_xor_sync(0xffffffffu, best, sft);
+                    best = o < best ? o : best;
+                }
+                if (wl == 0 && best != ~0ull) atomicMin(P.scan_out + h, best);
+            }
+        }
+        worker_sync();   // s_need, s_pmask, s_pcount, the B operand and the cleared candidate masks are complete
+        if (tid == 0) mbar_arrive(bar_go);
+        const int need = *reinterpret_cast<volatile int*>(&s_need);
+
+        // ---- 5. candidates: approximate scores out of tensor memory ----------------------------
+        {
+            float qc[GT][4], tauj[GT];
+#pragma unroll
+            for (int j = 0; j < GT; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) qc[j][e] = s_qc[j][e];
+                tauj[j] = j < nq ? s_tau[j] : CUDART_INF_F;
+            }
+            int k = 0;
+            bool failed = false;
+            for (int s = 0; s < n_stage_tile; ++s) {   // uniform over the workers
+                if (!((need >> s) & 1)) continue;
+                // warp-uniform outcome: tcgen05.ld below is a warp-wide instruction
+                const bool ok = mbar_wait(bar_done + 8 * k, 0) && !*reinterpret_cast<volatile int*>(&s_fail);
+                if (!__all_sync(0xffffffffu, ok)) {
+                    failed = true;
+                    if (wl == 0) *reinterpret_cast<volatile int*>(&s_fail) = 1;
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint32_t acc[16];
+                tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + k * Q8_NCOL, acc);
+                const int r = s * Q8_STAGE_ROWS + tid;
+                const int pl = div_bf(r, bf, P.bf_magic);
+                const uint32_t pm = s_pmask[pl];
+                const bool filled = (r - pl * bf) < s_pcount[pl];
+                const float2 mt = s_meta[k * Q8_STAGE_ROWS + tid];   // (step, err)
+                uint32_t cm = 0;
+#pragma unroll
+                for (int j = 0; j < GT; ++j) {
+                    const float d1 = __int2float_rn((int)acc[2 * j]), d2 = __int2float_rn((int)acc[2 * j + 1]);
+                    const float approx = mt.x * __fmaf_rn(qc[j][0], d1, qc[j][1] * d2);
+                    const float margin = __fmaf_rn(qc[j][2], mt.y, qc[j][3] * mt.x);
+                    const float upper = approx + margin * 1.001f + 1e-6f + 1e-6f * fabsf(approx);
+                    if (upper >= tauj[j]) cm |= 1u << j;
+                }
+                cm = filled ? (cm & pm) : 0u;
+                s_cand[r] = (unsigned char)cm;
+                if (cm) {   // the exact pass reads this row in the index dtype: start it towards L2 now
+                    const char* row = reinterpret_cast<const char*>(children + (tile_c0 + r) * P.dim);
+                    prefetch_l2(row);
+                    if (sizeof(T) * Q8_DIM > 128) prefetch_l2(row + 128);
+                    if (sizeof(T) * Q8_DIM > 256) { prefetch_l2(row + 256); prefetch_l2(row + 384); }
+                }
+                ++k;
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            worker_sync();
+            if (*reinterpret_cast<volatile int*>(&s_fail)) {   // the same for every worker after the barrier
+                // a bounded wait ran out: every filled row of a kept parent is a candidate (exact, only slower)
+                for (int r = tid; r < tile_rows; r += Q8_WORKERS) {
+                    const int pl = div_bf(r, bf, P.bf_magic);
+                    s_cand[r] = ((r - pl * bf) < s_pcount[pl] && !tile_empty) ? s_pmask[pl] : 0;
+                }
+                worker_sync();
+            }
+        }
+
+        // ---- 6. ascending list of candidate rows ------------------------------------------------
+        if (warp == 0) {
+            int n = 0;
+            for (int base = 0; base < tile_rows; base += 32) {
+                const bool m = s_cand[base + wl] != 0;
+                const uint32_t b = __ballot_sync(0xffffffffu, m);
+                if (m) s_list[n + __popc(b & ((1u << wl) - 1u))] = (unsigned short)(base + wl);
+                n += __popc(b);
+            }
+            if (wl == 0) s_ncand = n;
+        }
+        worker_sync();
+        const int ncand = s_ncand;
+
+        // ---- 7. exact scores of the candidates, canonical arithmetic ---------------------------
+        {
+            const bool writer = HeadReduce<GT>::is_writer(lane);
+            const float leaf_thr = (leaf_mode == HIRA_LEAF_GT) ? nextafterf(my_tau, CUDART_INF_F) : my_tau;
+            const int iters = (ncand + 2 * SEARCH_GROUPS - 1) / (2 * SEARCH_GROUPS);   // uniform over the workers
+            for (int it = 0; it < iters; ++it) {
+                const int e0 = it * 2 * SEARCH_GROUPS + grp, e1 = e0 + SEARCH_GROUPS;
+                const bool v0 = e0 < ncand, v1 = e1 < ncand;
+                const int r0 = v0 ? s_list[e0] : 0, r1 = v1 ? s_list[e1] : 0;
+                RawChunk<T> raw0[NCH], raw1[NCH];
+#pragma unroll
+                for (int ci = 0; ci < NCH; ++ci) {
+                    raw0[ci] = v0 ? load_chunk_stream<T>(children + (tile_c0 + r0) * P.dim, lane + GROUP * ci) : zero_chunk<T>();
+                    raw1[ci] = v1 ? load_chunk_stream<T>(children + (tile_c0 + r1) * P.dim, lane + GROUP * ci) : zero_chunk<T>();
+                }
+                const float d0 = gate_dot_raw<T, GT, NCH>(raw0, qreg, lane);
+                const float d1 = gate_dot_raw<T, GT, NCH>(raw1, qreg, lane);
+                if (writer) {
+                    if (v0) {
+                        const bool em = head_on && ((s_cand[r0] >> my_head) & 1u) && d0 >= leaf_thr;
+                        s_cscore[e0 * GT + my_head] = em ? __float_as_uint(d0) : NOT_EMITTED;
+                    }
+                    if (v1) {
+                        const bool em = head_on && ((s_cand[r1] >> my_head) & 1u) && d1 >= leaf_thr;
+                        s_cscore[e1 * GT + my_head] = em ? __float_as_uint(d1) : NOT_EMITTED;
+                    }
+                }
+            }
+        }
+        worker_sync();
+
+        // ---- 8. ordered compaction, one warp per head -------------------------------------------
+        if (warp < nq) {
+            const int j = warp;
+            const int qh = s_qh[j];
+            const float scale = s_scale[j];
+            const size_t out_base = (size_t)qh * cap_children + tile_c0;
+            int offset = 0;
+            for (int base = 0; base < ncand; base += 32) {
+                const int e = base + wl;
+                const uint32_t bits = e < ncand ? s_cscore[e * GT + j] : NOT_EMITTED;
+                const bool k = bits != NOT_EMITTED;
+                const uint32_t b = __ballot_sync(0xffffffffu, k);
+                if (k) {
+                    const int pos = offset + __popc(b & ((1u << wl) - 1u));
+                    P.out_idx[out_base + pos] = (int32_t)(tile_c0 + s_list[e]);
+                    P.out_score[out_base + pos] = __fmul_rn(__uint_as_float(bits), scale);
+                }
+                offset += __popc(b);
+            }
+            if (wl == 0) {
+                P.out_count[(size_t)qh * P.n_tiles + tile] = offset;
+                if (P.stats) {
+                    uint32_t* st = P.stats + (size_t)qh * HIRA_SEARCH_STATS;
+                    for (int k = 0; k < 8; ++k)
+                        if (k != 5 && s_stat[j][k]) atomicAdd(st + k, s_stat[j][k]);
+                    if (offset) atomicAdd(st + 5, (uint32_t)offset);
+                    if (j == 0) {
+                        if (ncand) atomicAdd(st + 8, (uint32_t)ncand);                           // rows re-read in the index dtype
+                        if (need) atomicAdd(st + 9, (uint32_t)(__popc(need) * Q8_STAGE_ROWS));   // int8 rows scored
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- 9. tensor memory back ----------------------------------------------------------------------
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 4) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(Q8_TMEM_COLS) : "memory");
+    }
+}
+
+template <typename T, int GT, bool SCAN>
+static int launch_q8(SearchParams P, int chunks, const hira_index_t* ix, cudaStream_t stream) {
+    auto kern = search_q8_kernel<T, GT, SCAN>;
+    const size_t smem = Q8Smem::TOTAL + 1024;
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+        set_error("hira_search (int8 pre-filter): cudaFuncSetAttribute(%zu B smem): %s", smem, cudaGetErrorString(e));
+        return HIRA_ERR_CUDA;
+    }
+    P.n_chunks = chunks;
+    HIRA_CHECK_ARG(P.n_tiles <= 65535 && P.n_heads <= 65535, HIRA_ERR_SHAPE,
+                   "hira_search: %d tiles x %d heads exceed the grid limits", P.n_tiles, P.n_heads);
+    dim3 grid((unsigned)chunks, (unsigned)P.n_tiles_active, (unsigned)P.n_heads);
+    kern<<<grid, Q8_THREADS, smem, stream>>>(P, reinterpret_cast<const int8_t*>(ix->children_q8),
+                                            reinterpret_cast<const float2*>(ix->children_q8_meta), ix->q8_chan_scale);
+    HIRA_CHECK_LAUNCH("hira_search (int8 pre-filter) launch");
+    return HIRA_OK;
+}
+
+template <typename T, int GT>
+static int launch_q8_scan(const SearchParams& P, int chunks, const hira_index_t* ix, cudaStream_t stream) {
+    if (P.scan_out != nullptr) return launch_q8<T, GT, true>(P, chunks, ix, stream);
+    return launch_q8<T, GT, false>(P, chunks, ix, stream);
+}
+
+bool search_q8_applicable(const hira_index_t* ix, const SearchParams& P) {
+    if (!ix->children_q8 || !ix->children_q8_meta || !ix->q8_chan_scale) return false;
+    if (ix->dim != Q8_DIM || P.qnorm != nullptr || P.out_dense != nullptr || P.out_idx == nullptr) return false;
+    if ((P.flags & (HIRA_LEAF_GE | HIRA_LEAF_GT)) == 0) return false;           // every child is emitted: nothing to filter
+    const int tile_rows = P.tile_parents * P.bf;
+    if (P.bf < 8 || P.tile_parents > Q8_MAX_TP || tile_rows % Q8_STAGE_ROWS != 0 || tile_rows > MAX_TILE_ROWS) return false;
+    if (P.cap_parents % P.tile_parents != 0) return false;                        // whole tiles only
+    return true;
+}
+
+int launch_search_q8(const SearchParams& P, const hira_index_t* ix, int max_group, cudaStream_t stream) {
+    int gt = 1;
+    while (gt < max_group && gt < 4) gt <<= 1;
+    const int chunks = (max_group + gt - 1) / gt;
+    const bool bf16 = ix->dtype == HIRA_BF16;
+    switch (gt) {
+        case 1: return bf16 ? launch_q8_scan<__nv_bfloat16, 1>(P, chunks, ix, stream) : launch_q8_scan<float, 1>(P, chunks, ix, stream);
+        case 2: return bf16 ? launch_q8_scan<__nv_bfloat16, 2>(P, chunks, ix, stream) : launch_q8_scan<float, 2>(P, chunks, ix, stream);
+        default: return bf16 ? launch_q8_scan<__nv_bfloat16, 4>(P, chunks, ix, stream) : launch_q8_scan<float, 4>(P, chunks, ix, stream);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Building and maintaining the side copy.
+// ---------------------------------------------------------------------------
+// per head: rms of every channel over a strided sample of the filled child slots -> s_i, min_i s_i
+template <typename T>
+__global__ void q8_chan_scale_kernel(const hira_index_t ix) {
+    const int h = blockIdx.x;
+    const int c = threadIdx.x;   // channel
+    const size_t capC = (size_t)ix.cap_parents * ix.bf;
+    const T* rows = reinterpret_cast<const T*>(ix.children) + (size_t)h * capC * Q8_DIM;
+    const int32_t* s2t = ix.slot2token ? ix.slot2token + (size_t)h * capC : nullptr;
+    const int32_t* cc = ix.child_counts + (size_t)h * ix.cap_parents;
+    const size_t n_slots = (size_t)(ix.depth == 3 ? ix.used[h * 4 + 1] * ix.bf : ix.used[h * 4 + 0]) * ix.bf;
+    const size_t stride = n_slots > 16384 ? n_slots / 8192 : 1;
+    float sum = 0.f;
+    int cnt = 0;
+    for (size_t r = 0; r < n_slots; r += stride) {
+        const bool filled = s2t ? s2t[r] >= 0 : (int)(r % ix.bf) < cc[r / ix.bf];
+        if (!filled) continue;
+        const float v = sizeof(T) == 2 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(rows)[r * Q8_DIM + c])
+                                       : reinterpret_cast<const float*>(rows)[r * Q8_DIM + c];
+        sum = __fmaf_rn(v, v, sum);
+        ++cnt;
+    }
+    float s = cnt > 0 ? sqrtf(sum / (float)cnt) : 1.f;
+    if (!(s > 1e-20f) || !(s < 1e20f)) s = 1.f;
+    __shared__ float s_min[4];
+    float m = s;
+#pragma unroll
+    for (int sft = 16; sft >= 1; sft >>= 1) m = fminf(m, __shfl_xor_sync(0xffffffffu, m, sft));
+    if ((c & 31) == 0) s_min[c >> 5] = m;
+    __syncthreads();
+    float* out = ix.q8_chan_scale + (size_t)h * HIRA_Q8_CHAN;
+    out[c] = s;
+    if (c == 0) out[Q8_DIM] = fminf(fminf(s_min[0], s_min[1]), fminf(s_min[2], s_min[3]));
+}
+
+// one 8-lane group per child slot: quantise the row (see q8_write_row in common.cuh)
+template <typename T>
+__global__ void q8_quantize_kernel(const hira_index_t ix) {
+    const int lane = threadIdx.x & (GROUP - 1);
+    const size_t capC = (size_t)ix.cap_parents * ix.bf;
+    const size_t w = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) / GROUP;   // (head, slot)
+    if (w >= (size_t)ix.n_heads * capC) return;
+    const int h = (int)(w / capC);
+    const size_t slot = w % capC;
+    const T* row = reinterpret_cast<const T*>(ix.children) + w * Q8_DIM;
+    float x[2][8];
+    load_vec<T, 2>(row, x, lane, Q8_DIM);
+    q8_write_row(x, ix.q8_chan_scale + (size_t)h * HIRA_Q8_CHAN, reinterpret_cast<int8_t*>(ix.children_q8) + w * Q8_DIM,
+                 reinterpret_cast<float2*>(ix.children_q8_meta) + w, (int)(slot & 7), lane);
+}
+
+int q8_refresh(const hira_index_t* ix, cudaStream_t s) {
+    if (!ix->children_q8) return HIRA_OK;
+    HIRA_CHECK_ARG(ix->dim == Q8_DIM && ix->children_q8_meta && ix->q8_chan_scale, HIRA_ERR_ARG,
+                   "the int8 side copy needs dim == 128 and its meta / channel-scale arrays");
+    const size_t rows = (size_t)ix->n_heads * ix->cap_parents * ix->bf;
+    const unsigned blocks = (unsigned)((rows * GROUP + 255) / 256);
+    if (ix->dtype == HIRA_BF16) {
+        q8_chan_scale_kernel<__nv_bfloat16><<<ix->n_heads, Q8_DIM, 0, s>>>(*ix);
+        q8_quantize_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(*ix);
+    } else {
+        q8_chan_scale_kernel<float><<<ix->n_heads, Q8_DIM, 0, s>>>(*ix);
+        q8_quantize_kernel<float><<<blocks, 256, 0, s>>>(*ix);
+    }
+    HIRA_CHECK_LAUNCH("int8 side copy launch");
+    return HIRA_OK;
+}
+
+}  // namespace hira
+
+extern "C" int hira_q8_refresh(const hira_index_t* ix, void* stream) {
+    int rc = hira::validate_index(ix, false);
+    if (rc != HIRA_OK) return rc;
+    HIRA_CHECK_ARG(ix->children_q8 != nullptr, HIRA_ERR_ARG, "hira_q8_refresh: the index has no int8 side copy");
+    return hira::q8_refresh(ix, reinterpret_cast<cudaStream_t>(stream));
+}

@@ -17,7 +17,8 @@ from . import _lib as L
 
 class IndexState:
     def __init__(self, *, n_heads: int, dim: int, vdim: int, bf: int, depth: int, cap_parents: int,
-                 dtype: torch.dtype, vdtype: Optional[torch.dtype], device, with_values: bool = True):
+                 dtype: torch.dtype, vdtype: Optional[torch.dtype], device, with_values: bool = True,
+                 int8_copy: Optional[bool] = None):
         if depth not in (2, 3):
             raise ValueError(f"Unsupported depth {depth}")
         self.n_heads, self.dim, self.vdim, self.bf, self.depth = n_heads, dim, vdim if with_values else 0, bf, depth
@@ -47,6 +48,19 @@ class IndexState:
         else:
             self.grand_parents = self.gp_radii = self.gp_sqnorm = self.gp_counts = None
         self.used = z((n_heads, 4), dtype=torch.int32, device=dev)
+        # int8 side copy of the children for the tensor-core pre-filter of the search (D = 128):
+        # +50 % on the bf16 keys' memory (128 B + 8 B per slot), about half the search's traffic
+        if int8_copy is None:
+            int8_copy = dim == 128 and self.device.type == "cuda"
+        if int8_copy and dim != 128:
+            raise ValueError("the int8 side copy needs dim == 128")
+        self.int8_copy = bool(int8_copy)
+        if self.int8_copy:
+            self.children_q8 = z((n_heads, capC, 128), dtype=torch.int8, device=dev)
+            self.children_q8_meta = z((n_heads, capC, 2), dtype=torch.float32, device=dev)
+            self.q8_chan_scale = torch.ones((n_heads, L.Q8_CHAN), dtype=torch.float32, device=dev)
+        else:
+            self.children_q8 = self.children_q8_meta = self.q8_chan_scale = None
         self.status = z((1,), dtype=torch.int32, device=dev)
         self._struct = None
         self._active_parents = 0
@@ -54,6 +68,7 @@ class IndexState:
 
     ARRAYS = ("children", "values", "slot2token", "parents", "parent_radii", "parent_sqnorm", "child_counts",
               "grand_parents", "gp_radii", "gp_sqnorm", "gp_counts", "used")
+    Q8_ARRAYS = ("children_q8", "children_q8_meta", "q8_chan_scale")   # derived from `children`: not part of a checkpoint
 
     @property
     def cap_children(self) -> int:
@@ -66,7 +81,7 @@ class IndexState:
         s.depth, s.bf, s.dim, s.vdim = self.depth, self.bf, self.dim, self.vdim
         s.n_heads, s.cap_parents, s.cap_gp = self.n_heads, self.cap_parents, self.cap_gp
         s.active_parents = self._active_parents
-        for name in self.ARRAYS:
+        for name in self.ARRAYS + self.Q8_ARRAYS:
             setattr(s, name, L.ptr(getattr(self, name)))
         self._struct = s
         return s
@@ -108,15 +123,30 @@ class IndexState:
             if src.dtype == torch.uint16 or (dst.dtype == torch.bfloat16 and src.dtype == torch.int16):
                 src = src.view(torch.bfloat16)
             dst.copy_(src.reshape(dst.shape).to(dst.dtype))
+        self.refresh_int8_copy()
+
+    def enable_int8_copy(self, on: bool = True):
+        """Switches the search between the int8 pre-filter (when the index carries the side copy)
+        and the plain streaming kernel; results are identical either way."""
+        for name in self.Q8_ARRAYS:
+            setattr(self._struct, name, L.ptr(getattr(self, name)) if (on and self.int8_copy) else None)
+
+    def refresh_int8_copy(self):
+        """Recomputes the int8 side copy from the children as stored now."""
+        if self.int8_copy and self.device.type == "cuda":
+            L.check(L.load().hira_q8_refresh(self.struct, L.current_stream(self.device)), "hira_q8_refresh")
 
     def grown(self, new_cap_parents: int) -> "IndexState":
         """A copy with more parent slots (and grandparent slots); existing slots keep their positions."""
         new = IndexState(n_heads=self.n_heads, dim=self.dim, vdim=self.vdim, bf=self.bf, depth=self.depth,
                          cap_parents=new_cap_parents, dtype=self.dtype, vdtype=self.vdtype, device=self.device,
-                         with_values=self.values is not None)
-        for name in self.ARRAYS:
+                         with_values=self.values is not None, int8_copy=self.int8_copy)
+        for name in self.ARRAYS + self.Q8_ARRAYS:
             src = getattr(self, name)
             if src is None or name == "used":
+                continue
+            if name == "q8_chan_scale":
+                getattr(new, name).copy_(src)
                 continue
             getattr(new, name)[:, : src.shape[1]].copy_(src)
         new.used.copy_(self.used)
@@ -203,6 +233,11 @@ def search(st: IndexState, q: torch.Tensor, tau: torch.Tensor, *, scaling=None, 
         compact.n_tiles_active = None if (st.active_parents == 0 or out_dense is not None) \
             else -(-st.active_parents // tp)
     return out_dense, compact
+
+
+def new_stats(hq: int, device) -> torch.Tensor:
+    """Zeroed traffic counters for `search(..., stats=)`: (H_q, HIRA_SEARCH_STATS) int32."""
+    return torch.zeros((hq, L.SEARCH_STATS), dtype=torch.int32, device=device)
 
 
 def alloc_compact(st: IndexState, hq: int, tp: Optional[int] = None) -> CompactResult:

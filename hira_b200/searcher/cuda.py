@@ -126,7 +126,7 @@ class CUDASearcher(BaseSearcher):
         searcher/cuda.py:145-239): per query head the child rows scanned and their share."""
         st, q, tau, scaling, q2kv, max_group, qnorm = self._prepare(query, threshold, indexer, q_head_to_kv, scaling)
         hq = q.shape[0]
-        stats = torch.zeros((hq, 8), dtype=torch.int32, device=st.device)
+        stats = S.new_stats(hq, st.device)
         c = S.alloc_compact(st, hq)
         S.search(st, q, tau, scaling=scaling, qnorm=qnorm, q2kv=q2kv, max_group=max_group, flags=self.flags,
                  compact=c, stats=stats)

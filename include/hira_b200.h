@@ -93,7 +93,17 @@ typedef struct hira_index {
     int32_t* gp_counts;    /* [n_heads][cap_gp] filled parent slots per grandparent    */
     int32_t* used;         /* [n_heads][4]: {parent slots in use (high-water mark),
                               grandparents in use, keys stored, reserved}             */
+    /* Optional int8 side copy of the children (dim == 128 only; all three NULL = none).  With it
+       hira_search reads 128-byte int8 rows, scores them on the tensor cores and re-reads only the
+       rows that can reach the threshold in the index dtype; results are bit-identical.  Written by
+       hira_build, kept up to date by the appends, recomputed by hira_q8_refresh.  The reference
+       has no counterpart.                                                                       */
+    void* children_q8;        /* [n_heads][cap_parents*bf][128] int8, 16-byte chunks of slot r
+                                 permuted by r & 7                                             */
+    float* children_q8_meta;  /* [n_heads][cap_parents*bf][2]: (quantisation step, error bound)  */
+    float* q8_chan_scale;     /* [n_heads][HIRA_Q8_CHAN]: 128 per-channel scales, their minimum  */
 } hira_index_t;
+#define HIRA_Q8_CHAN 136
 
 const char* hira_last_error(void);
 const char* hira_version(void);
@@ -123,15 +133,18 @@ const char* hira_version(void);
  *            its emitted child slots are written in ascending slot order to
  *            out_idx/out_score starting at element t*tile_parents*bf, and their
  *            number to out_count[qh][t].
- *   stats    [n_qheads][8] uint32 or NULL; added to, not cleared:
+ *   stats    [n_qheads][HIRA_SEARCH_STATS] uint32 or NULL; added to, not cleared:
  *            {gp tested, gp kept, parents tested, parents kept, child rows read
  *             on behalf of this head, children emitted, U, P} where U and P
  *            (booked on the first query head of each group) count the child
  *            rows and parent rows actually loaded, i.e. for the union of the
- *            group's heads -- the kernel's real memory traffic
+ *            group's heads -- the kernel's real memory traffic; with the int8 side copy also
+ *            {C, S} (again on the first head of a group): child rows re-read in the index dtype
+ *            after the int8 pre-filter, and int8 rows scored
  *   tile_parents: use hira_search_tile_parents(); n_tiles =
  *            ceil(cap_parents / tile_parents).
  */
+#define HIRA_SEARCH_STATS 10
 int hira_search_tile_parents(const hira_index_t* index);
 int hira_search(const hira_index_t* index, const float* q, const float* tau,
                 const float* scaling, const float* qnorm, const int32_t* q2kv,
@@ -384,6 +397,10 @@ int hira_build(const hira_index_t* index, const void* keys, const void* values,
  * over filled parents of (||parent - gp|| + parent radius); empty -> 0.  Also
  * refreshes the ||c||^2 caches. */
 int hira_recompute_radii(const hira_index_t* index, void* stream);
+
+/* (Re)computes the int8 side copy (per-channel scales, rows, error bounds) from the children as
+ * they are stored now: after the index arrays were loaded from elsewhere. */
+int hira_q8_refresh(const hira_index_t* index, void* stream);
 
 /* Gather the stored keys/values back into token order (slot2token) for a
  * rebuild: out_k [n_heads][n_out][dim]; rows of tokens not present are left

@@ -57,7 +57,7 @@ FLAG_CASES = [
 def _run_search_case(st, ox, q, tau, flags, scaling=None, qnorm=None, q2kv=None, max_group=0):
     hq = q.shape[0]
     dense = torch.full((hq, st.cap_children), float("nan"), device="cuda")
-    stats = torch.zeros((hq, 8), dtype=torch.int32, device="cuda")
+    stats = S.new_stats(hq, "cuda")
     _, compact = S.search(st, q, tau, scaling=scaling, qnorm=qnorm, q2kv=q2kv, max_group=max_group, flags=flags,
                           out_dense=dense, want_compact=True, stats=stats)
     torch.cuda.synchronize()

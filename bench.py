@@ -52,7 +52,7 @@ E2E_REPEATS = 5
 # DRAM bytes (read + write) of one search_kernel launch per (batch, kv head) group of 131,072 keys,
 # from an ncu capture of this bench at --batch 2 (16 groups); traffic grows in proportion to the
 # groups a launch covers.  Keyed by kernel variant; None = not captured.
-SEARCH_DRAM_BYTES_PER_GROUP = {"bf16_stream": (559.073280e6 + 7.247872e6) / 16}
+SEARCH_DRAM_BYTES_PER_GROUP = {"search_kernel": (559.073280e6 + 7.247872e6) / 16, "search_q8_kernel": None}
 
 
 def peaks():
@@ -149,7 +149,7 @@ class DecodeBench:
     (batch, kv head) groups of `ctx` keys each, `group` query heads per group."""
 
     def __init__(self, w: W.Workload, n_groups: int, ctx: int, appends: int, dev, seed_offset: int = 0,
-                 use_tc: bool = True, exchange=None):
+                 use_tc: bool = True, exchange=None, int8_copy: bool = True):
         from hira_b200 import _lib as L
         from hira_b200 import index_state as S
         self.L, self.S, self.w, self.dev = L, S, w, dev
@@ -162,7 +162,8 @@ class DecodeBench:
         self.k2 = -(-self.k1 // bf)
         spare_gp = appends + 16   # worst case every appended key opens a new grandparent block
         self.st = st = S.IndexState(n_heads=n_groups, dim=DIM, vdim=DIM, bf=bf, depth=w.levels,
-                                    cap_parents=(self.k2 + spare_gp) * bf, dtype=w.dtype, vdtype=w.dtype, device=dev)
+                                    cap_parents=(self.k2 + spare_gp) * bf, dtype=w.dtype, vdtype=w.dtype, device=dev,
+                                    int8_copy=int8_copy)
         cent1 = W.random_centres(n_groups, ctx, self.k1, 7 + seed_offset, dev)
         cent2 = W.random_centres(n_groups, self.k1, self.k2, 8 + seed_offset, dev)
         torch.cuda.synchronize()
@@ -227,13 +228,19 @@ class DecodeBench:
         S.search(self.st, q_hat, tau, scaling=lscale, flags=self.flags, compact=self.compact, stats=stats, tp=self.tp)
         torch.cuda.synchronize()
         s = stats.to(torch.int64).sum(dim=0).tolist()
-        rows_read, parents_read, emitted = s[6], s[7], s[5]
+        rows_read, parents_read, emitted, reread, rows8 = s[6], s[7], s[5], s[8], s[9]
         e = 2 if self.w.dtype == torch.bfloat16 else 4
-        search_bytes = self.n_groups * self.k2 * (DIM * e + 4) + parents_read * (DIM * e + 8) + rows_read * DIM * e
+        # child rows: in the index dtype, or -- through the int8 side copy -- 128 B + 8 B of (step, error)
+        # per scored row plus the candidates re-read in the index dtype
+        child_bytes = rows8 * (DIM + 8) + reread * DIM * e if rows8 else rows_read * DIM * e
+        self.search_kernel = "search_q8_kernel" if rows8 else "search_kernel"
+        self.reread_fraction = reread / float(rows8) if rows8 else None
+        search_bytes = self.n_groups * self.k2 * (DIM * e + 4) + parents_read * (DIM * e + 8) + child_bytes
         attn_bytes = emitted * (DIM * e + 8) + self.n_qheads * DIM * 4
         append_bytes = self.n_groups * ((self.k1 + self.k2) * (DIM * e + 4) + 2 * DIM * e)
         return dict(search_bytes=search_bytes, attn_bytes=attn_bytes, append_bytes=append_bytes,
-                    scanned_fraction=rows_read / float(self.n_groups * self.ctx), selected_per_qhead=emitted / self.n_qheads)
+                    scanned_fraction=rows_read / float(self.n_groups * self.ctx * -(-self.group // 4)),
+                    selected_per_qhead=emitted / self.n_qheads)
 
     # ---- the step ---------------------------------------------------------------------
     def step(self, i: int, ev=None, *, fused=True, side=None, tau_in_step=False, append=True, nccl_ev=None):
@@ -448,7 +455,7 @@ def secondary_cfg1(args, dev, barrier_local, peak):
     b.make_new_keys(steps + warm, 9100)
     c = b.counters()
     side = None if args.serial else torch.cuda.Stream(device=dev)
-    r = b.timed_loop(steps, warm, barrier_local, fused=True, side=side)
+    r = b.timed_loop(steps, warm, barrier_local, fused=b.search_kernel == "search_kernel", side=side)
     dense_ms = b.time_dense()
     step_us = r["total_ms"] / steps * 1e3
     ach = c["search_bytes"] / (r["search_ms"] * 1e-3) / 1e9
@@ -596,11 +603,15 @@ def run_ours(args):
     steps, warm = args.steps, args.warmup
     tau_steps, tau_warm = min(steps, 10), 3
     appends = (steps + warm) + (tau_steps + tau_warm) + 8
-    b = DecodeBench(w, n_groups, ctx, appends, dev, seed_offset=rank, use_tc=not args.no_tc)
+    b = DecodeBench(w, n_groups, ctx, appends, dev, seed_offset=rank, use_tc=not args.no_tc, int8_copy=not args.no_int8)
     b.make_queries(N_QUERY_SETS, 50 + 1000 * rank)
     b.make_new_keys(steps + warm, 9000 + rank)
     c = b.counters()
-    fused = not args.unfused
+    kernel_name, reread_fraction = b.search_kernel, b.reread_fraction
+    # The append's parent scan folded into the search pays with the streaming kernel (the parent rows
+    # are in registers anyway); with the int8 pre-filter the gates sit on each CTA's critical path and
+    # the separate scan hides beside the attention on the second stream, so it stays separate there.
+    fused = args.fused if args.fused is not None else (kernel_name == "search_kernel")
     side = None if args.serial else torch.cuda.Stream(device=dev)
 
     snap = b.snapshot()
@@ -672,7 +683,7 @@ def run_ours(args):
     achieved = c["search_bytes"] / (search_ms * 1e-3) / 1e9
     step_bytes = c["search_bytes"] + c["attn_bytes"] + c["append_bytes"]
     cpu = cpu_baseline_sample(args) if not args.no_cpu else None
-    traffic = SEARCH_DRAM_BYTES_PER_GROUP.get(args.traffic_key)
+    traffic = SEARCH_DRAM_BYTES_PER_GROUP.get(args.traffic_key or kernel_name)
     line = {
         "metric": "decode_step_us", "value": ms_per_step * 1e3, "unit": "us", "n_gpus": world, "steps": steps,
         "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong",
@@ -687,8 +698,9 @@ def run_ours(args):
         "e2e": {"value": e2e_ms * 1e3, "unit": "us", "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
                 "repeats": E2E_REPEATS, "min_us": e2e_min * 1e3, "max_us": e2e_max * 1e3,
                 "entry": "HiraDecodeStep -> hira_decode_step (one C call per step, host buffers)"},
-        "gpu_launches": steps * (2 + (1 if fused else 2)),   # search, sparse_attn (one split: no merge), [append_scan,] append
-        "roofline": {"bound": "hbm", "kernel": "search_kernel", "achieved": achieved, "peak": peak,
+        # [query terms,] search, sparse_attn (one split: no merge), [append_scan,] append
+        "gpu_launches": steps * ((2 if kernel_name == "search_q8_kernel" else 1) + 1 + (1 if fused else 2)),
+        "roofline": {"bound": "hbm", "kernel": kernel_name, "achieved": achieved, "peak": peak,
                      "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": (traffic * n_groups if (traffic and ctx == w.context) else None),
                      "algorithmic_bytes_per_launch": c["search_bytes"]},
@@ -699,6 +711,9 @@ def run_ours(args):
         "step_hbm": {"bytes": step_bytes, "achieved_gbs": step_bytes / (ms_per_step * 1e-3) / 1e9,
                      "frac_of_peak": step_bytes / (ms_per_step * 1e-3) / 1e9 / peak},
         "scanned_fraction": c["scanned_fraction"], "selected_per_qhead": c["selected_per_qhead"],
+        "int8_prefilter": None if reread_fraction is None else {
+            "rows_reread_in_index_dtype_fraction": reread_fraction,
+            "bytes_per_child_row": (DIM + 8) + reread_fraction * DIM * 2, "extra_memory": "136 B per child slot"},
         "dense_attention_us": None if dense_ms is None else dense_max * 1e3,
         "vs_dense": None if dense_ms is None else dense_max / ms_per_step,
         "secondary": secondary, "clocks": clocks, "cpu_baseline": cpu,
@@ -835,9 +850,12 @@ def main():
     ap.add_argument("--no-secondary", action="store_true", help="skip the secondary workloads (cfg1, cfg3, cfg4)")
     ap.add_argument("--stream-steps", type=int, default=4096, help="appends of the streaming workload (cfg3)")
     ap.add_argument("--serial", action="store_true", help="append after the attention on one stream instead of beside it")
-    ap.add_argument("--unfused", action="store_true",
-                    help="separate parent scan in the append instead of the scan folded into the search")
-    ap.add_argument("--traffic-key", default="bf16_stream", help=argparse.SUPPRESS)
+    ap.add_argument("--fused", dest="fused", action="store_true", default=None,
+                    help="fold the append's parent scan into the search (default with the streaming kernel)")
+    ap.add_argument("--unfused", dest="fused", action="store_false",
+                    help="separate parent scan in the append (default with the int8 pre-filter)")
+    ap.add_argument("--no-int8", action="store_true", help="search without the int8 side copy (plain streaming kernel)")
+    ap.add_argument("--traffic-key", default=None, help=argparse.SUPPRESS)
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3

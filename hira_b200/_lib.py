@@ -32,6 +32,7 @@ EXPORTED_SYMBOLS = [
 NOALLOC_SCRATCH_FLOATS = 1 << 20
 SEARCH_STATS = 10     # uint32 counters per query head (HIRA_SEARCH_STATS)
 Q8_CHAN = 136         # floats per head in q8_chan_scale (HIRA_Q8_CHAN)
+Q8_QUERY_BYTES = 4 * 2112   # bytes per head in q8_query_scratch (HIRA_Q8_QUERY_CHUNKS * HIRA_Q8_QUERY_BYTES)
 
 
 class HiraIndexStruct(C.Structure):
@@ -45,6 +46,7 @@ class HiraIndexStruct(C.Structure):
         ("child_counts", C.c_void_p), ("grand_parents", C.c_void_p), ("gp_radii", C.c_void_p),
         ("gp_sqnorm", C.c_void_p), ("gp_counts", C.c_void_p), ("used", C.c_void_p),
         ("children_q8", C.c_void_p), ("children_q8_meta", C.c_void_p), ("q8_chan_scale", C.c_void_p),
+        ("q8_query_scratch", C.c_void_p),
     ]
 
 

@@ -44,9 +44,9 @@ int validate_index(const hira_index_t* ix, bool need_values) {
         HIRA_CHECK_ARG(ix->grand_parents && ix->gp_radii && ix->gp_counts, HIRA_ERR_ARG,
                        "depth-3 index has a NULL grand_parents/gp_radii/gp_counts pointer");
     }
-    if (ix->children_q8 || ix->children_q8_meta || ix->q8_chan_scale) {
-        HIRA_CHECK_ARG(ix->children_q8 && ix->children_q8_meta && ix->q8_chan_scale, HIRA_ERR_ARG,
-                       "the int8 side copy needs children_q8, children_q8_meta and q8_chan_scale together");
+    if (ix->children_q8 || ix->children_q8_meta || ix->q8_chan_scale || ix->q8_query_scratch) {
+        HIRA_CHECK_ARG(ix->children_q8 && ix->children_q8_meta && ix->q8_chan_scale && ix->q8_query_scratch, HIRA_ERR_ARG,
+                       "the int8 side copy needs children_q8, children_q8_meta, q8_chan_scale and q8_query_scratch together");
         HIRA_CHECK_ARG(ix->dim == 128, HIRA_ERR_SHAPE, "the int8 side copy needs dim == 128 (got %d)", ix->dim);
     }
     if (need_values || ix->values) {

@@ -39,22 +39,28 @@ constexpr int Q8_DIM = 128;
 constexpr int Q8_STAGE_ROWS = 128;
 constexpr int Q8_STAGE_BYTES = Q8_STAGE_ROWS * Q8_DIM;    // 16 KB of int8 rows
 constexpr int Q8_META_BYTES = Q8_STAGE_ROWS * 8;          // (step, err) per row
-constexpr int Q8_SLOTS = 4;                               // stages in flight per CTA
+#ifndef HIRA_Q8_SLOTS
+#define HIRA_Q8_SLOTS 3
+#endif
+constexpr int Q8_SLOTS = HIRA_Q8_SLOTS;                   // stages in flight per CTA (3: three CTAs per SM)
 constexpr int Q8_MAX_STAGES = MAX_TILE_ROWS / Q8_STAGE_ROWS;   // 8
 constexpr int Q8_NCOL = 16;                               // accumulator columns per stage (N of the MMA)
 constexpr int Q8_TMEM_COLS = Q8_MAX_STAGES * Q8_NCOL;     // 128
 constexpr int Q8_THREADS = 160;                           // 4 worker warps + 1 producer/MMA warp
 constexpr int Q8_WORKERS = 128;
 constexpr int Q8_MAX_TP = 128;                            // parents per tile (bf >= 8)
+constexpr int Q8_HINT = 132;   // q8_chan_scale[h][132..134] as uint32: stages kept / stages of the last search, stream-all flag
+constexpr int Q8_QBYTES = HIRA_Q8_QUERY_BYTES;            // prepared query terms of one (kv head, chunk of 4 heads)
+static_assert(Q8_QBYTES == 2048 + 64, "B operand (16 rows x 128 B) + (c1, c2, A, B) of 4 heads");
 
 struct Q8Smem {   // offsets in the 1024-byte aligned dynamic shared memory
     static constexpr int RING = 0;                                    // Q8_SLOTS stages of rows; later the candidates' scores
-    static constexpr int BQ = Q8_SLOTS * Q8_STAGE_BYTES;              // 16 x 128 int8 query terms (B operand)
-    static constexpr int META = BQ + 2048;                            // [Q8_MAX_STAGES][128] float2
+    static constexpr int BQ = Q8_SLOTS * Q8_STAGE_BYTES;              // 16 x 128 int8 query terms (B operand) + constants
+    static constexpr int META = BQ + 3072;                            // [Q8_MAX_STAGES][128] float2
     static constexpr int CAND = META + Q8_MAX_STAGES * Q8_META_BYTES; // [1024] head masks
     static constexpr int LIST = CAND + MAX_TILE_ROWS;                 // [1024] uint16 candidate rows, ascending
-    static constexpr int BAR = LIST + 2 * MAX_TILE_ROWS;              // full[Q8_SLOTS], done[Q8_MAX_STAGES], go
-    static constexpr int TMEM_SLOT = BAR + 8 * (Q8_SLOTS + Q8_MAX_STAGES + 1);
+    static constexpr int BAR = LIST + 2 * MAX_TILE_ROWS;              // full[Q8_SLOTS], done[Q8_MAX_STAGES], go, query
+    static constexpr int TMEM_SLOT = BAR + 8 * (Q8_SLOTS + Q8_MAX_STAGES + 2);
     static constexpr int TOTAL = TMEM_SLOT + 16;
 };
 
@@ -109,10 +115,81 @@ __device__ __forceinline__ void worker_reduce(float (&v)[GT], float (*s_red)[8],
     }
 }
 
+// The query heads of one (kv head, chunk) as the B operand of the MMA, once per search: worker t owns
+// channel t.  q' = q (.) s is split into two int8 terms, q' = c1 a1 + c2 a2 + r2; out = 16 rows of
+// 128 int8 (row 2j = a1 of head j, row 2j+1 = a2; 16-byte chunks swizzled by the row; absent heads
+// zero) followed by (c1, c2, A, B) per head with A >= ||q'||_2, B >= 127 ||r2||_1 + rounding.
+__global__ void __launch_bounds__(Q8_WORKERS)
+search_q8_prepare_kernel(const float* __restrict__ q, const float* __restrict__ chan_scale, float* chan_scale_rw,
+                         int group, int gt, int dim, unsigned char* __restrict__ out) {
+    constexpr int GT = 4;
+    __shared__ float s_red[4][8];
+    const int tid = threadIdx.x, warp = tid >> 5, wl = tid & 31;
+    const int chunk = blockIdx.x, h = blockIdx.y;
+    int nq = group - chunk * gt;
+    nq = nq < 0 ? 0 : (nq > gt ? gt : nq);
+    const float cs = chan_scale[(size_t)h * HIRA_Q8_CHAN + tid];
+    float qp[GT], v[GT];
+#pragma unroll
+    for (int j = 0; j < GT; ++j) {
+        qp[j] = j < nq ? q[(size_t)(h * group + chunk * gt + j) * dim + tid] * cs : 0.f;
+        v[j] = fabsf(qp[j]);
+    }
+    worker_reduce<GT, true>(v, s_red, warp, wl);
+    float c1[GT], a1[GT], r1[GT];
+#pragma unroll
+    for (int j = 0; j < GT; ++j) {
+        c1[j] = v[j] > 0.f ? v[j] / 127.0f : 1.0f;
+        a1[j] = fminf(fmaxf(rintf(qp[j] / c1[j]), -127.f), 127.f);
+        r1[j] = __fmaf_rn(-a1[j], c1[j], qp[j]);
+        v[j] = fabsf(r1[j]);
+    }
+    worker_reduce<GT, true>(v, s_red, warp, wl);
+    float c2[GT], a2[GT], l1[GT], sq[GT];
+#pragma unroll
+    for (int j = 0; j < GT; ++j) {
+        c2[j] = v[j] > 0.f ? v[j] / 127.0f : 1.0f;
+        a2[j] = fminf(fmaxf(rintf(r1[j] / c2[j]), -127.f), 127.f);
+        l1[j] = fabsf(__fmaf_rn(-a2[j], c2[j], r1[j]));
+        sq[j] = qp[j] * qp[j];
+    }
+    worker_reduce<GT, false>(l1, s_red, warp, wl);
+    worker_reduce<GT, false>(sq, s_red, warp, wl);
+    if (chunk == 0 && tid == 0) {
+        // How the previous search of this head went decides how this one streams: if the gates kept
+        // at least 3/4 of the stages, every stage of a tile is requested before its gates are known
+        // (they overlap the stream); otherwise only the first few are.  Results never depend on it.
+        uint32_t* hint = reinterpret_cast<uint32_t*>(chan_scale_rw + (size_t)h * HIRA_Q8_CHAN + Q8_HINT);
+        const uint32_t kept = hint[0], total = hint[1];
+        if (total != 0) hint[2] = (4ull * kept >= 3ull * total) ? 1u : 0u;
+        hint[0] = 0u;
+        hint[1] = 0u;
+    }
+    unsigned char* dst = out + ((size_t)h * gridDim.x + chunk) * Q8_QBYTES;
+    const int ch16 = tid >> 4, byte = tid & 15;
+#pragma unroll
+    for (int n = 0; n < Q8_NCOL; ++n) {
+        float val = 0.f;
+        if (n < 2 * GT) val = (n & 1) ? a2[n >> 1] : a1[n >> 1];
+        const int off = (n >> 3) * 1024 + (n & 7) * 128 + ((ch16 ^ (n & 7)) << 4) + byte;
+        reinterpret_cast<signed char*>(dst)[off] = (signed char)(int)val;
+    }
+    if (tid < GT) {
+        const int j = tid;
+        float* qc = reinterpret_cast<float*>(dst + 2048) + 4 * j;
+        const float A = sqrtf(sq[j]) * 1.001f;
+        qc[0] = c1[j];
+        qc[1] = c2[j];
+        qc[2] = A;
+        // |r2 . k~| <= ||r2||_1 * 127, plus the rounding of the split itself
+        qc[3] = 127.0f * l1[j] * 1.001f + A * (127.0f * 11.32f * 3.9e-6f);
+    }
+}
+
 template <typename T, int GT, bool SCAN>
 __global__ void __launch_bounds__(Q8_THREADS, 3)
 search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const float2* __restrict__ k8_meta,
-                 const float* __restrict__ chan_scale) {
+                 const unsigned char* __restrict__ qterms, uint32_t* __restrict__ hints) {
     constexpr int NCH = 2;
     constexpr int SEARCH_GROUPS = Q8_WORKERS / GROUP;  // 16
     constexpr int PRE = 2;
@@ -126,15 +203,14 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
     const uint32_t bar_full = s_base + Q8Smem::BAR;                   // [Q8_SLOTS] stage landed
     const uint32_t bar_done = bar_full + 8 * Q8_SLOTS;                // [Q8_MAX_STAGES] MMAs of the k-th stage complete
     const uint32_t bar_go = bar_done + 8 * Q8_MAX_STAGES;             // gates known
+    const uint32_t bar_q = bar_go + 8;                                // prepared query terms landed
     volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(sm + Q8Smem::TMEM_SLOT);
 
     __shared__ int s_pcount[Q8_MAX_TP];
     __shared__ unsigned char s_pmask[Q8_MAX_TP], s_gpmask[Q8_MAX_TP];
     __shared__ int s_qh[GT];
     __shared__ float s_scale[GT], s_tau[GT];
-    __shared__ float s_qc[GT][4];   // c1, c2, A, B of each head
-    __shared__ float s_red[4][8];
-    __shared__ int s_nq, s_need, s_ncand, s_fail;
+    __shared__ int s_nq, s_need, s_ncand, s_fail, s_wcount[4];
     __shared__ uint32_t s_stat[GT][8];
     __shared__ unsigned long long s_scan[SEARCH_GROUPS];
     __shared__ __align__(16) float s_xkey[SCAN ? GROUP * NCH * 8 : 4];
@@ -198,6 +274,7 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
         for (int i = 0; i < Q8_SLOTS; ++i) mbar_init(bar_full + 8 * i, 1);
         for (int i = 0; i < Q8_MAX_STAGES; ++i) mbar_init(bar_done + 8 * i, 1);
         mbar_init(bar_go, 1);
+        mbar_init(bar_q, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -214,35 +291,56 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
     const int tile_p0 = tile * TP;
     const size_t tile_c0 = (size_t)tile_p0 * bf;
     const int n_stage_tile = tile_rows / Q8_STAGE_ROWS;
+    // stages requested before the gates are known: none for a tile beyond the slots in use
+    const bool tile_in_use = P.depth == 3 ? (P.tile_gp_shift >= 0 ? (tile >> P.tile_gp_shift)
+                                             : (P.tile_gp_shift == -1 ? tile * P.ng : div_bf(tile * TP, bf, P.bf_magic))) < P.used[h * 4 + 1]
+                                          : tile_p0 < P.used[h * 4 + 0];
+    uint32_t* hint = hints + (size_t)h * HIRA_Q8_CHAN + Q8_HINT;
+    const bool stream_all = hint[2] != 0u;
+    const int spec = tile_in_use ? ((stream_all || n_stage_tile < Q8_SLOTS) ? n_stage_tile : Q8_SLOTS) : 0;
 
     if (!worker) {
         // ======================= producer + MMA issuer (one thread) =========================
         if (tid == Q8_WORKERS) {
-            bool failed = !mbar_wait(bar_go, 0);
-            const int need = failed ? 0 : *reinterpret_cast<volatile int*>(&s_need);
-            int order[Q8_MAX_STAGES];
-            int n = 0;
-#pragma unroll
-            for (int s = 0; s < Q8_MAX_STAGES; ++s)
-                if (s < n_stage_tile && ((need >> s) & 1)) order[n++] = s;
+            // The first stages of a tile that holds keys are requested at once, before the gates are
+            // known (they are nearly always needed; at most Q8_SLOTS stages are read for nothing when
+            // the gates prune the whole tile); the rest follows the gates.
+            mbar_expect_tx(bar_q, Q8_QBYTES);
+            bulk_load(s_base + Q8Smem::BQ, qterms + ((size_t)h * P.n_chunks + chunk) * Q8_QBYTES, Q8_QBYTES, bar_q);
             const int8_t* rows_g = k8 + ((size_t)h * cap_children + tile_c0) * Q8_DIM;
             const float2* meta_g = k8_meta + (size_t)h * cap_children + tile_c0;
-            int issued = 0;
-            for (int k = 0; k < n && !failed; ++k) {
+            int order[Q8_MAX_STAGES] = {0, 0, 0, 0, 0, 0, 0, 0};
+            int n = spec, issued = 0;
+            bool failed = false, got_go = false;
+            auto issue = [&](int i) {
+                const int slot = i % Q8_SLOTS;
+                const uint32_t full = bar_full + 8 * slot;
+                mbar_expect_tx(full, Q8_STAGE_BYTES + Q8_META_BYTES);
+                bulk_load(s_base + Q8Smem::RING + slot * Q8_STAGE_BYTES, rows_g + (size_t)order[i] * Q8_STAGE_BYTES,
+                          Q8_STAGE_BYTES, full);
+                bulk_load(s_base + Q8Smem::META + i * Q8_META_BYTES, meta_g + (size_t)order[i] * Q8_STAGE_ROWS,
+                          Q8_META_BYTES, full);
+            };
+            for (int i = 0; i < spec; ++i) order[i] = i;
+            for (; issued < spec && issued < Q8_SLOTS; ++issued) issue(issued);
+            for (int k = 0; !failed; ++k) {
+                if (!got_go && k >= spec) {
+                    if (!mbar_wait(bar_go, 0)) { failed = true; break; }
+                    got_go = true;
+                    const int need = *reinterpret_cast<volatile int*>(&s_need);
+                    for (int s = spec; s < n_stage_tile; ++s)
+                        if ((need >> s) & 1) order[n++] = s;
+                }
+                if (k >= n) break;
                 while (issued < n && issued < k + Q8_SLOTS) {
                     // the slot held stage issued - Q8_SLOTS: free once its MMAs are complete
                     if (issued >= Q8_SLOTS && !mbar_wait(bar_done + 8 * (issued - Q8_SLOTS), 0)) { failed = true; break; }
-                    const int slot = issued % Q8_SLOTS;
-                    const uint32_t full = bar_full + 8 * slot;
-                    mbar_expect_tx(full, Q8_STAGE_BYTES + Q8_META_BYTES);
-                    bulk_load(s_base + Q8Smem::RING + slot * Q8_STAGE_BYTES, rows_g + (size_t)order[issued] * Q8_STAGE_BYTES,
-                              Q8_STAGE_BYTES, full);
-                    bulk_load(s_base + Q8Smem::META + issued * Q8_META_BYTES, meta_g + (size_t)order[issued] * Q8_STAGE_ROWS,
-                              Q8_META_BYTES, full);
+                    issue(issued);
                     ++issued;
                 }
                 if (failed) break;
                 const int slot = k % Q8_SLOTS;
+                if (k == 0 && !mbar_wait(bar_q, 0)) { failed = true; break; }
                 if (!mbar_wait(bar_full + 8 * slot, (k / Q8_SLOTS) & 1)) { failed = true; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t a0 = s_base + Q8Smem::RING + slot * Q8_STAGE_BYTES, b0 = s_base + Q8Smem::BQ;
@@ -254,6 +352,7 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
             if (failed) {
                 *reinterpret_cast<volatile int*>(&s_fail) = 1;
                 // let copies that may still be in flight land before the ring is reused (bounded)
+                mbar_wait(bar_q, 0);
                 for (int i = 0; i < issued && i < Q8_SLOTS; ++i) mbar_wait(bar_full + 8 * i, ((issued - 1 - i) / Q8_SLOTS) & 1);
             }
         }
@@ -333,58 +432,6 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
         unsigned long long scan_best = ~0ull;
         // candidate masks start empty (rows of stages that are not scored stay so)
         reinterpret_cast<uint2*>(s_cand)[tid] = make_uint2(0u, 0u);
-
-        // ---- 2. the query heads as two int8 terms each (B operand of the MMA) ----------------
-        {
-            const float cs = chan_scale[(size_t)h * HIRA_Q8_CHAN + tid];   // worker t owns channel t
-            float qp[GT], v[GT];
-#pragma unroll
-            for (int j = 0; j < GT; ++j) {
-                qp[j] = j < nq ? P.q[(size_t)qh_of[j] * P.dim + tid] * cs : 0.f;
-                v[j] = fabsf(qp[j]);
-            }
-            worker_reduce<GT, true>(v, s_red, warp, wl);
-            float c1[GT], a1[GT], r1[GT];
-#pragma unroll
-            for (int j = 0; j < GT; ++j) {
-                c1[j] = v[j] > 0.f ? v[j] / 127.0f : 1.0f;
-                a1[j] = fminf(fmaxf(rintf(qp[j] / c1[j]), -127.f), 127.f);
-                r1[j] = __fmaf_rn(-a1[j], c1[j], qp[j]);
-                v[j] = fabsf(r1[j]);
-            }
-            worker_reduce<GT, true>(v, s_red, warp, wl);
-            float c2[GT], a2[GT], l1[GT], sq[GT];
-#pragma unroll
-            for (int j = 0; j < GT; ++j) {
-                c2[j] = v[j] > 0.f ? v[j] / 127.0f : 1.0f;
-                a2[j] = fminf(fmaxf(rintf(r1[j] / c2[j]), -127.f), 127.f);
-                l1[j] = fabsf(__fmaf_rn(-a2[j], c2[j], r1[j]));
-                sq[j] = qp[j] * qp[j];
-            }
-            worker_reduce<GT, false>(l1, s_red, warp, wl);
-            worker_reduce<GT, false>(sq, s_red, warp, wl);
-            // B operand: row n = 2 * head + term, 128 int8, 16-byte chunks swizzled by the row; rows of
-            // absent heads are zero
-            const int ch16 = tid >> 4, byte = tid & 15;
-#pragma unroll
-            for (int n = 0; n < Q8_NCOL; ++n) {
-                float val = 0.f;
-                if (n < 2 * GT) val = (n & 1) ? a2[n >> 1] : a1[n >> 1];
-                const int off = (n >> 3) * 1024 + (n & 7) * 128 + ((ch16 ^ (n & 7)) << 4) + byte;
-                reinterpret_cast<signed char*>(sm + Q8Smem::BQ)[off] = (signed char)(int)val;
-            }
-            if (tid < GT) {
-                const int j = tid;
-                const float A = sqrtf(sq[j]) * 1.001f;
-                s_qc[j][0] = c1[j];
-                s_qc[j][1] = c2[j];
-                s_qc[j][2] = A;
-                // |r2 . k~| <= ||r2||_1 * 127, plus the rounding of the split itself
-                s_qc[j][3] = 127.0f * l1[j] * 1.001f + A * (127.0f * 11.32f * 3.9e-6f);
-            }
-            // the generic-proxy writes of the B operand must be visible to the tensor core
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        }
 
         bool tile_empty;
         if (P.depth == 3) tile_empty = g0 >= used_gp;
@@ -532,21 +579,36 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
             }
         }
         worker_sync();   // s_need, s_pmask, s_pcount, the B operand and the cleared candidate masks are complete
-        if (tid == 0) mbar_arrive(bar_go);
-        const int need = *reinterpret_cast<volatile int*>(&s_need);
+        if (tid == 0) {
+            mbar_arrive(bar_go);
+            if (chunk == 0 && tile_in_use) {   // what the gates kept, for the next search's streaming mode
+                atomicAdd(hint, (uint32_t)__popc(*reinterpret_cast<volatile int*>(&s_need)));
+                atomicAdd(hint + 1, (uint32_t)n_stage_tile);
+            }
+        }
+        const int need = *reinterpret_cast<volatile int*>(&s_need) | ((1 << spec) - 1);   // the stages requested up front come first
 
         // ---- 5. candidates: approximate scores out of tensor memory ----------------------------
         {
+            bool failed = false;
+            {   // the prepared query terms and their constants arrive by a bulk copy
+                const bool ok = mbar_wait(bar_q, 0);
+                if (!__all_sync(0xffffffffu, ok)) {
+                    failed = true;
+                    if (wl == 0) *reinterpret_cast<volatile int*>(&s_fail) = 1;
+                }
+            }
+            const float* s_qc = reinterpret_cast<const float*>(sm + Q8Smem::BQ + 2048);
             float qc[GT][4], tauj[GT];
 #pragma unroll
             for (int j = 0; j < GT; ++j) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e) qc[j][e] = s_qc[j][e];
+                for (int e = 0; e < 4; ++e) qc[j][e] = s_qc[4 * j + e];
                 tauj[j] = j < nq ? s_tau[j] : CUDART_INF_F;
             }
             int k = 0;
-            bool failed = false;
             for (int s = 0; s < n_stage_tile; ++s) {   // uniform over the workers
+                if (failed) break;
                 if (!((need >> s) & 1)) continue;
                 // warp-uniform outcome: tcgen05.ld below is a warp-wide instruction
                 const bool ok = mbar_wait(bar_done + 8 * k, 0) && !*reinterpret_cast<volatile int*>(&s_fail);
@@ -594,16 +656,23 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
             }
         }
 
-        // ---- 6. ascending list of candidate rows ------------------------------------------------
-        if (warp == 0) {
+        // ---- 6. ascending list of candidate rows (each warp lists its quarter of the tile) --------
+        {
+            const int quarter = tile_rows / 4;       // a multiple of 32
+            const int r_lo = warp * quarter;
             int n = 0;
-            for (int base = 0; base < tile_rows; base += 32) {
+            for (int base = r_lo; base < r_lo + quarter; base += 32) n += __popc(__ballot_sync(0xffffffffu, s_cand[base + wl] != 0));
+            if (wl == 0) s_wcount[warp] = n;
+            worker_sync();
+            int off = 0;
+            for (int w = 0; w < warp; ++w) off += s_wcount[w];
+            for (int base = r_lo; base < r_lo + quarter; base += 32) {
                 const bool m = s_cand[base + wl] != 0;
                 const uint32_t b = __ballot_sync(0xffffffffu, m);
-                if (m) s_list[n + __popc(b & ((1u << wl) - 1u))] = (unsigned short)(base + wl);
-                n += __popc(b);
+                if (m) s_list[off + __popc(b & ((1u << wl) - 1u))] = (unsigned short)(base + wl);
+                off += __popc(b);
             }
-            if (wl == 0) s_ncand = n;
+            if (tid == Q8_WORKERS - 1) s_ncand = off;   // the last warp ends at the total
         }
         worker_sync();
         const int ncand = s_ncand;
@@ -612,27 +681,26 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
         {
             const bool writer = HeadReduce<GT>::is_writer(lane);
             const float leaf_thr = (leaf_mode == HIRA_LEAF_GT) ? nextafterf(my_tau, CUDART_INF_F) : my_tau;
-            const int iters = (ncand + 2 * SEARCH_GROUPS - 1) / (2 * SEARCH_GROUPS);   // uniform over the workers
+            constexpr int XR = 4;   // candidate rows per group and iteration: their loads are in flight together
+            const int iters = (ncand + XR * SEARCH_GROUPS - 1) / (XR * SEARCH_GROUPS);   // uniform over the workers
             for (int it = 0; it < iters; ++it) {
-                const int e0 = it * 2 * SEARCH_GROUPS + grp, e1 = e0 + SEARCH_GROUPS;
-                const bool v0 = e0 < ncand, v1 = e1 < ncand;
-                const int r0 = v0 ? s_list[e0] : 0, r1 = v1 ? s_list[e1] : 0;
-                RawChunk<T> raw0[NCH], raw1[NCH];
+                int e[XR], r[XR];
+                RawChunk<T> raw[XR][NCH];
 #pragma unroll
-                for (int ci = 0; ci < NCH; ++ci) {
-                    raw0[ci] = v0 ? load_chunk_stream<T>(children + (tile_c0 + r0) * P.dim, lane + GROUP * ci) : zero_chunk<T>();
-                    raw1[ci] = v1 ? load_chunk_stream<T>(children + (tile_c0 + r1) * P.dim, lane + GROUP * ci) : zero_chunk<T>();
+                for (int u = 0; u < XR; ++u) {
+                    e[u] = (it * XR + u) * SEARCH_GROUPS + grp;
+                    r[u] = e[u] < ncand ? s_list[e[u]] : -1;
+#pragma unroll
+                    for (int ci = 0; ci < NCH; ++ci)
+                        raw[u][ci] = r[u] >= 0 ? load_chunk_stream<T>(children + (tile_c0 + r[u]) * P.dim, lane + GROUP * ci)
+                                               : zero_chunk<T>();
                 }
-                const float d0 = gate_dot_raw<T, GT, NCH>(raw0, qreg, lane);
-                const float d1 = gate_dot_raw<T, GT, NCH>(raw1, qreg, lane);
-                if (writer) {
-                    if (v0) {
-                        const bool em = head_on && ((s_cand[r0] >> my_head) & 1u) && d0 >= leaf_thr;
-                        s_cscore[e0 * GT + my_head] = em ? __float_as_uint(d0) : NOT_EMITTED;
-                    }
-                    if (v1) {
-                        const bool em = head_on && ((s_cand[r1] >> my_head) & 1u) && d1 >= leaf_thr;
-                        s_cscore[e1 * GT + my_head] = em ? __float_as_uint(d1) : NOT_EMITTED;
+#pragma unroll
+                for (int u = 0; u < XR; ++u) {
+                    const float d = gate_dot_raw<T, GT, NCH>(raw[u], qreg, lane);
+                    if (writer && r[u] >= 0) {
+                        const bool em = head_on && ((s_cand[r[u]] >> my_head) & 1u) && d >= leaf_thr;
+                        s_cscore[e[u] * GT + my_head] = em ? __float_as_uint(d) : NOT_EMITTED;
                     }
                 }
             }
@@ -667,7 +735,9 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
                     if (offset) atomicAdd(st + 5, (uint32_t)offset);
                     if (j == 0) {
                         if (ncand) atomicAdd(st + 8, (uint32_t)ncand);                           // rows re-read in the index dtype
-                        if (need) atomicAdd(st + 9, (uint32_t)(__popc(need) * Q8_STAGE_ROWS));   // int8 rows scored
+                        // int8 rows scored (none when a bounded wait ran out and the CTA fell back)
+                        if (need && !*reinterpret_cast<volatile int*>(&s_fail))
+                            atomicAdd(st + 9, (uint32_t)(__popc(need) * Q8_STAGE_ROWS));
                     }
                 }
             }
@@ -695,9 +765,14 @@ static int launch_q8(SearchParams P, int chunks, const hira_index_t* ix, cudaStr
     P.n_chunks = chunks;
     HIRA_CHECK_ARG(P.n_tiles <= 65535 && P.n_heads <= 65535, HIRA_ERR_SHAPE,
                    "hira_search: %d tiles x %d heads exceed the grid limits", P.n_tiles, P.n_heads);
+    unsigned char* qterms = reinterpret_cast<unsigned char*>(ix->q8_query_scratch);
+    search_q8_prepare_kernel<<<dim3((unsigned)chunks, (unsigned)P.n_heads), Q8_WORKERS, 0, stream>>>(
+        P.q, ix->q8_chan_scale, ix->q8_chan_scale, P.group, GT, P.dim, qterms);
+    HIRA_CHECK_LAUNCH("hira_search (int8 pre-filter, query terms) launch");
     dim3 grid((unsigned)chunks, (unsigned)P.n_tiles_active, (unsigned)P.n_heads);
     kern<<<grid, Q8_THREADS, smem, stream>>>(P, reinterpret_cast<const int8_t*>(ix->children_q8),
-                                            reinterpret_cast<const float2*>(ix->children_q8_meta), ix->q8_chan_scale);
+                                            reinterpret_cast<const float2*>(ix->children_q8_meta), qterms,
+                                            reinterpret_cast<uint32_t*>(ix->q8_chan_scale));
     HIRA_CHECK_LAUNCH("hira_search (int8 pre-filter) launch");
     return HIRA_OK;
 }
@@ -709,8 +784,9 @@ static int launch_q8_scan(const SearchParams& P, int chunks, const hira_index_t*
 }
 
 bool search_q8_applicable(const hira_index_t* ix, const SearchParams& P) {
-    if (!ix->children_q8 || !ix->children_q8_meta || !ix->q8_chan_scale) return false;
+    if (!ix->children_q8 || !ix->children_q8_meta || !ix->q8_chan_scale || !ix->q8_query_scratch) return false;
     if (ix->dim != Q8_DIM || P.qnorm != nullptr || P.out_dense != nullptr || P.out_idx == nullptr) return false;
+    if (P.q2kv != nullptr || P.group > 4 * HIRA_Q8_QUERY_CHUNKS) return false;   // default head grouping, <= 16 heads per kv head
     if ((P.flags & (HIRA_LEAF_GE | HIRA_LEAF_GT)) == 0) return false;           // every child is emitted: nothing to filter
     const int tile_rows = P.tile_parents * P.bf;
     if (P.bf < 8 || P.tile_parents > Q8_MAX_TP || tile_rows % Q8_STAGE_ROWS != 0 || tile_rows > MAX_TILE_ROWS) return false;
@@ -764,7 +840,13 @@ __global__ void q8_chan_scale_kernel(const hira_index_t ix) {
     __syncthreads();
     float* out = ix.q8_chan_scale + (size_t)h * HIRA_Q8_CHAN;
     out[c] = s;
-    if (c == 0) out[Q8_DIM] = fminf(fminf(s_min[0], s_min[1]), fminf(s_min[2], s_min[3]));
+    if (c == 0) {
+        out[Q8_DIM] = fminf(fminf(s_min[0], s_min[1]), fminf(s_min[2], s_min[3]));
+        uint32_t* hint = reinterpret_cast<uint32_t*>(out + Q8_HINT);
+        hint[0] = 0u;
+        hint[1] = 0u;
+        hint[2] = 1u;   // stream every stage until a search has shown that the gates prune
+    }
 }
 
 // one 8-lane group per child slot: quantise the row (see q8_write_row in common.cuh)

@@ -59,8 +59,9 @@ class IndexState:
             self.children_q8 = z((n_heads, capC, 128), dtype=torch.int8, device=dev)
             self.children_q8_meta = z((n_heads, capC, 2), dtype=torch.float32, device=dev)
             self.q8_chan_scale = torch.ones((n_heads, L.Q8_CHAN), dtype=torch.float32, device=dev)
+            self.q8_query_scratch = z((n_heads, L.Q8_QUERY_BYTES), dtype=torch.uint8, device=dev)
         else:
-            self.children_q8 = self.children_q8_meta = self.q8_chan_scale = None
+            self.children_q8 = self.children_q8_meta = self.q8_chan_scale = self.q8_query_scratch = None
         self.status = z((1,), dtype=torch.int32, device=dev)
         self._struct = None
         self._active_parents = 0
@@ -68,7 +69,8 @@ class IndexState:
 
     ARRAYS = ("children", "values", "slot2token", "parents", "parent_radii", "parent_sqnorm", "child_counts",
               "grand_parents", "gp_radii", "gp_sqnorm", "gp_counts", "used")
-    Q8_ARRAYS = ("children_q8", "children_q8_meta", "q8_chan_scale")   # derived from `children`: not part of a checkpoint
+    # derived from `children` (and scratch): not part of a checkpoint
+    Q8_ARRAYS = ("children_q8", "children_q8_meta", "q8_chan_scale", "q8_query_scratch")
 
     @property
     def cap_children(self) -> int:
@@ -145,7 +147,7 @@ class IndexState:
             src = getattr(self, name)
             if src is None or name == "used":
                 continue
-            if name == "q8_chan_scale":
+            if name in ("q8_chan_scale", "q8_query_scratch"):
                 getattr(new, name).copy_(src)
                 continue
             getattr(new, name)[:, : src.shape[1]].copy_(src)

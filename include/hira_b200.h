@@ -101,9 +101,17 @@ typedef struct hira_index {
     void* children_q8;        /* [n_heads][cap_parents*bf][128] int8, 16-byte chunks of slot r
                                  permuted by r & 7                                             */
     float* children_q8_meta;  /* [n_heads][cap_parents*bf][2]: (quantisation step, error bound)  */
-    float* q8_chan_scale;     /* [n_heads][HIRA_Q8_CHAN]: 128 per-channel scales, their minimum  */
+    float* q8_chan_scale;     /* [n_heads][HIRA_Q8_CHAN]: 128 per-channel scales, their minimum,
+                                 and three words the searches keep (how many stages the last
+                                 search's gates kept: decides how the next one streams)          */
+    void* q8_query_scratch;   /* [n_heads][HIRA_Q8_QUERY_CHUNKS][HIRA_Q8_QUERY_BYTES] bytes that
+                                 every hira_search through the side copy rewrites (the query
+                                 heads as int8 terms): searches of ONE index that overlap on the
+                                 GPU must not both use the side copy                            */
 } hira_index_t;
 #define HIRA_Q8_CHAN 136
+#define HIRA_Q8_QUERY_CHUNKS 4
+#define HIRA_Q8_QUERY_BYTES 2112
 
 const char* hira_last_error(void);
 const char* hira_version(void);

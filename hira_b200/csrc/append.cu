@@ -255,7 +255,7 @@ append_kernel(const AppendParams P) {
                     const size_t at = (size_t)h * capC + slot;
                     q8_write_row(x, ix.q8_chan_scale + (size_t)h * HIRA_Q8_CHAN,
                                  reinterpret_cast<int8_t*>(ix.children_q8) + at * 128,
-                                 reinterpret_cast<float2*>(ix.children_q8_meta) + at, slot & 7, lane);
+                                 reinterpret_cast<uint32_t*>(ix.children_q8_meta) + at, slot & 7, lane);
                 }
             }
         };

@@ -20,6 +20,7 @@
 
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <stdint.h>
 #include <stdio.h>
 
@@ -385,12 +386,12 @@ __device__ __forceinline__ void load_vec(const T* v, float (&b)[NCH][8], int lan
 //   x        the lane's two chunks of the row in fp32 (values exactly as stored in the index)
 //   chan     per-channel scales s_i [128] followed by min_i s_i at [128]
 //   dst      the row's 128 bytes;  swz = slot & 7 permutes its 16-byte chunks
-//   meta     (step, err): k'_i = x_i / s_i, step = max |k'_i| / 127, k~_i = rint(k'_i / step),
+//   meta     (step, err) as two fp16: k'_i = x_i / s_i, step = max |k'_i| / 127 rounded up, k~_i = rint(k'_i / step),
 //            err >= ||k' - step k~||_2 + 2^-15 ||x||_2 / min_i s_i  (the second term covers the
 //            rounding of the canonical fp32 dot product for any query: ||q (.) s|| >= min s ||q||)
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void q8_write_row(const float (&x)[2][8], const float* __restrict__ chan, int8_t* dst,
-                                             float2* meta, int swz, int lane) {
+                                             uint32_t* meta, int swz, int lane) {
     float kp[2][8];
     float amax = 0.f;
     Acc2 nx{0.f, 0.f};
@@ -411,8 +412,10 @@ __device__ __forceinline__ void q8_write_row(const float (&x)[2][8], const float
     amax = fmaxf(amax, __shfl_xor_sync(gm, amax, 4));
     amax = fmaxf(amax, __shfl_xor_sync(gm, amax, 2));
     amax = fmaxf(amax, __shfl_xor_sync(gm, amax, 1));
-    const bool ok = amax > 0.f && amax < 3.0e38f;
-    const float step = ok ? __fdiv_rn(amax, 127.0f) : 1.0f;
+    // the step is stored as fp16, so it is rounded (up) to one first and the row quantised with that
+    bool ok = amax > 0.f && amax < 3.0e38f;
+    float step = ok ? __half2float(__float2half_ru(__fdiv_rn(amax, 127.0f))) : 1.0f;
+    if (!(step > 0.f) || !(step < 6.0e4f)) { ok = false; step = 1.0f; }
     Acc2 ne{0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -436,7 +439,8 @@ __device__ __forceinline__ void q8_write_row(const float (&x)[2][8], const float
         const float min_s = __ldg(chan + 128);
         const float err = ok ? sqrtf(err2) * 1.001f + 3.1e-5f * sqrtf(xsq) / min_s
                              : (amax > 0.f ? 3.0e38f : 0.f);    // a row that cannot be quantised is always a candidate
-        *meta = make_float2(step, err);
+        // rounded up; beyond the fp16 range it becomes +inf, which keeps the row a candidate
+        *meta = (uint32_t)__half_as_ushort(__float2half_ru(step)) | ((uint32_t)__half_as_ushort(__float2half_ru(err)) << 16);
     }
 }
 

@@ -32,17 +32,15 @@
 #include "search_common.cuh"
 #include "tc_common.cuh"
 #include <math_constants.h>
+#include <cuda_fp16.h>
 
 namespace hira {
 
 constexpr int Q8_DIM = 128;
 constexpr int Q8_STAGE_ROWS = 128;
 constexpr int Q8_STAGE_BYTES = Q8_STAGE_ROWS * Q8_DIM;    // 16 KB of int8 rows
-constexpr int Q8_META_BYTES = Q8_STAGE_ROWS * 8;          // (step, err) per row
-#ifndef HIRA_Q8_SLOTS
-#define HIRA_Q8_SLOTS 3
-#endif
-constexpr int Q8_SLOTS = HIRA_Q8_SLOTS;                   // stages in flight per CTA (3: three CTAs per SM)
+constexpr int Q8_META_BYTES = Q8_STAGE_ROWS * 4;          // (step, err) per row as two fp16
+constexpr int Q8_SLOTS = 4;                               // stages in flight per CTA
 constexpr int Q8_MAX_STAGES = MAX_TILE_ROWS / Q8_STAGE_ROWS;   // 8
 constexpr int Q8_NCOL = 16;                               // accumulator columns per stage (N of the MMA)
 constexpr int Q8_TMEM_COLS = Q8_MAX_STAGES * Q8_NCOL;     // 128
@@ -53,16 +51,25 @@ constexpr int Q8_HINT = 132;   // q8_chan_scale[h][132..134] as uint32: stages k
 constexpr int Q8_QBYTES = HIRA_Q8_QUERY_BYTES;            // prepared query terms of one (kv head, chunk of 4 heads)
 static_assert(Q8_QBYTES == 2048 + 64, "B operand (16 rows x 128 B) + (c1, c2, A, B) of 4 heads");
 
-struct Q8Smem {   // offsets in the 1024-byte aligned dynamic shared memory
+// All of the kernel's shared memory is dynamic and 1024-byte aligned: 72 KB, three CTAs per SM.
+struct Q8Smem {
     static constexpr int RING = 0;                                    // Q8_SLOTS stages of rows; later the candidates' scores
     static constexpr int BQ = Q8_SLOTS * Q8_STAGE_BYTES;              // 16 x 128 int8 query terms (B operand) + constants
-    static constexpr int META = BQ + 3072;                            // [Q8_MAX_STAGES][128] float2
-    static constexpr int CAND = META + Q8_MAX_STAGES * Q8_META_BYTES; // [1024] head masks
-    static constexpr int LIST = CAND + MAX_TILE_ROWS;                 // [1024] uint16 candidate rows, ascending
-    static constexpr int BAR = LIST + 2 * MAX_TILE_ROWS;              // full[Q8_SLOTS], done[Q8_MAX_STAGES], go, query
+    static constexpr int META = BQ + 2176;                            // [Q8_MAX_STAGES][128] (step, err); later the candidate list
+    static constexpr int LIST = META;                                 // [1024] uint16 (row | head mask << 10), ascending rows
+    static constexpr int SEG = META + Q8_MAX_STAGES * Q8_META_BYTES;  // [32 segments][32] candidates; during the gates: the scanned key
+    static constexpr int PCOUNT = SEG + 2 * MAX_TILE_ROWS;            // [Q8_MAX_TP] int
+    static constexpr int PMASK = PCOUNT + 4 * Q8_MAX_TP;              // [Q8_MAX_TP] bytes
+    static constexpr int GPMASK = PMASK + Q8_MAX_TP;                  // [Q8_MAX_TP] bytes
+    static constexpr int SCAN = GPMASK + Q8_MAX_TP;                   // [16] uint64
+    static constexpr int STAT = SCAN + 128;                           // [4][8] uint32
+    static constexpr int MISC = STAT + 128;                           // small scalars, see the kernel
+    static constexpr int BAR = MISC + 256;                            // full[Q8_SLOTS], done[Q8_MAX_STAGES], go, query
     static constexpr int TMEM_SLOT = BAR + 8 * (Q8_SLOTS + Q8_MAX_STAGES + 2);
     static constexpr int TOTAL = TMEM_SLOT + 16;
 };
+static_assert(2 * MAX_TILE_ROWS <= Q8_MAX_STAGES * Q8_META_BYTES, "the candidate list fits where the meta rows were");
+static_assert(Q8Smem::META % 16 == 0 && Q8Smem::BAR % 8 == 0 && Q8Smem::SCAN % 8 == 0, "bulk-copy and mbarrier alignment");
 
 // kind::i8: D = int32, A = B = signed int8, both K-major, M = 128, N = 16
 constexpr uint32_t Q8_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(Q8_NCOL >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
@@ -186,34 +193,58 @@ search_q8_prepare_kernel(const float* __restrict__ q, const float* __restrict__ 
     }
 }
 
+#ifdef HIRA_Q8_PROFILE
+__device__ unsigned long long g_q8_prof[16384][16];
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define Q8_STAMP(slot, who)                                                                       \
+    do {                                                                                          \
+        const unsigned lin__ = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;     \
+        if (threadIdx.x == (who) && lin__ < 16384) g_q8_prof[lin__][slot] = gtime();              \
+    } while (0)
+#else
+#define Q8_STAMP(slot, who) do { } while (0)
+#endif
+
 template <typename T, int GT, bool SCAN>
 __global__ void __launch_bounds__(Q8_THREADS, 3)
-search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const float2* __restrict__ k8_meta,
+search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const uint32_t* __restrict__ k8_meta,
                  const unsigned char* __restrict__ qterms, uint32_t* __restrict__ hints) {
     constexpr int NCH = 2;
     constexpr int SEARCH_GROUPS = Q8_WORKERS / GROUP;  // 16
     constexpr int PRE = 2;
-    extern __shared__ unsigned char q8_smem_raw[];
-    unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(q8_smem_raw) + 1023) & ~(uintptr_t)1023);
+    extern __shared__ __align__(1024) unsigned char sm[];
     const uint32_t s_base = smem_u32(sm);
-    unsigned char* s_cand = sm + Q8Smem::CAND;
-    unsigned short* s_list = reinterpret_cast<unsigned short*>(sm + Q8Smem::LIST);
-    const float2* s_meta = reinterpret_cast<const float2*>(sm + Q8Smem::META);
+    // Candidates: the 128 rows of a stage are 4 segments of 32 (one per worker warp); segment
+    // s * 4 + warp lists its candidate rows in ascending order as (lane | head mask << 8).
+    unsigned short* s_seg = reinterpret_cast<unsigned short*>(sm + Q8Smem::SEG);
+    unsigned short* s_list = reinterpret_cast<unsigned short*>(sm + Q8Smem::LIST);   // all segments, concatenated
+    const uint32_t* s_meta = reinterpret_cast<const uint32_t*>(sm + Q8Smem::META);
     uint32_t* s_cscore = reinterpret_cast<uint32_t*>(sm + Q8Smem::RING);   // after the last MMA: [candidate][GT]
     const uint32_t bar_full = s_base + Q8Smem::BAR;                   // [Q8_SLOTS] stage landed
     const uint32_t bar_done = bar_full + 8 * Q8_SLOTS;                // [Q8_MAX_STAGES] MMAs of the k-th stage complete
     const uint32_t bar_go = bar_done + 8 * Q8_MAX_STAGES;             // gates known
     const uint32_t bar_q = bar_go + 8;                                // prepared query terms landed
     volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(sm + Q8Smem::TMEM_SLOT);
-
-    __shared__ int s_pcount[Q8_MAX_TP];
-    __shared__ unsigned char s_pmask[Q8_MAX_TP], s_gpmask[Q8_MAX_TP];
-    __shared__ int s_qh[GT];
-    __shared__ float s_scale[GT], s_tau[GT];
-    __shared__ int s_nq, s_need, s_ncand, s_fail, s_wcount[4];
-    __shared__ uint32_t s_stat[GT][8];
-    __shared__ unsigned long long s_scan[SEARCH_GROUPS];
-    __shared__ __align__(16) float s_xkey[SCAN ? GROUP * NCH * 8 : 4];
+    int* s_pcount = reinterpret_cast<int*>(sm + Q8Smem::PCOUNT);
+    unsigned char* s_pmask = sm + Q8Smem::PMASK;
+    unsigned char* s_gpmask = sm + Q8Smem::GPMASK;
+    unsigned long long* s_scan = reinterpret_cast<unsigned long long*>(sm + Q8Smem::SCAN);
+    uint32_t (*s_stat)[8] = reinterpret_cast<uint32_t (*)[8]>(sm + Q8Smem::STAT);
+    float* s_xkey = reinterpret_cast<float*>(sm + Q8Smem::SEG);          // [lane][chunk][8]; dead before the first candidate is listed
+    int* misc = reinterpret_cast<int*>(sm + Q8Smem::MISC);
+    int* s_qh = misc;                                         // [4]
+    float* s_scale = reinterpret_cast<float*>(misc + 4);      // [4]
+    float* s_tau = reinterpret_cast<float*>(misc + 8);        // [4]
+    int& s_nq = misc[12];
+    int& s_need = misc[13];
+    int& s_ncand = misc[14];
+    int& s_fail = misc[15];
+    int* s_wcount = misc + 16;                                // [Q8_MAX_STAGES * 4] candidates per segment
+    static_assert(GROUP * NCH * 8 * 4 <= 2 * MAX_TILE_ROWS, "the scanned key fits in the candidate segments' place");
 
     const int TP = P.tile_parents;
     const int bf = P.bf;
@@ -235,6 +266,7 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
 
     // ---- 1. query heads of this kv head handled by this CTA (as in search.cu) -------------
     if (tid < GT * 8) (&s_stat[0][0])[tid] = 0;
+    if (tid < Q8_MAX_STAGES * 4) s_wcount[tid] = 0;
     int nq;
     int qh_of[GT];
     if (P.q2kv == nullptr) {
@@ -265,10 +297,15 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
         for (int j = 0; j < GT; ++j) qh_of[j] = s_qh[j < nq ? j : 0];
     }
     if (nq == 0) return;  // uniform over the CTA; nothing allocated yet
+    Q8_STAMP(0, 0);
 
     // ---- 0. barriers, tensor memory ----------------------------------------------------------
+    // The operand tiles need a 1024-byte aligned base (the kernel has no static shared memory, so the
+    // dynamic window starts aligned); should a driver ever place it otherwise, the tensor path is left
+    // out and every row of a kept parent is scored exactly.
+    const bool aligned = (s_base & 1023u) == 0u;
     if (tid == 0) {
-        s_fail = 0;
+        s_fail = aligned ? 0 : 1;
         s_need = 0;
         s_ncand = 0;
         for (int i = 0; i < Q8_SLOTS; ++i) mbar_init(bar_full + 8 * i, 1);
@@ -287,6 +324,7 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *s_tmem;
+    Q8_STAMP(1, 0);
 
     const int tile_p0 = tile * TP;
     const size_t tile_c0 = (size_t)tile_p0 * bf;
@@ -301,14 +339,14 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
 
     if (!worker) {
         // ======================= producer + MMA issuer (one thread) =========================
-        if (tid == Q8_WORKERS) {
+        if (tid == Q8_WORKERS && aligned) {
             // The first stages of a tile that holds keys are requested at once, before the gates are
             // known (they are nearly always needed; at most Q8_SLOTS stages are read for nothing when
             // the gates prune the whole tile); the rest follows the gates.
             mbar_expect_tx(bar_q, Q8_QBYTES);
             bulk_load(s_base + Q8Smem::BQ, qterms + ((size_t)h * P.n_chunks + chunk) * Q8_QBYTES, Q8_QBYTES, bar_q);
             const int8_t* rows_g = k8 + ((size_t)h * cap_children + tile_c0) * Q8_DIM;
-            const float2* meta_g = k8_meta + (size_t)h * cap_children + tile_c0;
+            const uint32_t* meta_g = k8_meta + (size_t)h * cap_children + tile_c0;
             int order[Q8_MAX_STAGES] = {0, 0, 0, 0, 0, 0, 0, 0};
             int n = spec, issued = 0;
             bool failed = false, got_go = false;
@@ -323,6 +361,7 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
             };
             for (int i = 0; i < spec; ++i) order[i] = i;
             for (; issued < spec && issued < Q8_SLOTS; ++issued) issue(issued);
+            Q8_STAMP(8, Q8_WORKERS);
             for (int k = 0; !failed; ++k) {
                 if (!got_go && k >= spec) {
                     if (!mbar_wait(bar_go, 0)) { failed = true; break; }
@@ -342,6 +381,8 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
                 const int slot = k % Q8_SLOTS;
                 if (k == 0 && !mbar_wait(bar_q, 0)) { failed = true; break; }
                 if (!mbar_wait(bar_full + 8 * slot, (k / Q8_SLOTS) & 1)) { failed = true; break; }
+                if (k == 0) Q8_STAMP(9, Q8_WORKERS);
+                if (k == 3) Q8_STAMP(11, Q8_WORKERS);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t a0 = s_base + Q8Smem::RING + slot * Q8_STAGE_BYTES, b0 = s_base + Q8Smem::BQ;
 #pragma unroll
@@ -349,6 +390,7 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
                     umma_i8(tmem + k * Q8_NCOL, umma_desc(a0 + ks * 32), umma_desc(b0 + ks * 32), Q8_IDESC, ks > 0 ? 1u : 0u);
                 umma_commit(bar_done + 8 * k);
             }
+            Q8_STAMP(10, Q8_WORKERS);
             if (failed) {
                 *reinterpret_cast<volatile int*>(&s_fail) = 1;
                 // let copies that may still be in flight land before the ring is reused (bounded)
@@ -430,8 +472,6 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
             }
         }
         unsigned long long scan_best = ~0ull;
-        // candidate masks start empty (rows of stages that are not scored stay so)
-        reinterpret_cast<uint2*>(s_cand)[tid] = make_uint2(0u, 0u);
 
         bool tile_empty;
         if (P.depth == 3) tile_empty = g0 >= used_gp;
@@ -578,7 +618,8 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
                 if (wl == 0 && best != ~0ull) atomicMin(P.scan_out + h, best);
             }
         }
-        worker_sync();   // s_need, s_pmask, s_pcount, the B operand and the cleared candidate masks are complete
+        worker_sync();   // s_need, s_pmask, s_pcount are complete; the scanned key is no longer needed
+        Q8_STAMP(2, 0);
         if (tid == 0) {
             mbar_arrive(bar_go);
             if (chunk == 0 && tile_in_use) {   // what the gates kept, for the next search's streaming mode
@@ -588,16 +629,24 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
         }
         const int need = *reinterpret_cast<volatile int*>(&s_need) | ((1 << spec) - 1);   // the stages requested up front come first
 
+        // a stage's candidates into its warp's segment, in row order
+        auto list_candidate = [&](int s, uint32_t cm) {
+            const uint32_t bal = __ballot_sync(0xffffffffu, cm != 0u);
+            if (cm) s_seg[(s * 4 + warp) * 32 + __popc(bal & ((1u << wl) - 1u))] = (unsigned short)(wl | (cm << 8));
+            if (wl == 0) s_wcount[s * 4 + warp] = __popc(bal);
+        };
+
         // ---- 5. candidates: approximate scores out of tensor memory ----------------------------
         {
-            bool failed = false;
-            {   // the prepared query terms and their constants arrive by a bulk copy
+            bool failed = !aligned;
+            if (aligned) {   // the prepared query terms and their constants arrive by a bulk copy
                 const bool ok = mbar_wait(bar_q, 0);
                 if (!__all_sync(0xffffffffu, ok)) {
                     failed = true;
                     if (wl == 0) *reinterpret_cast<volatile int*>(&s_fail) = 1;
                 }
             }
+            Q8_STAMP(3, 0);
             const float* s_qc = reinterpret_cast<const float*>(sm + Q8Smem::BQ + 2048);
             float qc[GT][4], tauj[GT];
 #pragma unroll
@@ -624,18 +673,20 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
                 const int pl = div_bf(r, bf, P.bf_magic);
                 const uint32_t pm = s_pmask[pl];
                 const bool filled = (r - pl * bf) < s_pcount[pl];
-                const float2 mt = s_meta[k * Q8_STAGE_ROWS + tid];   // (step, err)
+                const uint32_t mw = s_meta[k * Q8_STAGE_ROWS + tid];   // (step, err) as two fp16
+                const float step = __half2float(__ushort_as_half((unsigned short)(mw & 0xffffu)));
+                const float err = __half2float(__ushort_as_half((unsigned short)(mw >> 16)));
                 uint32_t cm = 0;
 #pragma unroll
                 for (int j = 0; j < GT; ++j) {
                     const float d1 = __int2float_rn((int)acc[2 * j]), d2 = __int2float_rn((int)acc[2 * j + 1]);
-                    const float approx = mt.x * __fmaf_rn(qc[j][0], d1, qc[j][1] * d2);
-                    const float margin = __fmaf_rn(qc[j][2], mt.y, qc[j][3] * mt.x);
+                    const float approx = step * __fmaf_rn(qc[j][0], d1, qc[j][1] * d2);
+                    const float margin = __fmaf_rn(qc[j][2], err, qc[j][3] * step);
                     const float upper = approx + margin * 1.001f + 1e-6f + 1e-6f * fabsf(approx);
                     if (upper >= tauj[j]) cm |= 1u << j;
                 }
                 cm = filled ? (cm & pm) : 0u;
-                s_cand[r] = (unsigned char)cm;
+                list_candidate(s, cm);
                 if (cm) {   // the exact pass reads this row in the index dtype: start it towards L2 now
                     const char* row = reinterpret_cast<const char*>(children + (tile_c0 + r) * P.dim);
                     prefetch_l2(row);
@@ -646,36 +697,41 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             worker_sync();
+            Q8_STAMP(4, 0);
             if (*reinterpret_cast<volatile int*>(&s_fail)) {   // the same for every worker after the barrier
                 // a bounded wait ran out: every filled row of a kept parent is a candidate (exact, only slower)
-                for (int r = tid; r < tile_rows; r += Q8_WORKERS) {
+                for (int s = 0; s < n_stage_tile; ++s) {
+                    const int r = s * Q8_STAGE_ROWS + tid;
                     const int pl = div_bf(r, bf, P.bf_magic);
-                    s_cand[r] = ((r - pl * bf) < s_pcount[pl] && !tile_empty) ? s_pmask[pl] : 0;
+                    list_candidate(s, ((r - pl * bf) < s_pcount[pl] && !tile_empty) ? (uint32_t)s_pmask[pl] : 0u);
                 }
                 worker_sync();
             }
         }
 
-        // ---- 6. ascending list of candidate rows (each warp lists its quarter of the tile) --------
+        // ---- 6. the segments concatenated into one ascending list (each warp copies 8 segments) ---
+        int ncand;
         {
-            const int quarter = tile_rows / 4;       // a multiple of 32
-            const int r_lo = warp * quarter;
-            int n = 0;
-            for (int base = r_lo; base < r_lo + quarter; base += 32) n += __popc(__ballot_sync(0xffffffffu, s_cand[base + wl] != 0));
-            if (wl == 0) s_wcount[warp] = n;
-            worker_sync();
-            int off = 0;
-            for (int w = 0; w < warp; ++w) off += s_wcount[w];
-            for (int base = r_lo; base < r_lo + quarter; base += 32) {
-                const bool m = s_cand[base + wl] != 0;
-                const uint32_t b = __ballot_sync(0xffffffffu, m);
-                if (m) s_list[off + __popc(b & ((1u << wl) - 1u))] = (unsigned short)(base + wl);
-                off += __popc(b);
+            const int cnt = wl < n_stage_tile * 4 ? s_wcount[wl] : 0;   // lane i: candidates of segment i
+            int incl = cnt;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int t = __shfl_up_sync(0xffffffffu, incl, d);
+                if (wl >= d) incl += t;
             }
-            if (tid == Q8_WORKERS - 1) s_ncand = off;   // the last warp ends at the total
+            ncand = __shfl_sync(0xffffffffu, incl, 31);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int seg = warp * 8 + i;
+                const int c = __shfl_sync(0xffffffffu, cnt, seg), off = __shfl_sync(0xffffffffu, incl, seg) - c;
+                if (wl < c) {
+                    const int e = s_seg[seg * 32 + wl];
+                    s_list[off + wl] = (unsigned short)((seg * 32 + (e & 31)) | ((e >> 8) << 10));
+                }
+            }
         }
         worker_sync();
-        const int ncand = s_ncand;
+        Q8_STAMP(5, 0);
 
         // ---- 7. exact scores of the candidates, canonical arithmetic ---------------------------
         {
@@ -689,23 +745,24 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
 #pragma unroll
                 for (int u = 0; u < XR; ++u) {
                     e[u] = (it * XR + u) * SEARCH_GROUPS + grp;
-                    r[u] = e[u] < ncand ? s_list[e[u]] : -1;
+                    r[u] = e[u] < ncand ? s_list[e[u]] : -1;   // row | head mask << 10
 #pragma unroll
                     for (int ci = 0; ci < NCH; ++ci)
-                        raw[u][ci] = r[u] >= 0 ? load_chunk_stream<T>(children + (tile_c0 + r[u]) * P.dim, lane + GROUP * ci)
+                        raw[u][ci] = r[u] >= 0 ? load_chunk_stream<T>(children + (tile_c0 + (r[u] & 1023)) * P.dim, lane + GROUP * ci)
                                                : zero_chunk<T>();
                 }
 #pragma unroll
                 for (int u = 0; u < XR; ++u) {
                     const float d = gate_dot_raw<T, GT, NCH>(raw[u], qreg, lane);
                     if (writer && r[u] >= 0) {
-                        const bool em = head_on && ((s_cand[r[u]] >> my_head) & 1u) && d >= leaf_thr;
+                        const bool em = head_on && ((r[u] >> (10 + my_head)) & 1) && d >= leaf_thr;
                         s_cscore[e[u] * GT + my_head] = em ? __float_as_uint(d) : NOT_EMITTED;
                     }
                 }
             }
         }
         worker_sync();
+        Q8_STAMP(6, 0);
 
         // ---- 8. ordered compaction, one warp per head -------------------------------------------
         if (warp < nq) {
@@ -721,7 +778,7 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
                 const uint32_t b = __ballot_sync(0xffffffffu, k);
                 if (k) {
                     const int pos = offset + __popc(b & ((1u << wl) - 1u));
-                    P.out_idx[out_base + pos] = (int32_t)(tile_c0 + s_list[e]);
+                    P.out_idx[out_base + pos] = (int32_t)(tile_c0 + (s_list[e] & 1023));
                     P.out_score[out_base + pos] = __fmul_rn(__uint_as_float(bits), scale);
                 }
                 offset += __popc(b);
@@ -744,6 +801,7 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
         }
     }
 
+    Q8_STAMP(7, 0);
     // ---- 9. tensor memory back ----------------------------------------------------------------------
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -756,7 +814,7 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const floa
 template <typename T, int GT, bool SCAN>
 static int launch_q8(SearchParams P, int chunks, const hira_index_t* ix, cudaStream_t stream) {
     auto kern = search_q8_kernel<T, GT, SCAN>;
-    const size_t smem = Q8Smem::TOTAL + 1024;
+    const size_t smem = Q8Smem::TOTAL;
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) {
         set_error("hira_search (int8 pre-filter): cudaFuncSetAttribute(%zu B smem): %s", smem, cudaGetErrorString(e));
@@ -771,7 +829,7 @@ static int launch_q8(SearchParams P, int chunks, const hira_index_t* ix, cudaStr
     HIRA_CHECK_LAUNCH("hira_search (int8 pre-filter, query terms) launch");
     dim3 grid((unsigned)chunks, (unsigned)P.n_tiles_active, (unsigned)P.n_heads);
     kern<<<grid, Q8_THREADS, smem, stream>>>(P, reinterpret_cast<const int8_t*>(ix->children_q8),
-                                            reinterpret_cast<const float2*>(ix->children_q8_meta), qterms,
+                                            reinterpret_cast<const uint32_t*>(ix->children_q8_meta), qterms,
                                             reinterpret_cast<uint32_t*>(ix->q8_chan_scale));
     HIRA_CHECK_LAUNCH("hira_search (int8 pre-filter) launch");
     return HIRA_OK;
@@ -862,7 +920,7 @@ __global__ void q8_quantize_kernel(const hira_index_t ix) {
     float x[2][8];
     load_vec<T, 2>(row, x, lane, Q8_DIM);
     q8_write_row(x, ix.q8_chan_scale + (size_t)h * HIRA_Q8_CHAN, reinterpret_cast<int8_t*>(ix.children_q8) + w * Q8_DIM,
-                 reinterpret_cast<float2*>(ix.children_q8_meta) + w, (int)(slot & 7), lane);
+                 reinterpret_cast<uint32_t*>(ix.children_q8_meta) + w, (int)(slot & 7), lane);
 }
 
 int q8_refresh(const hira_index_t* ix, cudaStream_t s) {
@@ -883,6 +941,12 @@ int q8_refresh(const hira_index_t* ix, cudaStream_t s) {
 }
 
 }  // namespace hira
+
+#ifdef HIRA_Q8_PROFILE
+extern "C" int hira_q8_profile_read(unsigned long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, hira::g_q8_prof, sizeof(hira::g_q8_prof)) == cudaSuccess ? 0 : -1;
+}
+#endif
 
 extern "C" int hira_q8_refresh(const hira_index_t* ix, void* stream) {
     int rc = hira::validate_index(ix, false);

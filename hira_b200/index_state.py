@@ -49,7 +49,7 @@ class IndexState:
             self.grand_parents = self.gp_radii = self.gp_sqnorm = self.gp_counts = None
         self.used = z((n_heads, 4), dtype=torch.int32, device=dev)
         # int8 side copy of the children for the tensor-core pre-filter of the search (D = 128):
-        # +50 % on the bf16 keys' memory (128 B + 8 B per slot), about half the search's traffic
+        # +52 % on the bf16 keys' memory (128 B + 4 B per slot), about half the search's traffic
         if int8_copy is None:
             int8_copy = dim == 128 and self.device.type == "cuda"
         if int8_copy and dim != 128:
@@ -57,7 +57,7 @@ class IndexState:
         self.int8_copy = bool(int8_copy)
         if self.int8_copy:
             self.children_q8 = z((n_heads, capC, 128), dtype=torch.int8, device=dev)
-            self.children_q8_meta = z((n_heads, capC, 2), dtype=torch.float32, device=dev)
+            self.children_q8_meta = z((n_heads, capC), dtype=torch.int32, device=dev)   # (step, error bound) as two fp16
             self.q8_chan_scale = torch.ones((n_heads, L.Q8_CHAN), dtype=torch.float32, device=dev)
             self.q8_query_scratch = z((n_heads, L.Q8_QUERY_BYTES), dtype=torch.uint8, device=dev)
         else:

@@ -100,7 +100,7 @@ typedef struct hira_index {
        has no counterpart.                                                                       */
     void* children_q8;        /* [n_heads][cap_parents*bf][128] int8, 16-byte chunks of slot r
                                  permuted by r & 7                                             */
-    float* children_q8_meta;  /* [n_heads][cap_parents*bf][2]: (quantisation step, error bound)  */
+    uint32_t* children_q8_meta; /* [n_heads][cap_parents*bf]: (quantisation step, error bound) as two fp16 */
     float* q8_chan_scale;     /* [n_heads][HIRA_Q8_CHAN]: 128 per-channel scales, their minimum,
                                  and three words the searches keep (how many stages the last
                                  search's gates kept: decides how the next one streams)          */

@@ -149,7 +149,7 @@ class DecodeBench:
     (batch, kv head) groups of `ctx` keys each, `group` query heads per group."""
 
     def __init__(self, w: W.Workload, n_groups: int, ctx: int, appends: int, dev, seed_offset: int = 0,
-                 use_tc: bool = True, exchange=None, int8_copy: bool = True):
+                 use_tc: bool = True, exchange=None, int8_copy: bool = True, n_iters: int = 1, balance_rounds: int = 0):
         from hira_b200 import _lib as L
         from hira_b200 import index_state as S
         self.L, self.S, self.w, self.dev = L, S, w, dev
@@ -168,7 +168,8 @@ class DecodeBench:
         cent2 = W.random_centres(n_groups, self.k1, self.k2, 8 + seed_offset, dev)
         torch.cuda.synchronize()
         t1 = time.time()
-        S.build(st, keys, vals, cent_idx1=cent1, cent_idx2=cent2, n_iters=1, use_tensor_cores=use_tc)
+        S.build(st, keys, vals, cent_idx1=cent1, cent_idx2=cent2, n_iters=n_iters, balance_rounds=balance_rounds,
+                use_tensor_cores=use_tc)
         torch.cuda.synchronize()
         self.build_s = time.time() - t1
         # threshold samples: 1000 stored key rows per head (filled slots are the first ctx of a fresh build)
@@ -455,7 +456,7 @@ def secondary_cfg1(args, dev, barrier_local, peak):
     b.make_new_keys(steps + warm, 9100)
     c = b.counters()
     side = None if args.serial else torch.cuda.Stream(device=dev)
-    r = b.timed_loop(steps, warm, barrier_local, fused=b.search_kernel == "search_kernel", side=side)
+    r = b.timed_loop(steps, warm, barrier_local, fused=True, side=side)   # small launch: the separate scan would not hide
     dense_ms = b.time_dense()
     step_us = r["total_ms"] / steps * 1e3
     ach = c["search_bytes"] / (r["search_ms"] * 1e-3) / 1e9
@@ -463,6 +464,26 @@ def secondary_cfg1(args, dev, barrier_local, peak):
             "append_us": r["append_ms"] * 1e3, "algorithmic_bytes": c["search_bytes"] + c["attn_bytes"] + c["append_bytes"],
             "search_bytes": c["search_bytes"], "search_gbs": ach, "frac": ach / peak,
             "scanned_fraction": c["scanned_fraction"], "dense_attention_us": dense_ms * 1e3, "build_ms": b.build_s * 1e3}
+
+
+def secondary_clustered(args, dev, barrier_local, peak):
+    """Control: configuration 1's shape on clustered keys (1,024 tight clusters per head), index built
+    with 4 Lloyd iterations and 4 capacity-aware rounds -- data on which the ball gates do prune, to
+    show the step when the hierarchy has something to skip."""
+    w = W.CLUSTERED
+    steps, warm = args.steps, args.warmup
+    b = DecodeBench(w, w.kv_heads, w.context, steps + warm + 8, dev, seed_offset=900, use_tc=not args.no_tc,
+                    n_iters=4, balance_rounds=4)
+    b.make_queries(N_QUERY_SETS, 350)
+    b.make_new_keys(steps + warm, 9300)
+    c = b.counters()
+    side = None if args.serial else torch.cuda.Stream(device=dev)
+    r = b.timed_loop(steps, warm, barrier_local, fused=True, side=side)
+    ach = c["search_bytes"] / (r["search_ms"] * 1e-3) / 1e9
+    return {"workload": w.name, "note": "control, not a BASELINE configuration: clustered keys, 4 Lloyd iterations, 4 balanced rounds",
+            "step_us": r["total_ms"] / steps * 1e3, "search_us": r["search_ms"] * 1e3, "sparse_attn_us": r["attn_ms"] * 1e3,
+            "scanned_fraction": c["scanned_fraction"], "selected_per_qhead": c["selected_per_qhead"],
+            "search_bytes": c["search_bytes"], "search_gbs": ach, "build_ms": b.build_s * 1e3}
 
 
 def secondary_cfg3(args, dev):
@@ -570,6 +591,61 @@ def secondary_cfg4(args, dev, rank, world, dist, barrier, peak):
             "merged_vs_one_rank_max_rel_err": check}
 
 
+def pruning_table(args):
+    """Index quality against pruning power (`--pruning-table`): for the two data distributions
+    (cfg0: per-channel scaled Gaussian, fp32, 4,096 keys; cfg1: RoPE + outlier channels, bf16, 32,768
+    keys; 8 KV heads, one query head each, 3 levels, tau = the exact 2 % score), branching factors,
+    Lloyd iterations and capacity-aware assignment rounds: the share of leaf rows the gates let
+    through (from the search kernel's own counters), the mean leaf-ball radius against the
+    threshold, and the search time.  One JSON line per setting."""
+    from hira_b200 import _lib as L
+    from hira_b200 import index_state as S
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    rows = []
+    for w in (W.CFG0, W.CFG1, W.CLUSTERED):
+        keys, vals, q = W.make_inputs(w, dev)
+        h, n, d = keys.shape
+        q = q.view(h, w.group, d)[:, 0].contiguous()          # one query head per KV head
+        q_hat = (q / q.norm(dim=-1, keepdim=True)).contiguous()
+        sc = torch.einsum("hd,hnd->hn", q_hat, keys.float())
+        tau = torch.sort(sc, dim=-1, descending=True).values[:, max(1, n // 50) - 1].contiguous()
+        for bf in (8, 16, 32, 64):
+            k1 = -(-n // bf)
+            k2 = -(-k1 // bf)
+            for iters in (1, 4, 10):
+                for rounds in (0, 4):
+                    st = S.IndexState(n_heads=h, dim=d, vdim=d, bf=bf, depth=3, cap_parents=k2 * bf, dtype=w.dtype,
+                                      vdtype=w.dtype, device=dev)
+                    S.build(st, keys, vals, cent_idx1=W.random_centres(h, n, k1, 7, dev),
+                            cent_idx2=W.random_centres(h, k1, k2, 8, dev), n_iters=iters, balance_rounds=rounds,
+                            use_tensor_cores=False)
+                    stats = S.new_stats(h, dev)
+                    flags = L.HIRA_GATE_GE | L.HIRA_LEAF_GE
+                    _, compact = S.search(st, q_hat, tau, flags=flags, want_compact=True, stats=stats)
+                    a, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    for _ in range(3):
+                        S.search(st, q_hat, tau, flags=flags, compact=compact)
+                    a.record()
+                    for _ in range(10):
+                        S.search(st, q_hat, tau, flags=flags, compact=compact)
+                    e.record()
+                    torch.cuda.synchronize()
+                    s = stats.to(torch.int64).sum(dim=0).tolist()
+                    filled = st.child_counts > 0
+                    rows.append({"data": w.name.split("_")[0], "keys": n, "bf": bf, "lloyd_iterations": iters,
+                                 "balance_rounds": rounds, "scanned_fraction": s[6] / float(h * n),
+                                 "parents_kept_fraction": s[3] / float(max(1, s[2])),
+                                 "gp_kept_fraction": s[1] / float(max(1, s[0])),
+                                 "mean_leaf_radius": float(st.parent_radii[filled].mean()),
+                                 "mean_gp_radius": float(st.gp_radii[:, :k2].mean()),
+                                 "tau_mean": float(tau.mean()), "selected": s[5] / float(h),
+                                 "search_us": a.elapsed_time(e) * 100.0})
+                    print(json.dumps(rows[-1]), flush=True)
+                    del st
+    return rows
+
+
 # ----------------------------------------------------------------------------------
 # our arm
 # ----------------------------------------------------------------------------------
@@ -665,6 +741,11 @@ def run_ours(args):
                 secondary["cfg1"] = secondary_cfg1(args, dev, torch.cuda.synchronize, peak)
             except Exception as ex:  # reported, never fatal for the headline
                 secondary["cfg1"] = {"error": repr(ex)}
+            torch.cuda.empty_cache()
+            try:
+                secondary["clustered"] = secondary_clustered(args, dev, torch.cuda.synchronize, peak)
+            except Exception as ex:
+                secondary["clustered"] = {"error": repr(ex)}
             torch.cuda.empty_cache()
             try:
                 secondary["cfg3"] = secondary_cfg3(args, dev)
@@ -855,11 +936,15 @@ def main():
     ap.add_argument("--unfused", dest="fused", action="store_false",
                     help="separate parent scan in the append (default with the int8 pre-filter)")
     ap.add_argument("--no-int8", action="store_true", help="search without the int8 side copy (plain streaming kernel)")
+    ap.add_argument("--pruning-table", action="store_true",
+                    help="print scanned fraction against branching factor, Lloyd iterations and balanced rounds, then exit")
     ap.add_argument("--traffic-key", default=None, help=argparse.SUPPRESS)
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
-    if args.impl == "reference":
+    if args.pruning_table:
+        pruning_table(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

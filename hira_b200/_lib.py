@@ -113,7 +113,7 @@ def _declare(lib):
     lib.hira_build_workspace_bytes.restype = SZ
     lib.hira_build_workspace_bytes.argtypes = [IX, I32]
     lib.hira_build.restype = C.c_int
-    lib.hira_build.argtypes = [IX, P, P, I32, I64, I64, I32, P, P, I32, I32, P, P, SZ, P]
+    lib.hira_build.argtypes = [IX, P, P, I32, I64, I64, I32, P, P, I32, I32, I32, P, P, SZ, P]
     lib.hira_q8_refresh.restype = C.c_int
     lib.hira_q8_refresh.argtypes = [IX, P]
     lib.hira_recompute_radii.restype = C.c_int

@@ -53,6 +53,9 @@ class HiraCacheLayer(CacheLayerMixin):
 
     def lazy_initialization(self, key_states, value_states):
         self.dim = key_states.shape[-1]
+        self.vdim = value_states.shape[-1]
+        self.vdtype = value_states.dtype
+        self._queue_k = self._queue_v = None
         self.B = key_states.shape[0]
         self.H_kv = key_states.shape[-3]
         self.dtype = key_states.dtype
@@ -65,10 +68,30 @@ class HiraCacheLayer(CacheLayerMixin):
         self.is_initialized = True
 
     def _reset_queue(self):
-        shape = (self.B, self.H_kv, 0, self.dim)
-        self.queued_keys = torch.empty(shape, dtype=self.dtype, device=self.device)
-        self.queued_values = torch.empty(shape, dtype=self.dtype, device=self.device)
+        """The queue of not-yet-indexed tokens is a pre-allocated buffer of `update_every` rows per
+        head; `queued_keys` / `queued_values` are views of its filled part.  (The reference grows the
+        queue by `torch.cat` on every token, cache/hira_cache.py:121-124.)"""
+        if getattr(self, "_queue_k", None) is None:
+            cap = max(1, int(self.update_every))
+            self._queue_k = torch.empty((self.B, self.H_kv, cap, self.dim), dtype=self.dtype, device=self.device)
+            self._queue_v = torch.empty((self.B, self.H_kv, cap, self.vdim), dtype=self.vdtype, device=self.device)
         self.queued_len = 0
+        self.queued_keys = self._queue_k[:, :, :0]
+        self.queued_values = self._queue_v[:, :, :0]
+
+    def _enqueue(self, key_states: torch.Tensor, value_states: torch.Tensor):
+        n = key_states.shape[-2]
+        if self.queued_len + n > self._queue_k.shape[2]:     # more tokens at once than a flush period: make room
+            cap = max(2 * self._queue_k.shape[2], self.queued_len + n)
+            for name, src in (("_queue_k", self._queue_k), ("_queue_v", self._queue_v)):
+                bigger = torch.empty(src.shape[:2] + (cap, src.shape[3]), dtype=src.dtype, device=src.device)
+                bigger[:, :, : self.queued_len] = src[:, :, : self.queued_len]
+                setattr(self, name, bigger)
+        self._queue_k[:, :, self.queued_len:self.queued_len + n] = key_states
+        self._queue_v[:, :, self.queued_len:self.queued_len + n] = value_states
+        self.queued_len += n
+        self.queued_keys = self._queue_k[:, :, : self.queued_len]
+        self.queued_values = self._queue_v[:, :, : self.queued_len]
 
     def update(self, key_states: torch.Tensor, value_states: torch.Tensor,
                cache_kwargs: dict[str, Any] | None = None, *args, **kwargs):
@@ -82,9 +105,7 @@ class HiraCacheLayer(CacheLayerMixin):
                             indexer=self.indexer, searcher=self.searcher),
                 None,
             )
-        self.queued_keys = torch.cat([self.queued_keys, key_states], dim=-2)
-        self.queued_values = torch.cat([self.queued_values, value_states], dim=-2)
-        self.queued_len += key_states.shape[-2]
+        self._enqueue(key_states, value_states)
         if self.queued_len >= self.update_every:
             self.update_index()
         return (

@@ -33,6 +33,7 @@ class HiraConfig:
     max_context: Optional[int] = None  # pre-allocate the index for this many keys per head
     gate: str = "ge"                   # tree gate used by hira_attention: "ge" or "gt"
     use_tensor_cores: bool = True
+    balance_rounds: int = 0            # capacity-aware assignment rounds of the index build (0: the reference's rule)
 
     @classmethod
     def from_dict(cls, config_dict: dict) -> "HiraConfig":
@@ -65,6 +66,8 @@ class HiraConfig:
                 kw["max_context"] = self.max_context
             if not self.use_tensor_cores:
                 kw["use_tensor_cores"] = False
+            if self.balance_rounds:
+                kw["balance_rounds"] = self.balance_rounds
         return kw
 
     def get_searcher_kwargs(self) -> dict:

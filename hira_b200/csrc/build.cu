@@ -162,14 +162,16 @@ static int launch_assign_cc(const T* points, long long p_head_stride, const T* c
 
 static int run_assign(int dtype, const void* points, long long p_head_stride, const void* cents, float* csq,
                       int n_heads, int n, int k, int dim, int use_tc, int32_t* out_idx, float* out_d2,
-                      cudaStream_t s) {
+                      cudaStream_t s, bool csq_ready = false) {
     const long long rows = (long long)n_heads * k;
     const int blocks = (int)((rows + 255) / 256);
-    if (dtype == HIRA_BF16)
-        sqnorm_seq_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(cents), rows, dim, csq);
-    else
-        sqnorm_seq_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const float*>(cents), rows, dim, csq);
-    HIRA_CHECK_LAUNCH("sqnorm launch");
+    if (!csq_ready) {
+        if (dtype == HIRA_BF16)
+            sqnorm_seq_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(cents), rows, dim, csq);
+        else
+            sqnorm_seq_kernel<<<blocks, 256, 0, s>>>(reinterpret_cast<const float*>(cents), rows, dim, csq);
+        HIRA_CHECK_LAUNCH("sqnorm launch");
+    }
     if (use_tc && assign_tc_supported(dtype, n, k, dim))
         return launch_assign_tc(points, p_head_stride, cents, csq, n_heads, n, k, dim, out_idx, out_d2, s);
     if (dtype == HIRA_BF16)
@@ -208,12 +210,19 @@ __global__ void gather_centres_kernel(const T* __restrict__ points, long long p_
 // bounded barrier wait ran out -- must not reach the segment arithmetic below: the point goes to
 // centre 0 at distance 0 (so that every later index stays in range) and the caller is told through
 // the status word.
+// `placed` (balanced rounds): points that already have a slot sort behind every real segment.
 __global__ void make_sort_keys_kernel(const int32_t* __restrict__ idx, const float* __restrict__ d2, int n, int k,
-                                      long long total, uint64_t* __restrict__ keys, uint32_t* __restrict__ vals,
+                                      long long total, long long n_seg, const int32_t* __restrict__ placed,
+                                      uint64_t* __restrict__ keys, uint32_t* __restrict__ vals,
                                       int32_t* __restrict__ status) {
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const int h = (int)(i / n);
+    if (placed && placed[i] >= 0) {
+        keys[i] = (uint64_t)n_seg << 32;
+        vals[i] = (uint32_t)(i - (long long)h * n);
+        return;
+    }
     int c = idx[i];
     float d = d2[i];
     if (c < 0 || c >= k || !(d >= 0.f)) {
@@ -281,24 +290,57 @@ __global__ void means_kernel(const T* __restrict__ points, long long p_head_stri
     }
 }
 
-// per head: exclusive scans of free slots and overflow counts over the centres
+// Balanced rounds: centres that are full drop out of the next assignment (score +inf).
+__global__ void mask_full_centres_kernel(const float* __restrict__ csq, const int32_t* __restrict__ filled, int bf,
+                                         long long n_seg, float* __restrict__ csq_masked) {
+    const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= n_seg) return;
+    csq_masked[c] = filled[c] < bf ? csq[c] : CUDART_INF_F;
+}
+
+// An intermediate balanced round: every centre accepts, closest first, as many of the points that
+// chose it as it still has room for; the rest stay unplaced for the next round.
+__global__ void accept_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restrict__ sorted_ids,
+                              const int32_t* __restrict__ start, const int32_t* __restrict__ filled, int n, int k,
+                              int bf, long long total, long long n_seg, int32_t* __restrict__ slot) {
+    const long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= total) return;
+    const long long seg = (long long)(keys[j] >> 32);
+    if (seg >= n_seg) return;   // placed earlier
+    const int h = (int)(seg / k);
+    const int c = (int)(seg - (long long)h * k);
+    const int rank = (int)(j - start[seg]);
+    const int have = filled[seg];
+    if (rank < bf - have) slot[(size_t)h * n + sorted_ids[j]] = c * bf + have + rank;
+}
+__global__ void accept_counts_kernel(const int32_t* __restrict__ start, int bf, long long n_seg,
+                                     int32_t* __restrict__ filled) {
+    const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= n_seg) return;
+    const int cnt = start[c + 1] - start[c], room = bf - filled[c];
+    filled[c] += cnt < room ? cnt : room;
+}
+
+// per head: exclusive scans of free slots and overflow counts over the centres; `filled` = slots
+// taken in earlier balanced rounds (all zero without them)
 __global__ void __launch_bounds__(1024)
-capacity_scan_kernel(const int32_t* __restrict__ start, int k, int bf, int32_t* __restrict__ free_base,
-                     int32_t* __restrict__ left_base, int32_t* __restrict__ fill_cnt) {
+capacity_scan_kernel(const int32_t* __restrict__ start, const int32_t* __restrict__ filled, int k, int bf,
+                     int32_t* __restrict__ free_base, int32_t* __restrict__ left_base, int32_t* __restrict__ fill_cnt) {
     typedef cub::BlockScan<int, 1024> Scan;
     __shared__ typename Scan::TempStorage tmp;
     __shared__ int s_total_left;
     const int h = blockIdx.x;
     const int32_t* st = start + (size_t)h * k;
+    const int32_t* fl = filled + (size_t)h * k;
     int32_t* fb = free_base + (size_t)h * (k + 1);
     int32_t* lb = left_base + (size_t)h * (k + 1);
     int carry_f = 0, carry_l = 0;
     for (int c0 = 0; c0 < k; c0 += 1024) {
         const int c = c0 + threadIdx.x;
-        int cnt = 0;
-        if (c < k) cnt = st[c + 1] - st[c];
-        const int fr = (c < k) ? max(bf - cnt, 0) : 0;
-        const int lf = (c < k) ? max(cnt - bf, 0) : 0;
+        int cnt = 0, room = 0;
+        if (c < k) { cnt = st[c + 1] - st[c]; room = bf - fl[c]; }
+        const int fr = (c < k) ? max(room - cnt, 0) : 0;
+        const int lf = (c < k) ? max(cnt - room, 0) : 0;
         int ef, el, tf, tl;
         Scan(tmp).ExclusiveSum(fr, ef, tf);
         __syncthreads();
@@ -311,32 +353,35 @@ capacity_scan_kernel(const int32_t* __restrict__ start, int k, int bf, int32_t* 
     __syncthreads();
     const int total_left = s_total_left;
     for (int c = threadIdx.x; c < k; c += 1024) {
-        const int cnt = st[c + 1] - st[c];
-        const int fr = max(bf - cnt, 0);
+        const int cnt = st[c + 1] - st[c], room = bf - fl[c];
+        const int fr = max(room - cnt, 0);
         int recv = total_left - fb[c];
         recv = recv < 0 ? 0 : (recv > fr ? fr : recv);
-        fill_cnt[(size_t)h * k + c] = min(cnt, bf) + recv;
+        fill_cnt[(size_t)h * k + c] = fl[c] + min(cnt, room) + recv;
     }
 }
 
-// slot (centre*bf + rank) of every point inside its level
+// slot (centre*bf + rank) of every point inside its level (the last round: everything is placed)
 __global__ void placement_kernel(const uint64_t* __restrict__ keys, const uint32_t* __restrict__ sorted_ids,
-                                 const int32_t* __restrict__ start, const int32_t* __restrict__ free_base,
-                                 const int32_t* __restrict__ left_base, int n, int k, int bf, long long total,
-                                 int32_t* __restrict__ slot) {
+                                 const int32_t* __restrict__ start, const int32_t* __restrict__ filled,
+                                 const int32_t* __restrict__ free_base, const int32_t* __restrict__ left_base, int n,
+                                 int k, int bf, long long total, long long n_seg, int32_t* __restrict__ slot) {
     const long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= total) return;
     const long long seg = (long long)(keys[j] >> 32);
+    if (seg >= n_seg) return;   // placed in an earlier balanced round
     const int h = (int)(seg / k);
     const int c = (int)(seg - (long long)h * k);
     const int rank = (int)(j - start[seg]);
+    const int32_t* fl = filled + (size_t)h * k;
+    const int room = bf - fl[c];
     int s;
-    if (rank < bf) {
-        s = c * bf + rank;
+    if (rank < room) {
+        s = c * bf + fl[c] + rank;
     } else {
         const int32_t* fb = free_base + (size_t)h * (k + 1);
         const int32_t* st = start + (size_t)h * k;
-        const int L = left_base[(size_t)h * (k + 1) + c] + (rank - bf);
+        const int L = left_base[(size_t)h * (k + 1) + c] + (rank - room);
         // largest c2 with fb[c2] <= L and a free slot there: upper_bound(fb, L) - 1
         int lo = 0, hi = k;  // search in fb[0..k]
         while (lo < hi) {
@@ -346,7 +391,7 @@ __global__ void placement_kernel(const uint64_t* __restrict__ keys, const uint32
         // skip centres without free slots (fb equal runs): lo is the last index with fb[lo] <= L,
         // which has fb[lo+1] > L, hence at least one free slot
         const int cnt2 = st[lo + 1] - st[lo];
-        s = lo * bf + min(cnt2, bf) + (L - fb[lo]);
+        s = lo * bf + fl[lo] + min(cnt2, bf - fl[lo]) + (L - fb[lo]);
     }
     slot[(size_t)h * n + sorted_ids[j]] = s;
 }
@@ -527,8 +572,8 @@ __global__ void export_rows_kernel(const T* __restrict__ src, const int32_t* __r
 // ---------------------------------------------------------------------------
 struct BuildWs {
     size_t total = 0;
-    size_t cents1, cents2, csq, a_idx, a_d2, keys_in, keys_out, vals_in, vals_out, start, fill1, fill2, fbase,
-        lbase, slot1, slot2, cub;
+    size_t cents1, cents2, csq, csq_masked, filled, a_idx, a_d2, keys_in, keys_out, vals_in, vals_out, start, fill1,
+        fill2, fbase, lbase, slot1, slot2, cub;
     size_t cub_bytes = 0;
 };
 
@@ -543,13 +588,15 @@ static BuildWs carve(const hira_index_t* ix, int n_keys) {
     w.cents1 = take(H * k1 * D * es);
     w.cents2 = take(H * k2 * D * es);
     w.csq = take(H * k1 * 4);
+    w.csq_masked = take(H * k1 * 4);
+    w.filled = take(H * k1 * 4);
     w.a_idx = take(H * n * 4);
     w.a_d2 = take(H * n * 4);
     w.keys_in = take(H * n * 8);
     w.keys_out = take(H * n * 8);
     w.vals_in = take(H * n * 4);
     w.vals_out = take(H * n * 4);
-    w.start = take((H * k1 + 1) * 4);
+    w.start = take((H * k1 + 2) * 4);
     w.fill1 = take(H * k1 * 4);
     w.fill2 = take(H * k2 * 4);
     w.fbase = take(H * (k1 + 1) * 4);
@@ -569,7 +616,7 @@ static BuildWs carve(const hira_index_t* ix, int n_keys) {
 // and per-centre filled count.
 template <typename T>
 static int build_level(int dtype, const T* points, long long p_head_stride, int n_heads, int n, int k, int bf,
-                       int dim, const int32_t* cent_idx, int n_iters, int use_tc, T* cents, char* base,
+                       int dim, const int32_t* cent_idx, int n_iters, int balance_rounds, int use_tc, T* cents, char* base,
                        const BuildWs& w, int32_t* slot, int32_t* fill, int32_t* status, cudaStream_t s) {
     const long long total = (long long)n_heads * n;
     const long long n_seg = (long long)n_heads * k;
@@ -596,7 +643,7 @@ static int build_level(int dtype, const T* points, long long p_head_stride, int 
         int rc = run_assign(dtype, points, p_head_stride, cents, csq, n_heads, n, k, dim, use_tc, a_idx, a_d2, s);
         if (rc != HIRA_OK) return rc;
         const int blocks = (int)((total + 255) / 256);
-        make_sort_keys_kernel<<<blocks, 256, 0, s>>>(a_idx, a_d2, n, k, total, keys_in, vals_in, status);
+        make_sort_keys_kernel<<<blocks, 256, 0, s>>>(a_idx, a_d2, n, k, total, n_seg, nullptr, keys_in, vals_in, status);
         HIRA_CHECK_LAUNCH("sort keys launch");
         size_t cub_bytes = w.cub_bytes;
         cudaError_t e = cub::DeviceRadixSort::SortPairs(base + w.cub, cub_bytes, keys_in, keys_out, vals_in, vals_out,
@@ -612,10 +659,37 @@ static int build_level(int dtype, const T* points, long long p_head_stride, int 
             HIRA_CHECK_LAUNCH("means launch");
         }
     }
-    capacity_scan_kernel<<<n_heads, 1024, 0, s>>>(start, k, bf, fbase, lbase, fill);
-    HIRA_CHECK_LAUNCH("capacity scan launch");
+    // ---- capacity-aware rounds: points that did not fit under their nearest centre choose again
+    // among the centres that still have room, closest first, `balance_rounds` times; what is left
+    // after that (and everything beyond the bf closest when balance_rounds == 0, the reference's
+    // rule, indexer/cuda.py:252-334) goes to the free slots in (centre, distance) order.
+    int32_t* filled = reinterpret_cast<int32_t*>(base + w.filled);
+    float* csq_masked = reinterpret_cast<float*>(base + w.csq_masked);
+    cudaMemsetAsync(filled, 0, (size_t)n_seg * 4, s);
     const int blocks = (int)((total + 255) / 256);
-    placement_kernel<<<blocks, 256, 0, s>>>(keys_out, vals_out, start, fbase, lbase, n, k, bf, total, slot);
+    const int seg_blocks = (int)((n_seg + 255) / 256);
+    if (balance_rounds > 0) cudaMemsetAsync(slot, 0xff, (size_t)total * 4, s);
+    for (int r = 0; r < balance_rounds; ++r) {
+        accept_kernel<<<blocks, 256, 0, s>>>(keys_out, vals_out, start, filled, n, k, bf, total, n_seg, slot);
+        accept_counts_kernel<<<seg_blocks, 256, 0, s>>>(start, bf, n_seg, filled);
+        mask_full_centres_kernel<<<seg_blocks, 256, 0, s>>>(csq, filled, bf, n_seg, csq_masked);
+        HIRA_CHECK_LAUNCH("balanced round launch");
+        int rc = run_assign(dtype, points, p_head_stride, cents, csq_masked, n_heads, n, k, dim, use_tc, a_idx, a_d2, s, true);
+        if (rc != HIRA_OK) return rc;
+        make_sort_keys_kernel<<<blocks, 256, 0, s>>>(a_idx, a_d2, n, k, total, n_seg, slot, keys_in, vals_in, status);
+        HIRA_CHECK_LAUNCH("sort keys launch");
+        size_t cub_bytes = w.cub_bytes;
+        int bits = 1;
+        while ((1ll << bits) <= n_seg) ++bits;   // the sentinel segment n_seg needs one more value
+        cudaError_t e = cub::DeviceRadixSort::SortPairs(base + w.cub, cub_bytes, keys_in, keys_out, vals_in, vals_out,
+                                                        total, 0, 32 + bits, s);
+        if (e != cudaSuccess) { set_error("radix sort: %s", cudaGetErrorString(e)); return HIRA_ERR_CUDA; }
+        segment_starts_kernel<<<(int)((total + 1 + 255) / 256), 256, 0, s>>>(keys_out, total, n_seg, start);
+        HIRA_CHECK_LAUNCH("segment starts launch");
+    }
+    capacity_scan_kernel<<<n_heads, 1024, 0, s>>>(start, filled, k, bf, fbase, lbase, fill);
+    HIRA_CHECK_LAUNCH("capacity scan launch");
+    placement_kernel<<<blocks, 256, 0, s>>>(keys_out, vals_out, start, filled, fbase, lbase, n, k, bf, total, n_seg, slot);
     HIRA_CHECK_LAUNCH("placement launch");
     return HIRA_OK;
 }
@@ -623,7 +697,7 @@ static int build_level(int dtype, const T* points, long long p_head_stride, int 
 template <typename T>
 static int build_impl(const hira_index_t* ix, const void* keys_v, const void* values, int n_keys,
                       long long k_head_stride, long long v_head_stride, int token_base, const int32_t* cent_idx1,
-                      const int32_t* cent_idx2, int n_iters, int use_tc, char* base, const BuildWs& w,
+                      const int32_t* cent_idx2, int n_iters, int balance_rounds, int use_tc, char* base, const BuildWs& w,
                       int32_t* status, cudaStream_t s) {
     const T* keys = reinterpret_cast<const T*>(keys_v);
     const int H = ix->n_heads, bf = ix->bf, dim = ix->dim;
@@ -657,12 +731,12 @@ static int build_impl(const hira_index_t* ix, const void* keys_v, const void* va
     int32_t* slot2 = reinterpret_cast<int32_t*>(base + w.slot2);
     int32_t* fill1 = reinterpret_cast<int32_t*>(base + w.fill1);
     int32_t* fill2 = reinterpret_cast<int32_t*>(base + w.fill2);
-    int rc = build_level<T>(ix->dtype, keys, k_head_stride, H, n_keys, k1, bf, dim, cent_idx1, n_iters, use_tc,
+    int rc = build_level<T>(ix->dtype, keys, k_head_stride, H, n_keys, k1, bf, dim, cent_idx1, n_iters, balance_rounds, use_tc,
                             cents1, base, w, slot1, fill1, status, s);
     if (rc != HIRA_OK) return rc;
     const int32_t* slot2_used = nullptr;
     if (ix->depth == 3) {
-        rc = build_level<T>(ix->dtype, cents1, (long long)k1 * dim, H, k1, k2, bf, dim, cent_idx2, n_iters, use_tc,
+        rc = build_level<T>(ix->dtype, cents1, (long long)k1 * dim, H, k1, k2, bf, dim, cent_idx2, n_iters, balance_rounds, use_tc,
                             cents2, base, w, slot2, fill2, status, s);
         if (rc != HIRA_OK) return rc;
         slot2_used = slot2;
@@ -719,11 +793,12 @@ extern "C" size_t hira_build_workspace_bytes(const hira_index_t* ix, int32_t n_k
 extern "C" int hira_build(const hira_index_t* ix, const void* keys, const void* values, int32_t n_keys,
                           int64_t k_head_stride, int64_t v_head_stride, int32_t token_base,
                           const int32_t* cent_idx1, const int32_t* cent_idx2, int32_t n_iters,
-                          int32_t use_tensor_cores, int32_t* status, void* workspace, size_t workspace_bytes,
-                          void* stream) {
+                          int32_t balance_rounds, int32_t use_tensor_cores, int32_t* status, void* workspace,
+                          size_t workspace_bytes, void* stream) {
     int rc = validate_index(ix, false);
     if (rc != HIRA_OK) return rc;
     HIRA_CHECK_ARG(n_keys >= 0, HIRA_ERR_SHAPE, "hira_build: n_keys=%d", n_keys);
+    HIRA_CHECK_ARG(balance_rounds >= 0 && balance_rounds <= 64, HIRA_ERR_ARG, "hira_build: balance_rounds=%d", balance_rounds);
     HIRA_CHECK_ARG(n_keys == 0 || keys, HIRA_ERR_ARG, "hira_build: keys is NULL");
     HIRA_CHECK_ARG((ix->values == nullptr) == (values == nullptr) || n_keys == 0, HIRA_ERR_ARG,
                    "hira_build: values must be given iff the index stores values");
@@ -742,9 +817,9 @@ extern "C" int hira_build(const hira_index_t* ix, const void* keys, const void* 
     char* base = reinterpret_cast<char*>(workspace);
     if (ix->dtype == HIRA_BF16)
         return build_impl<__nv_bfloat16>(ix, keys, values, n_keys, k_head_stride, v_head_stride, token_base, cent_idx1,
-                                         cent_idx2, n_iters, use_tensor_cores, base, w, status, s);
+                                         cent_idx2, n_iters, balance_rounds, use_tensor_cores, base, w, status, s);
     return build_impl<float>(ix, keys, values, n_keys, k_head_stride, v_head_stride, token_base, cent_idx1, cent_idx2,
-                             n_iters, use_tensor_cores, base, w, status, s);
+                             n_iters, balance_rounds, use_tensor_cores, base, w, status, s);
 }
 
 extern "C" int hira_recompute_radii(const hira_index_t* ix, void* stream) {

@@ -411,7 +411,7 @@ def kth_score(st: IndexState, compact: CompactResult, k: torch.Tensor, out=None)
 
 
 def build(st: IndexState, keys: torch.Tensor, values: Optional[torch.Tensor], *, cent_idx1=None, cent_idx2=None,
-          n_iters: int = 1, use_tensor_cores: bool = True, token_base: int = 0):
+          n_iters: int = 1, balance_rounds: int = 0, use_tensor_cores: bool = True, token_base: int = 0):
     """keys (n_heads, n, D), values (n_heads, n, V) contiguous, index dtypes."""
     lib = L.load()
     assert keys.is_contiguous() and keys.dtype == st.dtype
@@ -423,7 +423,7 @@ def build(st: IndexState, keys: torch.Tensor, values: Optional[torch.Tensor], *,
     ws = torch.empty((max(nbytes, 1),), dtype=torch.uint8, device=st.device)
     rc = lib.hira_build(st.struct, L.ptr(keys), L.ptr(values), n, n * st.dim,
                         n * st.vdim if values is not None else 0, token_base, L.ptr(cent_idx1), L.ptr(cent_idx2),
-                        n_iters, 1 if use_tensor_cores else 0, L.ptr(st.status), L.ptr(ws), nbytes,
+                        n_iters, int(balance_rounds), 1 if use_tensor_cores else 0, L.ptr(st.status), L.ptr(ws), nbytes,
                         L.current_stream(st.device))
     L.check(rc, "hira_build")
 

@@ -39,7 +39,8 @@ class CUDAIndexer(BaseIndexer):
 
     def __init__(self, num_levels, max_iterations: int, branching_factor: int, verbose: bool = False,
                  pad_value: float = DEFAULT_PAD_VALUE, *, max_context: Optional[int] = None,
-                 reserve_worst_case: bool = False, use_tensor_cores: bool = True, seed: int = 1234):
+                 reserve_worst_case: bool = False, use_tensor_cores: bool = True, seed: int = 1234,
+                 balance_rounds: int = 0):
         self.depth = num_levels if isinstance(num_levels, CUDAIndexer.DEPTH) else CUDAIndexer.DEPTH(num_levels)
         self.max_iterations = max_iterations
         self.branching_factor = int(branching_factor)
@@ -47,6 +48,7 @@ class CUDAIndexer(BaseIndexer):
         self.pad_value = pad_value
         self.max_context = max_context
         self.reserve_worst_case = reserve_worst_case
+        self.balance_rounds = int(balance_rounds)   # capacity-aware assignment rounds of the build (0: reference rule)
         self.use_tensor_cores = use_tensor_cores
         self.seed = seed
         self.dim: int = 0
@@ -171,7 +173,7 @@ class CUDAIndexer(BaseIndexer):
             if st.depth == 3:
                 cent2 = torch.rand((h, k1), generator=g, device=keys.device).topk(k2, dim=1).indices.to(torch.int32).contiguous()
         S.build(st, keys, values, cent_idx1=cent1, cent_idx2=cent2, n_iters=max(1, int(self.max_iterations)),
-                use_tensor_cores=self.use_tensor_cores)
+                balance_rounds=self.balance_rounds, use_tensor_cores=self.use_tensor_cores)
         self.state = st
         self._n_keys = n
         self._parents_bound = k2 * bf if st.depth == 3 else k1
@@ -363,7 +365,7 @@ class CUDAIndexer(BaseIndexer):
         keys, values = S.export(st, n)
         b = self.__class__(self.depth, self.max_iterations, self.branching_factor, self.verbose, self.pad_value,
                            max_context=self.max_context, reserve_worst_case=self.reserve_worst_case,
-                           use_tensor_cores=self.use_tensor_cores, seed=self.seed)
+                           use_tensor_cores=self.use_tensor_cores, seed=self.seed, balance_rounds=self.balance_rounds)
         b.build(keys.unsqueeze(0), None if values is None else values.unsqueeze(0))
         self.state, self._parents_bound, self._gp_bound = b.state, b._parents_bound, b._gp_bound
         self._snapshot = None

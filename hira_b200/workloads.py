@@ -42,7 +42,7 @@ class Workload:
     levels: int
     branching: int
     dtype: torch.dtype
-    dist: str                 # "rope_outlier" | "aniso"
+    dist: str                 # "rope_outlier" | "aniso" | "clustered"
     keep: float               # fraction of keys tau keeps (exact k-th largest score per query head)
     seed: int = 0
 
@@ -60,6 +60,8 @@ CFG1 = Workload("cfg1_b1_ctx32768", 1, 8, 32, 32768, 3, 32, torch.bfloat16, "rop
 CFG2 = Workload("cfg2_b16_ctx131072", 16, 8, 32, 131072, 3, 32, torch.bfloat16, "rope_outlier", 0.02)
 CFG3 = Workload("cfg3_streaming_prefix65536", 1, 8, 32, 65536, 3, 32, torch.bfloat16, "rope_outlier", 0.02)
 CFG4 = Workload("cfg4_seqshard_131072_per_gpu", 1, 8, 64, 131072, 3, 64, torch.bfloat16, "rope_outlier", 0.02)
+# control: cfg1's shape on clustered keys (not a BASELINE configuration)
+CLUSTERED = Workload("clustered_b1_ctx32768", 1, 8, 32, 32768, 3, 32, torch.bfloat16, "clustered", 0.02)
 CONFIGS = {w.name.split("_")[0]: w for w in (CFG0, CFG1, CFG2, CFG3, CFG4)}
 
 
@@ -102,6 +104,12 @@ def make_kv(n_heads: int, n: int, seed: int, device, *, dist: str = "rope_outlie
             k[:, list(OUTLIER_CHANNELS)] *= OUTLIER_SCALE
         elif dist == "aniso":
             k *= scale
+        elif dist == "clustered":
+            # a mixture of 1,024 tight clusters (centres N(0, 9 I), spread 0.35): data on which ball
+            # pruning has something to prune -- not one of the reference's distributions, a control
+            cent = torch.randn((1024, dim), generator=g, device=device, dtype=torch.float32) * 3.0
+            which = torch.randint(0, 1024, (n,), generator=g, device=device)
+            k = cent[which] + 0.35 * k
         else:
             raise ValueError(f"unknown distribution {dist!r}")
         keys[i] = k.to(dtype)

@@ -388,6 +388,11 @@ int hira_kth_score(const hira_index_t* index, int32_t n_qheads,
  *          ids used as initial grandparent centres.  NULL = evenly strided.
  *   The index arrays are fully (re)initialised: unused slots are zero rows,
  *   radius 0, count 0, slot2token -1.
+ *   balance_rounds: 0 = the reference's rule (every centre keeps its bf closest points, the
+ *          overflow is dealt to whatever slots are free).  R > 0 = capacity-aware assignment: the
+ *          overflow chooses again, R times, among the centres that still have room (nearest
+ *          first, closest points accepted first); only what is left after that is dealt out.
+ *          Tighter balls at the price of R more assignment passes; radii as always from the layout.
  *   use_tensor_cores: 1 = tcgen05 assignment GEMM when dtype is bf16 and the
  *          shapes allow it, 0 = CUDA-core fp32 assignment.
  *   status: device int32 or NULL, OR-ed with HIRA_STATUS_ASSIGN_FAILED (see there).
@@ -396,7 +401,7 @@ size_t hira_build_workspace_bytes(const hira_index_t* index, int32_t n_keys);
 int hira_build(const hira_index_t* index, const void* keys, const void* values,
                int32_t n_keys, int64_t k_head_stride, int64_t v_head_stride,
                int32_t token_base, const int32_t* cent_idx1,
-               const int32_t* cent_idx2, int32_t n_iters,
+               const int32_t* cent_idx2, int32_t n_iters, int32_t balance_rounds,
                int32_t use_tensor_cores, int32_t* status, void* workspace,
                size_t workspace_bytes, void* stream);
 

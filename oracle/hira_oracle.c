@@ -523,9 +523,40 @@ static int cmp_item(const void* a, const void* b) {
     if (x->key != y->key) return x->key < y->key ? -1 : 1;
     return (x->id > y->id) - (x->id < y->id);
 }
+/* arg-min over the centres that still have room (balanced rounds), same arithmetic as oracle_assign */
+static void assign_masked_head(const void* points, int64_t p_head_stride, const void* cents, int dtype, int h, int n,
+                               int k, int dim, int bf, const int32_t* filled, const int32_t* slot, int32_t* out_idx,
+                               float* out_d2) {
+    const size_t es = dtype == HIRA_BF16 ? 2 : 4;
+    float* C = (float*)malloc(sizeof(float) * (size_t)k * dim);
+    float* csq = (float*)malloc(sizeof(float) * k);
+    for (int c = 0; c < k; ++c) {
+        load_row(cents, dtype, (size_t)h * k + c, dim, C + (size_t)c * dim);
+        csq[c] = dot_seq(C + (size_t)c * dim, C + (size_t)c * dim, dim);
+    }
+#pragma omp parallel for schedule(static)
+    for (int i = 0; i < n; ++i) {
+        if (slot[i] >= 0) continue;
+        float x[256];
+        load_row((const char*)points + (size_t)h * p_head_stride * es, dtype, i, dim, x);
+        float best = INFINITY;
+        int bi = 0x7fffffff;
+        for (int c = 0; c < k; ++c) {
+            if (filled[c] >= bf) continue;
+            const float s = csq[c] - 2.0f * dot_seq(x, C + (size_t)c * dim, dim);
+            if (s < best) { best = s; bi = c; }
+        }
+        const float d2 = dot_seq(x, x, dim) + best;
+        out_idx[i] = bi;
+        out_d2[i] = d2 > 0.0f ? d2 : 0.0f;
+    }
+    free(C);
+    free(csq);
+}
+
 static void build_level(const void* points, int64_t p_head_stride, int dtype, int n_heads, int n, int k, int bf,
-                        int dim, const int32_t* cent_idx, int n_iters, void* cents /* [H][k][dim] dtype */,
-                        int32_t* slot /* [H][n] */, int32_t* fill /* [H][k] */) {
+                        int dim, const int32_t* cent_idx, int n_iters, int balance_rounds,
+                        void* cents /* [H][k][dim] dtype */, int32_t* slot /* [H][n] */, int32_t* fill /* [H][k] */) {
     const size_t es = dtype == HIRA_BF16 ? 2 : 4;
     int32_t* a_idx = (int32_t*)malloc(sizeof(int32_t) * (size_t)n_heads * n);
     float* a_d2 = (float*)malloc(sizeof(float) * (size_t)n_heads * n);
@@ -540,19 +571,25 @@ static void build_level(const void* points, int64_t p_head_stride, int dtype, in
     const int iters = n_iters < 1 ? 1 : n_iters;
     sort_item* items = (sort_item*)malloc(sizeof(sort_item) * n);
     int32_t* start = (int32_t*)malloc(sizeof(int32_t) * (k + 1));
+    int32_t* filled = (int32_t*)malloc(sizeof(int32_t) * k);
     for (int it = 0; it < iters; ++it) {
         oracle_assign(points, p_head_stride, cents, dtype, n_heads, n, k, dim, a_idx, a_d2);
         for (int h = 0; h < n_heads; ++h) {
+            int32_t* hslot = slot + (size_t)h * n;
+            int32_t* hidx = a_idx + (size_t)h * n;
+            float* hd2 = a_d2 + (size_t)h * n;
+            int n_items = 0;
             for (int i = 0; i < n; ++i) {
                 uint32_t bits;
-                memcpy(&bits, &a_d2[(size_t)h * n + i], 4);
-                items[i].key = ((uint64_t)(uint32_t)a_idx[(size_t)h * n + i] << 32) | bits;
+                memcpy(&bits, &hd2[i], 4);
+                items[i].key = ((uint64_t)(uint32_t)hidx[i] << 32) | bits;
                 items[i].id = (uint32_t)i;
             }
-            qsort(items, n, sizeof(sort_item), cmp_item);
+            n_items = n;
+            qsort(items, n_items, sizeof(sort_item), cmp_item);
             int pos = 0;
             for (int c = 0; c <= k; ++c) {
-                while (pos < n && (int)(items[pos].key >> 32) < c) ++pos;
+                while (pos < n_items && (int)(items[pos].key >> 32) < c) ++pos;
                 start[c] = pos;
             }
             if (it + 1 < iters) {
@@ -569,24 +606,55 @@ static void build_level(const void* points, int64_t p_head_stride, int dtype, in
                 }
                 continue;
             }
-            /* final pass: placement */
+            /* capacity-aware rounds: every centre accepts, closest first, what it has room for; points
+             * left over choose again among the centres with room (balance_rounds times) */
+            for (int c = 0; c < k; ++c) filled[c] = 0;
+            if (balance_rounds > 0)
+                for (int i = 0; i < n; ++i) hslot[i] = -1;
+            for (int r = 0; r < balance_rounds; ++r) {
+                for (int c = 0; c < k; ++c) {
+                    const int room = bf - filled[c];
+                    int acc = 0;
+                    for (int m = start[c]; m < start[c + 1] && acc < room; ++m, ++acc)
+                        hslot[items[m].id] = c * bf + filled[c] + acc;
+                    filled[c] += acc;
+                }
+                assign_masked_head(points, p_head_stride, cents, dtype, h, n, k, dim, bf, filled, hslot, hidx, hd2);
+                n_items = 0;
+                for (int i = 0; i < n; ++i) {
+                    if (hslot[i] >= 0) continue;
+                    uint32_t bits;
+                    memcpy(&bits, &hd2[i], 4);
+                    items[n_items].key = ((uint64_t)(uint32_t)hidx[i] << 32) | bits;
+                    items[n_items].id = (uint32_t)i;
+                    ++n_items;
+                }
+                qsort(items, n_items, sizeof(sort_item), cmp_item);
+                pos = 0;
+                for (int c = 0; c <= k; ++c) {
+                    while (pos < n_items && (int)(items[pos].key >> 32) < c) ++pos;
+                    start[c] = pos;
+                }
+            }
+            /* final pass: placement of what the last sort holds */
             int* fbase = (int*)malloc(sizeof(int) * (k + 1));
             int f = 0;
             for (int c = 0; c < k; ++c) {
-                const int cnt = start[c + 1] - start[c];
+                const int cnt = start[c + 1] - start[c], room = bf - filled[c];
                 fbase[c] = f;
-                f += bf - cnt > 0 ? bf - cnt : 0;
-                fill[(size_t)h * k + c] = cnt < bf ? cnt : bf;
+                f += room - cnt > 0 ? room - cnt : 0;
+                fill[(size_t)h * k + c] = filled[c] + (cnt < room ? cnt : room);
             }
             fbase[k] = f;
             int L = 0, c2 = 0;
             for (int c = 0; c < k; ++c) {
+                const int room = bf - filled[c];
                 for (int m = start[c]; m < start[c + 1]; ++m) {
                     const int rank = m - start[c];
-                    if (rank < bf) { slot[(size_t)h * n + items[m].id] = c * bf + rank; continue; }
+                    if (rank < room) { hslot[items[m].id] = c * bf + filled[c] + rank; continue; }
                     while (fbase[c2 + 1] <= L) ++c2;
-                    const int cnt2 = start[c2 + 1] - start[c2];
-                    slot[(size_t)h * n + items[m].id] = c2 * bf + (cnt2 < bf ? cnt2 : bf) + (L - fbase[c2]);
+                    const int cnt2 = start[c2 + 1] - start[c2], room2 = bf - filled[c2];
+                    hslot[items[m].id] = c2 * bf + filled[c2] + (cnt2 < room2 ? cnt2 : room2) + (L - fbase[c2]);
                     fill[(size_t)h * k + c2] += 1;
                     ++L;
                 }
@@ -594,12 +662,12 @@ static void build_level(const void* points, int64_t p_head_stride, int dtype, in
             free(fbase);
         }
     }
-    free(items); free(start); free(a_idx); free(a_d2);
+    free(items); free(start); free(filled); free(a_idx); free(a_d2);
 }
 
 int oracle_build(const hira_index_t* ix, const void* keys, const void* values, int n_keys, int64_t k_head_stride,
                  int64_t v_head_stride, int token_base, const int32_t* cent_idx1, const int32_t* cent_idx2,
-                 int n_iters) {
+                 int n_iters, int balance_rounds) {
     const int H = ix->n_heads, bf = ix->bf, dim = ix->dim, vdim = ix->vdim;
     const size_t es = ix->dtype == HIRA_BF16 ? 2 : 4, vs = ix->vdtype == HIRA_BF16 ? 2 : 4;
     const size_t capP = ix->cap_parents, capC = capP * bf, capG = ix->cap_gp;
@@ -625,9 +693,9 @@ int oracle_build(const hira_index_t* ix, const void* keys, const void* values, i
     int32_t* slot2 = (int32_t*)malloc(sizeof(int32_t) * (size_t)H * k1);
     int32_t* fill1 = (int32_t*)malloc(sizeof(int32_t) * (size_t)H * k1);
     int32_t* fill2 = (int32_t*)malloc(sizeof(int32_t) * (size_t)H * k2);
-    build_level(keys, k_head_stride, ix->dtype, H, n_keys, k1, bf, dim, cent_idx1, n_iters, cents1, slot1, fill1);
+    build_level(keys, k_head_stride, ix->dtype, H, n_keys, k1, bf, dim, cent_idx1, n_iters, balance_rounds, cents1, slot1, fill1);
     if (ix->depth == 3)
-        build_level(cents1, (int64_t)k1 * dim, ix->dtype, H, k1, k2, bf, dim, cent_idx2, n_iters, cents2, slot2, fill2);
+        build_level(cents1, (int64_t)k1 * dim, ix->dtype, H, k1, k2, bf, dim, cent_idx2, n_iters, balance_rounds, cents2, slot2, fill2);
     for (int h = 0; h < H; ++h) {
         for (int c = 0; c < k1; ++c) {
             const int s = ix->depth == 3 ? slot2[(size_t)h * k1 + c] : c;

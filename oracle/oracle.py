@@ -34,6 +34,9 @@ class _IndexStruct(C.Structure):
         ("parents", C.c_void_p), ("parent_radii", C.c_void_p), ("parent_sqnorm", C.c_void_p),
         ("child_counts", C.c_void_p), ("grand_parents", C.c_void_p), ("gp_radii", C.c_void_p),
         ("gp_sqnorm", C.c_void_p), ("gp_counts", C.c_void_p), ("used", C.c_void_p),
+        # the device-side int8 side copy of the children: always NULL here (the oracle has no use for it)
+        ("children_q8", C.c_void_p), ("children_q8_meta", C.c_void_p), ("q8_chan_scale", C.c_void_p),
+        ("q8_query_scratch", C.c_void_p),
     ]
 
 
@@ -264,13 +267,14 @@ def assign(points, cents):
     return idx, d2
 
 
-def build(ix: OracleIndex, keys, values, *, cent_idx1=None, cent_idx2=None, n_iters: int = 1, token_base: int = 0):
+def build(ix: OracleIndex, keys, values, *, cent_idx1=None, cent_idx2=None, n_iters: int = 1, token_base: int = 0,
+          balance_rounds: int = 0):
     keys, values = to_host(keys), to_host(values)
     c1, c2 = _i32(cent_idx1), _i32(cent_idx2)
     n = keys.shape[1]
     s = ix.struct()
     rc = lib().oracle_build(C.byref(s), _p(keys), _p(values), n, C.c_int64(n * ix.dim), C.c_int64(n * ix.vdim),
-                            token_base, _p(c1), _p(c2), n_iters)
+                            token_base, _p(c1), _p(c2), n_iters, balance_rounds)
     assert rc == 0
 
 

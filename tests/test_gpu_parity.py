@@ -9,7 +9,8 @@ from hira_b200 import _lib as L
 from hira_b200 import index_state as S
 from oracle import oracle as O
 
-from util import (assert_index_equal, build_both, compact_sets, exact_tau, make_keys, make_queries, new_state)
+from util import (assert_index_equal, build_both, compact_sets, exact_tau, make_keys, make_queries, new_state,
+                  random_centres)
 
 pytestmark = pytest.mark.gpu
 
@@ -436,6 +437,37 @@ def test_build_with_tensor_cores_gives_a_valid_index():
         must = set(torch.nonzero(sc[qh] > tau[qh] + 1e-4).flatten().tolist())
         never = set(torch.nonzero(sc[qh] < tau[qh] - 1e-4).flatten().tolist())
         assert must <= got and not (got & never)
+
+
+@pytest.mark.parametrize("h,n,d,bf,depth,dtype,n_iters,rounds", [
+    (2, 1000, 32, 8, 3, torch.float32, 1, 1),
+    (1, 4096, 128, 32, 3, torch.bfloat16, 1, 3),
+    (2, 777, 64, 16, 2, torch.float32, 3, 2),
+    (3, 300, 16, 5, 3, torch.float32, 1, 8),
+])
+def test_balanced_build_matches_oracle(h, n, d, bf, depth, dtype, n_iters, rounds):
+    """Capacity-aware assignment rounds: the layout, the counts and the radii equal the oracle's, every
+    key is stored once, and the balls are no larger on average than with the reference's rule."""
+    keys = make_keys(h, n, d, 91, dtype, normalize=False)
+    vals = make_keys(h, n, d, 92, dtype, normalize=False)
+    k1 = -(-n // bf)
+    k2 = -(-k1 // bf)
+    cap = k2 * bf if depth == 3 else k1
+    c1 = random_centres(h, n, k1, 93)
+    c2 = random_centres(h, k1, k2, 94) if depth == 3 else None
+    code = O.HIRA_BF16 if dtype == torch.bfloat16 else O.HIRA_F32
+    radii = []
+    for r in (0, rounds):
+        st = new_state(h, d, bf, depth, cap, dtype)
+        S.build(st, keys, vals, cent_idx1=c1, cent_idx2=c2, n_iters=n_iters, balance_rounds=r, use_tensor_cores=False)
+        torch.cuda.synchronize()
+        ox = O.OracleIndex(n_heads=h, dim=d, vdim=d, bf=bf, depth=depth, cap_parents=cap, dtype=code, vdtype=code)
+        O.build(ox, keys, vals, cent_idx1=c1, cent_idx2=c2, n_iters=n_iters, balance_rounds=r)
+        assert_index_equal(st, ox, f"balance_rounds={r}")
+        tok = st.slot2token[st.slot2token >= 0].reshape(h, n).sort(dim=1).values.cpu()
+        assert torch.equal(tok, torch.arange(n).expand(h, n).to(tok.dtype))
+        radii.append(float(st.parent_radii[:, :k1 if depth == 2 else k2 * bf].mean()))
+    assert radii[1] <= radii[0] * 1.0001, radii
 
 
 def test_export_roundtrip():

@@ -513,7 +513,9 @@ def secondary_cfg3(args, dev):
         torch.cuda.synchronize()
         append_us.append(e0.elapsed_time(e1) * 1e3 / n)
         pos += n
-        ix._n_keys = pos
+        ix._n_keys = pos                      # the library was called directly: keep the indexer's host-side
+        ix._parents_bound += n                # key count and worst-case bounds on the slots in use by hand
+        ix._gp_bound += n
         ix.check_status()
         if pos < prefix + steps:
             ix.max_context = pos + every + 8
@@ -589,6 +591,48 @@ def secondary_cfg4(args, dev, rank, world, dist, barrier, peak):
             "exchange_bytes_per_gpu": ex.message_bytes, "algorithmic_bytes_per_gpu": c["search_bytes"] + c["attn_bytes"],
             "search_gbs_per_gpu": ach, "frac": ach / peak, "scanned_fraction": c["scanned_fraction"],
             "merged_vs_one_rank_max_rel_err": check}
+
+
+def phase_profile(args):
+    """`--phase-profile`: per-CTA phase times of the int8 pre-filter search kernel at the headline
+    shape, from the profiling build of the library (`python -m hira_b200.build --profile`), whose
+    kernel stamps %globaltimer at its phase boundaries.  One JSON line."""
+    import ctypes as C
+    import numpy as np
+    from hira_b200 import _lib as L
+    from hira_b200.build import PROFILE_LIB_PATH
+    if not PROFILE_LIB_PATH.exists():
+        raise SystemExit("build the profiling library first: python -m hira_b200.build --profile")
+    L.LIB_PATH = PROFILE_LIB_PATH
+    from hira_b200 import index_state as S
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    b = DecodeBench(W.CFG2, args.batch * W.CFG2.kv_heads, args.ctx, 32, dev)
+    b.make_queries(1, 50)
+    q_hat, tau, lscale, _ = b.qsets[0]
+    for _ in range(3):
+        S.search(b.st, q_hat, tau, scaling=lscale, flags=b.flags, compact=b.compact, tp=b.tp)
+    torch.cuda.synchronize()
+    a, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    S.search(b.st, q_hat, tau, scaling=lscale, flags=b.flags, compact=b.compact, tp=b.tp)
+    e.record()
+    torch.cuda.synchronize()
+    lib = L.load()
+    buf = np.zeros((16384, 16), np.uint64)
+    lib.hira_q8_profile_read.argtypes = [C.c_void_p]
+    if lib.hira_q8_profile_read(buf.ctypes.data) != 0:
+        raise SystemExit("reading the stamps failed")
+    t = buf.astype(np.int64)
+    t = t[(t[:, 0] > 0) & (t[:, 7] > 0)]
+    mid = t[(t[:, 0] > np.percentile(t[:, 0], 20)) & (t[:, 0] < np.percentile(t[:, 0], 80))]   # CTAs of the steady state
+    us = lambda x, y: float(((mid[:, x] - mid[:, y]) / 1e3).mean())
+    out = {"workload": f"b{args.batch}_ctx{args.ctx}", "search_us": a.elapsed_time(e) * 1e3, "ctas_stamped": int(len(t)),
+           "per_cta_us": {"init": us(1, 0), "gates": us(2, 1), "wait_query_terms": us(3, 2), "scores_until_last_stage": us(4, 3),
+                          "candidate_list": us(5, 4), "exact_pass": us(6, 5), "compaction": us(7, 6), "total": us(7, 0)},
+           "producer_us": {"start_to_first_request": us(8, 0), "first_request_to_first_stage": us(9, 8),
+                           "first_to_fourth_stage": us(11, 9), "first_stage_to_last_mma": us(10, 9)}}
+    print(json.dumps(out), flush=True)
 
 
 def pruning_table(args):
@@ -936,13 +980,17 @@ def main():
     ap.add_argument("--unfused", dest="fused", action="store_false",
                     help="separate parent scan in the append (default with the int8 pre-filter)")
     ap.add_argument("--no-int8", action="store_true", help="search without the int8 side copy (plain streaming kernel)")
+    ap.add_argument("--phase-profile", action="store_true",
+                    help="per-CTA phase times of the pre-filter search kernel (needs the profiling build), then exit")
     ap.add_argument("--pruning-table", action="store_true",
                     help="print scanned fraction against branching factor, Lloyd iterations and balanced rounds, then exit")
     ap.add_argument("--traffic-key", default=None, help=argparse.SUPPRESS)
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
-    if args.pruning_table:
+    if args.phase_profile:
+        phase_profile(args)
+    elif args.pruning_table:
         pruning_table(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -15,6 +15,7 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libhira_b200.so"
+PROFILE_LIB_PATH = PKG_DIR / "libhira_b200_profile.so"   # the same library with phase time stamps in search_q8.cu
 OBJ_DIR = CSRC / "build"
 
 SOURCES = ["api.cu", "search.cu", "search_q8.cu", "attention.cu", "append.cu", "threshold.cu", "build.cu", "assign_tc.cu"]
@@ -76,6 +77,30 @@ def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool =
     return LIB_PATH
 
 
+def build_profile_library() -> Path:
+    """A second library whose int8 pre-filter search kernel writes globaltimer stamps at its phase
+    boundaries (-DHIRA_Q8_PROFILE); read back by `python bench.py --phase-profile`.  Never loaded by
+    the package itself."""
+    nvcc = _nvcc()
+    build_library()
+    obj = OBJ_DIR / "search_q8.profile.o"
+    r = subprocess.run([nvcc, *NVCC_FLAGS, "-DHIRA_Q8_PROFILE", "-c", str(CSRC / "search_q8.cu"), "-o", str(obj)],
+                       capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError("nvcc failed on search_q8.cu (profile build)")
+    objs = [str(OBJ_DIR / (s + ".o")) for s in SOURCES if s != "search_q8.cu"] + [str(obj)]
+    r = subprocess.run([nvcc, "-shared", "-o", str(PROFILE_LIB_PATH), *objs, "-gencode", "arch=compute_100a,code=sm_100a"],
+                       capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError("linking the profile library failed")
+    return PROFILE_LIB_PATH
+
+
 if __name__ == "__main__":
-    p = build_library(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv)
-    print(p)
+    if "--profile" in sys.argv:
+        print(build_profile_library())
+    else:
+        p = build_library(force="--force" in sys.argv, verbose=True, ptxas_info="--ptxas" in sys.argv)
+        print(p)

@@ -706,18 +706,32 @@ static int build_impl(const hira_index_t* ix, const void* keys_v, const void* va
     const size_t es = elem_size(ix->dtype);
     const size_t capP = ix->cap_parents, capC = capP * bf;
     // ---- clear the index -----------------------------------------------------
-    cudaMemsetAsync(ix->children, 0, (size_t)H * capC * dim * es, s);
-    if (ix->values) cudaMemsetAsync(ix->values, 0, (size_t)H * capC * ix->vdim * elem_size(ix->vdtype), s);
-    if (ix->slot2token) cudaMemsetAsync(ix->slot2token, 0xff, (size_t)H * capC * 4, s);
-    cudaMemsetAsync(ix->parents, 0, (size_t)H * capP * dim * es, s);
-    cudaMemsetAsync(ix->parent_radii, 0, (size_t)H * capP * 4, s);
-    if (ix->parent_sqnorm) cudaMemsetAsync(ix->parent_sqnorm, 0, (size_t)H * capP * 4, s);
-    cudaMemsetAsync(ix->child_counts, 0, (size_t)H * capP * 4, s);
-    if (ix->depth == 3) {
-        cudaMemsetAsync(ix->grand_parents, 0, (size_t)H * ix->cap_gp * dim * es, s);
-        cudaMemsetAsync(ix->gp_radii, 0, (size_t)H * ix->cap_gp * 4, s);
-        if (ix->gp_sqnorm) cudaMemsetAsync(ix->gp_sqnorm, 0, (size_t)H * ix->cap_gp * 4, s);
-        cudaMemsetAsync(ix->gp_counts, 0, (size_t)H * ix->cap_gp * 4, s);
+    // Everything, or -- when the host vouches through active_parents that no slot beyond that bound
+    // was ever used -- the slots up to the larger of that bound and what this build fills.
+    {
+        size_t clearP = capP;
+        if (ix->active_parents > 0) {
+            const size_t fills = ix->depth == 3 ? (size_t)k2 * bf : (size_t)k1;
+            clearP = (size_t)ix->active_parents > fills ? (size_t)ix->active_parents : fills;
+            if (clearP > capP) clearP = capP;
+        }
+        const size_t clearC = clearP * bf, clearG = ix->depth == 3 ? (clearP + bf - 1) / bf : 0;
+        auto clear = [&](void* ptr, int value, size_t row_bytes, size_t rows_cap, size_t rows_clear) {
+            if (ptr) cudaMemset2DAsync(ptr, rows_cap * row_bytes, value, rows_clear * row_bytes, (size_t)H, s);
+        };
+        clear(ix->children, 0, dim * es, capC, clearC);
+        clear(ix->values, 0, ix->values ? ix->vdim * elem_size(ix->vdtype) : 0, capC, clearC);
+        clear(ix->slot2token, 0xff, 4, capC, clearC);
+        clear(ix->parents, 0, dim * es, capP, clearP);
+        clear(ix->parent_radii, 0, 4, capP, clearP);
+        clear(ix->parent_sqnorm, 0, 4, capP, clearP);
+        clear(ix->child_counts, 0, 4, capP, clearP);
+        if (ix->depth == 3) {
+            clear(ix->grand_parents, 0, dim * es, ix->cap_gp, clearG);
+            clear(ix->gp_radii, 0, 4, ix->cap_gp, clearG);
+            clear(ix->gp_sqnorm, 0, 4, ix->cap_gp, clearG);
+            clear(ix->gp_counts, 0, 4, ix->cap_gp, clearG);
+        }
     }
     HIRA_CHECK_LAUNCH("index clear");
     if (n_keys == 0) {

@@ -867,10 +867,13 @@ int launch_search_q8(const SearchParams& P, const hira_index_t* ix, int max_grou
 // ---------------------------------------------------------------------------
 // Building and maintaining the side copy.
 // ---------------------------------------------------------------------------
-// per head: rms of every channel over a strided sample of the filled child slots -> s_i, min_i s_i
+// per head: rms of every channel over a strided sample of the filled child slots -> s_i, min_i s_i.
+// Two kernels: slices of the sample summed by many CTAs (atomicAdd into the head's 128 accumulators,
+// which are the scale array itself, and a row count at [135]), then one CTA per head finishes.
+constexpr int Q8_CHAN_PARTS = 64;
 template <typename T>
-__global__ void q8_chan_scale_kernel(const hira_index_t ix) {
-    const int h = blockIdx.x;
+__global__ void q8_chan_sums_kernel(const hira_index_t ix) {
+    const int h = blockIdx.y, part = blockIdx.x;
     const int c = threadIdx.x;   // channel
     const size_t capC = (size_t)ix.cap_parents * ix.bf;
     const T* rows = reinterpret_cast<const T*>(ix.children) + (size_t)h * capC * Q8_DIM;
@@ -878,9 +881,13 @@ __global__ void q8_chan_scale_kernel(const hira_index_t ix) {
     const int32_t* cc = ix.child_counts + (size_t)h * ix.cap_parents;
     const size_t n_slots = (size_t)(ix.depth == 3 ? ix.used[h * 4 + 1] * ix.bf : ix.used[h * 4 + 0]) * ix.bf;
     const size_t stride = n_slots > 16384 ? n_slots / 8192 : 1;
+    const size_t n_samples = (n_slots + stride - 1) / stride;
+    const size_t per = (n_samples + Q8_CHAN_PARTS - 1) / Q8_CHAN_PARTS;
+    const size_t i0 = part * per, i1 = i0 + per < n_samples ? i0 + per : n_samples;
     float sum = 0.f;
     int cnt = 0;
-    for (size_t r = 0; r < n_slots; r += stride) {
+    for (size_t i = i0; i < i1; ++i) {
+        const size_t r = i * stride;
         const bool filled = s2t ? s2t[r] >= 0 : (int)(r % ix.bf) < cc[r / ix.bf];
         if (!filled) continue;
         const float v = sizeof(T) == 2 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(rows)[r * Q8_DIM + c])
@@ -888,7 +895,17 @@ __global__ void q8_chan_scale_kernel(const hira_index_t ix) {
         sum = __fmaf_rn(v, v, sum);
         ++cnt;
     }
-    float s = cnt > 0 ? sqrtf(sum / (float)cnt) : 1.f;
+    float* out = ix.q8_chan_scale + (size_t)h * HIRA_Q8_CHAN;
+    if (cnt) atomicAdd(out + c, sum);
+    if (c == 0 && cnt) atomicAdd(out + 135, (float)cnt);
+}
+
+__global__ void q8_chan_finish_kernel(const hira_index_t ix) {
+    const int h = blockIdx.x;
+    const int c = threadIdx.x;
+    float* out = ix.q8_chan_scale + (size_t)h * HIRA_Q8_CHAN;
+    const float cnt = out[135];
+    float s = cnt > 0.f ? sqrtf(out[c] / cnt) : 1.f;
     if (!(s > 1e-20f) || !(s < 1e20f)) s = 1.f;
     __shared__ float s_min[4];
     float m = s;
@@ -896,7 +913,6 @@ __global__ void q8_chan_scale_kernel(const hira_index_t ix) {
     for (int sft = 16; sft >= 1; sft >>= 1) m = fminf(m, __shfl_xor_sync(0xffffffffu, m, sft));
     if ((c & 31) == 0) s_min[c >> 5] = m;
     __syncthreads();
-    float* out = ix.q8_chan_scale + (size_t)h * HIRA_Q8_CHAN;
     out[c] = s;
     if (c == 0) {
         out[Q8_DIM] = fminf(fminf(s_min[0], s_min[1]), fminf(s_min[2], s_min[3]));
@@ -916,6 +932,9 @@ __global__ void q8_quantize_kernel(const hira_index_t ix) {
     if (w >= (size_t)ix.n_heads * capC) return;
     const int h = (int)(w / capC);
     const size_t slot = w % capC;
+    // slots beyond the blocks in use hold no keys (and never did since the last clear): nothing to write
+    const size_t in_use = (size_t)(ix.depth == 3 ? ix.used[h * 4 + 1] * ix.bf : ix.used[h * 4 + 0]) * ix.bf;
+    if (slot >= in_use) return;
     const T* row = reinterpret_cast<const T*>(ix.children) + w * Q8_DIM;
     float x[2][8];
     load_vec<T, 2>(row, x, lane, Q8_DIM);
@@ -929,11 +948,15 @@ int q8_refresh(const hira_index_t* ix, cudaStream_t s) {
                    "the int8 side copy needs dim == 128 and its meta / channel-scale arrays");
     const size_t rows = (size_t)ix->n_heads * ix->cap_parents * ix->bf;
     const unsigned blocks = (unsigned)((rows * GROUP + 255) / 256);
+    cudaMemsetAsync(ix->q8_chan_scale, 0, (size_t)ix->n_heads * HIRA_Q8_CHAN * sizeof(float), s);
+    const dim3 parts(Q8_CHAN_PARTS, (unsigned)ix->n_heads);
     if (ix->dtype == HIRA_BF16) {
-        q8_chan_scale_kernel<__nv_bfloat16><<<ix->n_heads, Q8_DIM, 0, s>>>(*ix);
+        q8_chan_sums_kernel<__nv_bfloat16><<<parts, Q8_DIM, 0, s>>>(*ix);
+        q8_chan_finish_kernel<<<ix->n_heads, Q8_DIM, 0, s>>>(*ix);
         q8_quantize_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(*ix);
     } else {
-        q8_chan_scale_kernel<float><<<ix->n_heads, Q8_DIM, 0, s>>>(*ix);
+        q8_chan_sums_kernel<float><<<parts, Q8_DIM, 0, s>>>(*ix);
+        q8_chan_finish_kernel<<<ix->n_heads, Q8_DIM, 0, s>>>(*ix);
         q8_quantize_kernel<float><<<blocks, 256, 0, s>>>(*ix);
     }
     HIRA_CHECK_LAUNCH("int8 side copy launch");

@@ -124,6 +124,13 @@ class CUDAIndexer(BaseIndexer):
         b, h, l, d = t.shape
         return t.reshape(b * h, l, d).contiguous()
 
+    @staticmethod
+    def _stratified(h: int, n: int, k: int, g: torch.Generator, device) -> torch.Tensor:
+        lo = (torch.arange(k + 1, device=device, dtype=torch.int64) * n) // k        # stride boundaries
+        width = (lo[1:] - lo[:-1]).to(torch.float32)
+        jitter = (torch.rand((h, k), generator=g, device=device) * width).to(torch.int64)
+        return (lo[:-1] + torch.minimum(jitter, (lo[1:] - lo[:-1] - 1).clamp_min(0))).to(torch.int32).contiguous()
+
     def _capacity_parents(self, n_keys: int) -> int:
         bf = self.branching_factor
         k1 = max(1, -(-n_keys // bf))
@@ -147,6 +154,11 @@ class CUDAIndexer(BaseIndexer):
     @torch.no_grad()
     def build(self, keys: torch.Tensor, values: Optional[torch.Tensor] = None):
         """keys (B, H, L, D); values optional (B, H, L, V)."""
+        return self._build(keys, values, reuse=None)
+
+    def _build(self, keys, values, reuse: Optional[S.IndexState]):
+        """`reuse`: a state of this indexer whose arrays are taken over when they are large enough
+        (a rebuild): nothing is allocated and only the slots that were in use are cleared."""
         if not torch.cuda.is_available():
             raise RuntimeError("CUDAIndexer needs a CUDA device (there is no CPU fallback)")
         keys = self._fold(keys.to("cuda"))
@@ -158,20 +170,30 @@ class CUDAIndexer(BaseIndexer):
         self.num_heads, self.dim = h, d
         bf = self.branching_factor
         cap_p = self._capacity_parents(n)
-        st = S.IndexState(n_heads=h, dim=d, vdim=values.shape[-1] if values is not None else 0, bf=bf,
-                          depth=self.depth.value, cap_parents=cap_p, dtype=keys.dtype,
-                          vdtype=values.dtype if values is not None else None, device=keys.device,
-                          with_values=values is not None)
+        vdim = values.shape[-1] if values is not None else 0
+        st = reuse
+        if st is not None and not (st.n_heads == h and st.dim == d and st.vdim == vdim and st.bf == bf
+                                   and st.depth == self.depth.value and st.dtype == keys.dtype
+                                   and (values is None or st.vdtype == values.dtype)
+                                   and st.cap_parents >= (-(-cap_p // bf) * bf if st.depth == 3 else cap_p)):
+            st = None
+        if st is None:
+            st = S.IndexState(n_heads=h, dim=d, vdim=vdim, bf=bf, depth=self.depth.value, cap_parents=cap_p,
+                              dtype=keys.dtype, vdtype=values.dtype if values is not None else None, device=keys.device,
+                              with_values=values is not None)
+        else:
+            st.active_parents = self.active_parents     # the build clears only what was in use
         k1 = -(-n // bf) if n else 0
         k2 = -(-k1 // bf) if k1 else 0
         g = torch.Generator(device=keys.device)
         g.manual_seed(self.seed)
         cent1 = cent2 = None
         if n:
-            # distinct random points as initial centres (indexer/cuda.py:229-237)
-            cent1 = torch.rand((h, n), generator=g, device=keys.device).topk(k1, dim=1).indices.to(torch.int32).contiguous()
+            # distinct random points as initial centres (indexer/cuda.py:229-237): one uniformly drawn
+            # point out of each of k equal strides of the sequence (O(k), no sort)
+            cent1 = self._stratified(h, n, k1, g, keys.device)
             if st.depth == 3:
-                cent2 = torch.rand((h, k1), generator=g, device=keys.device).topk(k2, dim=1).indices.to(torch.int32).contiguous()
+                cent2 = self._stratified(h, k1, k2, g, keys.device)
         S.build(st, keys, values, cent_idx1=cent1, cent_idx2=cent2, n_iters=max(1, int(self.max_iterations)),
                 balance_rounds=self.balance_rounds, use_tensor_cores=self.use_tensor_cores)
         self.state = st
@@ -180,6 +202,8 @@ class CUDAIndexer(BaseIndexer):
         self._gp_bound = k2
         self._snapshot = None
         self._scan_slots, self._scan_pending = None, False
+        self._appended = 0
+        st.active_parents = 0
         return self
 
     # ---- update -------------------------------------------------------------
@@ -358,18 +382,14 @@ class CUDAIndexer(BaseIndexer):
 
     @torch.no_grad()
     def rebuild(self):
-        """Full rebuild over the keys currently stored (token order), e.g. every N decode steps."""
+        """Full rebuild over the keys currently stored (token order), e.g. every N decode steps.  The
+        arrays are reused when they have room for `max_context` again: no allocation, and only the
+        slots that were in use are cleared."""
         self.wait_pending_update() if self.state is not None else None
         st = self.state
         n = self._n_keys
         keys, values = S.export(st, n)
-        b = self.__class__(self.depth, self.max_iterations, self.branching_factor, self.verbose, self.pad_value,
-                           max_context=self.max_context, reserve_worst_case=self.reserve_worst_case,
-                           use_tensor_cores=self.use_tensor_cores, seed=self.seed, balance_rounds=self.balance_rounds)
-        b.build(keys.unsqueeze(0), None if values is None else values.unsqueeze(0))
-        self.state, self._parents_bound, self._gp_bound = b.state, b._parents_bound, b._gp_bound
-        self._snapshot = None
-        self._scan_slots, self._scan_pending = None, False
+        self._build(keys.unsqueeze(0), None if values is None else values.unsqueeze(0), reuse=st)
         return self
 
     # ---- checkpoint ---------------------------------------------------------

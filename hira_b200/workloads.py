@@ -105,11 +105,11 @@ def make_kv(n_heads: int, n: int, seed: int, device, *, dist: str = "rope_outlie
         elif dist == "aniso":
             k *= scale
         elif dist == "clustered":
-            # a mixture of 1,024 tight clusters (centres N(0, 9 I), spread 0.35): data on which ball
+            # a mixture of 1,024 tight clusters (centres N(0, 9 I), spread 0.05): data on which ball
             # pruning has something to prune -- not one of the reference's distributions, a control
             cent = torch.randn((1024, dim), generator=g, device=device, dtype=torch.float32) * 3.0
             which = torch.randint(0, 1024, (n,), generator=g, device=device)
-            k = cent[which] + 0.35 * k
+            k = cent[which] + 0.05 * k
         else:
             raise ValueError(f"unknown distribution {dist!r}")
         keys[i] = k.to(dtype)

@@ -386,8 +386,10 @@ int hira_kth_score(const hira_index_t* index, int32_t n_qheads,
  *   cent_idx1 [n_heads][ceil(n_keys/bf)] int32: key positions used as initial
  *          parent centres; cent_idx2 [n_heads][ceil(n1/bf)] (depth 3): parent
  *          ids used as initial grandparent centres.  NULL = evenly strided.
- *   The index arrays are fully (re)initialised: unused slots are zero rows,
- *   radius 0, count 0, slot2token -1.
+ *   The index arrays are (re)initialised: unused slots are zero rows, radius 0, count 0,
+ *   slot2token -1.  With index->active_parents == 0 the whole capacity is cleared; with a bound
+ *   there (the host vouches that no parent slot beyond it was ever used, and that the arrays
+ *   were zero / -1 when allocated) only the slots below max(bound, what this build fills).
  *   balance_rounds: 0 = the reference's rule (every centre keeps its bf closest points, the
  *          overflow is dealt to whatever slots are free).  R > 0 = capacity-aware assignment: the
  *          overflow chooses again, R times, among the centres that still have room (nearest

@@ -158,11 +158,22 @@ def test_update_matches_brute_force_and_keeps_values_aligned(levels, max_context
     for hh in range(h):
         got = set(tok[hh][out[hh] != 0].tolist())
         assert got == set(torch.nonzero(gt[hh] > tau[hh]).flatten().tolist())
-    # a full rebuild over the stored keys selects the same tokens
+    # a full rebuild over the stored keys selects the same tokens; with pre-allocated room the arrays
+    # are reused, and whatever the old layout held beyond the new one is cleared
+    before = ix.state
     ix.rebuild()
+    if max_context is not None:
+        assert ix.state is before
     out2 = CUDASearcher(block_c=bf, gate="ge", leaf="ge").search(q, tau, ix)
     for hh in range(h):
         assert set(ix.slot2token[hh][out2[hh] != 0].tolist()) == set(torch.nonzero(gt[hh] > tau[hh]).flatten().tolist())
+    valid = _valid_slots(ix)
+    assert int(valid.sum()) == h * (n + extra)
+    assert float(ix.children[~valid].abs().sum()) == 0.0 and float(ix.values[0][~valid].abs().sum()) == 0.0
+    assert int(ix._child_counts.sum()) == h * (n + extra)
+    ix.update(keys[:, :, :3], vals[:, :, :3])               # and the rebuilt index takes appends again
+    ix.check_status()
+    assert int(_valid_slots(ix).sum()) == h * (n + extra + 3)
 
 
 def test_state_dict_roundtrip():

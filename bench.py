@@ -52,7 +52,8 @@ E2E_REPEATS = 5
 # DRAM bytes (read + write) of one search_kernel launch per (batch, kv head) group of 131,072 keys,
 # from an ncu capture of this bench at --batch 2 (16 groups); traffic grows in proportion to the
 # groups a launch covers.  Keyed by kernel variant; None = not captured.
-SEARCH_DRAM_BYTES_PER_GROUP = {"search_kernel": (559.073280e6 + 7.247872e6) / 16, "search_q8_kernel": None}
+SEARCH_DRAM_BYTES_PER_GROUP = {"search_kernel": (559.073280e6 + 7.247872e6) / 16,
+                               "search_q8_kernel": (323.394304e6 + 4.631552e6) / 16}
 
 
 def peaks():

@@ -3,6 +3,13 @@ child->parent maps with clusters of any size, indexer/cpu.py:12-22,48-122) into 
 arrays the CUDA kernels search.  The block size becomes the largest cluster of any level;
 smaller clusters leave free slots (count < block size).  Radii are taken over as stored,
 so the search visits exactly the nodes the reference CPU search visits.
+
+A CPU index may be deeper than the blocked layout's three levels (CPUIndexer builds any depth,
+indexer/cpu.py:79-120; HiraConfig.num_levels defaults to 5).  Its levels above the third are then
+left out: every ball encloses all of its descendants (the radii are triangle-inequality bounds,
+indexer/cpu.py:263-311), so a key with q.k >= tau passes every ancestor's gate whatever the depth,
+and the selected set under the leaf-tested rule is the same -- the upper levels could only have
+skipped whole grandparent blocks earlier.
 """
 from __future__ import annotations
 
@@ -15,9 +22,11 @@ def blocked_from_levels(centers, radii, c2p, values=None):
     centers = [np.asarray(c, dtype=np.float32) for c in centers]
     radii = [np.asarray(r, dtype=np.float32) for r in radii]
     c2p = [np.asarray(c, dtype=np.int64) for c in c2p]
+    if len(centers) < 2:
+        raise ValueError(f"Unsupported depth {len(centers)}: the blocked index has 2 or 3 levels")
+    if len(centers) > 3:          # deeper trees: the lowest three levels select the same keys (see above)
+        centers, radii, c2p = centers[:3], radii[:3], c2p[:2]
     n_levels = len(centers)
-    if n_levels not in (2, 3):
-        raise ValueError(f"Unsupported depth {n_levels}: the blocked index has 2 or 3 levels")
     H, N, D = centers[0].shape
     K1 = centers[1].shape[1]
     bf = 1

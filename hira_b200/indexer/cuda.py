@@ -41,6 +41,13 @@ class CUDAIndexer(BaseIndexer):
                  pad_value: float = DEFAULT_PAD_VALUE, *, max_context: Optional[int] = None,
                  reserve_worst_case: bool = False, use_tensor_cores: bool = True, seed: int = 1234,
                  balance_rounds: int = 0):
+        # More than three levels (HiraConfig.num_levels defaults to 5, the CPU indexer's depth) are
+        # served by a three-level index: balls enclose all their descendants, so the keys selected
+        # under a leaf-tested rule do not depend on the depth; further levels would only skip whole
+        # grandparent blocks earlier.  The reference's CUDAIndexer rejects such depths (indexer/cuda.py:18-21).
+        self.requested_levels = num_levels.value if isinstance(num_levels, CUDAIndexer.DEPTH) else int(num_levels)
+        if not isinstance(num_levels, CUDAIndexer.DEPTH):
+            num_levels = min(int(num_levels), 3)
         self.depth = num_levels if isinstance(num_levels, CUDAIndexer.DEPTH) else CUDAIndexer.DEPTH(num_levels)
         self.max_iterations = max_iterations
         self.branching_factor = int(branching_factor)

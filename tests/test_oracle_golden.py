@@ -446,3 +446,34 @@ def test_cfg0_cuda_search_matches_reference_cpu_kernel():
     w = torch.softmax(torch.where(mask, sc, torch.full_like(sc, float("-inf"))).double(), dim=-1)
     want = torch.einsum("hn,hnd->hd", w, vals.double()).float()
     assert float((out - want).abs().max() / want.abs().max()) < 1e-5
+
+
+def test_five_level_cpu_index_converts_to_three_levels_with_the_same_selection():
+    """A CPU-format index of 5 levels (HiraConfig's default depth) searched by the reference C++ kernel
+    selects exactly the tokens that the blocked conversion of its lowest three levels selects."""
+    import torch
+    from hira_b200 import workloads as W
+    from hira_b200.indexer.convert import blocked_from_levels
+    from oracle import cpu_index as CI
+    ext = CI.load_reference_kernel(ROOT)
+    if ext is None:
+        pytest.skip("oracle/_ref/hira_torch_ext_v3.so is not built (make -C oracle ref REF=...)")
+    keys, vals = W.make_kv(2, 4096, 17, "cpu", dist="clustered", dtype=torch.float32)
+    levels = CI.build_levels(keys.numpy(), 5, 4, 2)
+    assert [lv["size"] for lv in levels] == [4096, 1024, 256, 64, 16]
+    q = W.make_queries(4, 3, "cpu")
+    q_hat = (q / q.norm(dim=-1, keepdim=True)).contiguous()
+    sc = torch.einsum("hgd,hnd->hgn", q_hat.view(2, 2, 128), keys).reshape(4, 4096)
+    tau = W.guard_banded_tau(sc, 40)
+    want = CI.reference_search(ext, levels, q_hat, tau).numpy()
+    arrays = blocked_from_levels([lv["centers"] for lv in levels], [lv["radii"] for lv in levels],
+                                 [lv["c2p"] for lv in levels[:-1]])
+    assert arrays["meta"]["depth"] == 3
+    ox = O.OracleIndex.from_arrays(arrays)
+    dense, keep = O.search(ox, q_hat.numpy(), tau.numpy(), flags=O.GATE_GE | O.LEAF_GE)
+    for qh in range(4):
+        toks = ox.slot2token[qh // 2][np.nonzero(keep[qh])[0]]
+        assert sorted(toks.tolist()) == np.nonzero(want[qh])[0].tolist()
+        assert len(toks) == 40
+    # the five-level search pruned at its upper levels, the conversion did not need them
+    assert (want != 0).sum() == 160

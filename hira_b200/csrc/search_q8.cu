@@ -737,7 +737,7 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const uint
         {
             const bool writer = HeadReduce<GT>::is_writer(lane);
             const float leaf_thr = (leaf_mode == HIRA_LEAF_GT) ? nextafterf(my_tau, CUDART_INF_F) : my_tau;
-            constexpr int XR = 4;   // candidate rows per group and iteration: their loads are in flight together
+            constexpr int XR = 2;   // candidate rows per group and iteration: their loads are in flight together
             const int iters = (ncand + XR * SEARCH_GROUPS - 1) / (XR * SEARCH_GROUPS);   // uniform over the workers
             for (int it = 0; it < iters; ++it) {
                 int e[XR], r[XR];

@@ -131,7 +131,9 @@ def test_bad_inputs_raise_value_error():
     with pytest.raises(ValueError):
         CUDASearcher(block_c=8).search(_query(2, 32, 1), torch.zeros(2).cuda(), CUDAIndexer(2, 1, 8))  # not built
     with pytest.raises(ValueError):
-        CUDAIndexer(5, 1, 8)                                                    # only 2 or 3 levels
+        CUDAIndexer(1, 1, 8)                                                    # fewer than 2 levels
+    deep = CUDAIndexer(5, 1, 8)                                                 # deeper trees are served by 3 levels
+    assert deep.requested_levels == 5 and deep.depth == CUDAIndexer.DEPTH.THREE_LEVELS
 
 
 @pytest.mark.parametrize("levels", [2, 3])

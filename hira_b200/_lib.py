@@ -28,7 +28,10 @@ EXPORTED_SYMBOLS = [
     "hira_recompute_radii", "hira_export", "hira_assign", "hira_sparse_attn_noalloc", "hira_decode_attention",
     "hira_search_scan", "hira_append_scanned", "hira_step_events_create", "hira_step_events_destroy",
     "hira_decode_step", "hira_q8_refresh",
+    "hira_exchange_bytes", "hira_peer_alloc", "hira_peer_open", "hira_peer_close", "hira_peer_free", "hira_exchange_merge",
 ]
+MAX_PEERS = 16            # HIRA_MAX_PEERS
+PEER_HANDLE_BYTES = 64    # HIRA_PEER_HANDLE_BYTES
 NOALLOC_SCRATCH_FLOATS = 1 << 20
 SEARCH_STATS = 10     # uint32 counters per query head (HIRA_SEARCH_STATS)
 Q8_CHAN = 136         # floats per head in q8_chan_scale (HIRA_Q8_CHAN)
@@ -100,6 +103,18 @@ def _declare(lib):
     lib.hira_sparse_attn_noalloc.argtypes = [IX, P, P, P, I32, I32, P, P, P, P, P, I32, I64, I32, P, P, I64, I64, P]
     lib.hira_merge_partials.restype = C.c_int
     lib.hira_merge_partials.argtypes = [P, P, I32, I32, I32, I64, I64, I64, I64, P, P, P]
+    lib.hira_exchange_bytes.restype = I64
+    lib.hira_exchange_bytes.argtypes = [I32, I32, I32]
+    lib.hira_peer_alloc.restype = C.c_int
+    lib.hira_peer_alloc.argtypes = [I64, C.POINTER(C.c_void_p), C.c_char_p]
+    lib.hira_peer_open.restype = C.c_int
+    lib.hira_peer_open.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
+    lib.hira_peer_close.restype = C.c_int
+    lib.hira_peer_close.argtypes = [P]
+    lib.hira_peer_free.restype = C.c_int
+    lib.hira_peer_free.argtypes = [P]
+    lib.hira_exchange_merge.restype = C.c_int
+    lib.hira_exchange_merge.argtypes = [P, C.POINTER(C.c_void_p), I32, I32, I32, I32, C.c_uint32, I32, C.c_float, P, P, P, P]
     lib.hira_append.restype = C.c_int
     lib.hira_append.argtypes = [IX, P, P, I32, I64, I64, I32, P, P, SZ, P]
     lib.hira_append_workspace_bytes.restype = SZ

@@ -18,7 +18,7 @@ LIB_PATH = PKG_DIR / "libhira_b200.so"
 PROFILE_LIB_PATH = PKG_DIR / "libhira_b200_profile.so"   # the same library with phase time stamps in search_q8.cu
 OBJ_DIR = CSRC / "build"
 
-SOURCES = ["api.cu", "search.cu", "search_q8.cu", "attention.cu", "append.cu", "threshold.cu", "build.cu", "assign_tc.cu"]
+SOURCES = ["api.cu", "search.cu", "search_q8.cu", "attention.cu", "append.cu", "threshold.cu", "build.cu", "assign_tc.cu", "exchange.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -45,7 +45,7 @@ def _stale(target: Path, deps) -> bool:
 def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> Path:
     nvcc = _nvcc()
     OBJ_DIR.mkdir(parents=True, exist_ok=True)
-    headers = [CSRC / "common.cuh", CSRC / "search_common.cuh", CSRC / "tc_common.cuh", PKG_DIR.parent / "include" / "hira_b200.h"]
+    headers = [CSRC / "common.cuh", CSRC / "search_common.cuh", CSRC / "tc_common.cuh", CSRC / "merge_row.cuh", PKG_DIR.parent / "include" / "hira_b200.h"]
     sources = list(SOURCES)
     jobs = []
     for src in sources:

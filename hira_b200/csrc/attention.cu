@@ -11,6 +11,7 @@
 // gather one value row (256 B for V=128 bf16) with two 128-bit loads per lane,
 // four rows in flight per thread; softmax is online in fp32.
 #include "common.cuh"
+#include "merge_row.cuh"
 #include <math_constants.h>
 #include <atomic>
 
@@ -358,31 +359,8 @@ __global__ void merge_kernel(const float* __restrict__ part_o, const float* __re
                              int n_parts, int vdim, int normalised, float* __restrict__ out,
                              float* __restrict__ out_ml, long long out_stride, long long out_ml_stride) {
     const int qh = blockIdx.x;
-    float M = -CUDART_INF_F;
-    for (int s = 0; s < n_parts; ++s)
-        M = fmaxf(M, part_ml[s * ml_part_stride + qh * ml_head_stride]);
-    float L = 0.f;
-    for (int s = 0; s < n_parts; ++s) {
-        const float ms = part_ml[s * ml_part_stride + qh * ml_head_stride];
-        const float ls = part_ml[s * ml_part_stride + qh * ml_head_stride + 1];
-        if (ms > -CUDART_INF_F) L += ls * __expf(ms - M);
-    }
-    for (int d = threadIdx.x; d < vdim; d += blockDim.x) {
-        float o = 0.f;
-        for (int s = 0; s < n_parts; ++s) {
-            const float ms = part_ml[s * ml_part_stride + qh * ml_head_stride];
-            if (ms > -CUDART_INF_F) {
-                float w = __expf(ms - M);
-                if (normalised) w *= part_ml[s * ml_part_stride + qh * ml_head_stride + 1];
-                o += w * part_o[s * o_part_stride + qh * o_head_stride + d];
-            }
-        }
-        out[(size_t)qh * out_stride + d] = L > 0.f ? o / L : 0.f;
-    }
-    if (out_ml && threadIdx.x == 0) {
-        out_ml[(size_t)qh * out_ml_stride] = M;
-        out_ml[(size_t)qh * out_ml_stride + 1] = L;
-    }
+    merge_row(part_o + qh * o_head_stride, part_ml + qh * ml_head_stride, o_part_stride, ml_part_stride, n_parts, vdim,
+              normalised, out + (size_t)qh * out_stride, out_ml ? out_ml + (size_t)qh * out_ml_stride : nullptr);
 }
 
 template <typename TK, typename TV, int NCH, int NVCH>

@@ -6,9 +6,11 @@ Two ways to spread the path over the GPUs of a node, neither present in the refe
     output, so each rank owns whole heads and nothing is exchanged (`shard_heads`);
   * by sequence shard (million-token contexts): each rank indexes a contiguous slice of the
     sequence, all ranks search with the same threshold, and the per-shard softmax partials
-    (m, l, normalised o) are all-gathered and merged with the log-sum-exp kernel
-    (`PartialsExchange`, or the allocation-per-call `gather_partials` + `merge_gathered`).
-    The append goes to the last shard only.
+    (m, l, normalised o) are exchanged and merged with the log-sum-exp arithmetic: by ONE
+    kernel per step that stores this rank's rows into every peer's buffer over NVLink peer
+    memory, waits for the peers' rows and merges them (`PeerPartialsExchange`), or by an NCCL
+    all-gather followed by the merge kernel (`PartialsExchange`, or the allocation-per-call
+    `gather_partials` + `merge_gathered`).  The append goes to the last shard only.
 """
 from __future__ import annotations
 
@@ -68,6 +70,110 @@ class PartialsExchange:
         """Log-sum-exp merge of the gathered partials on the device (hira_merge_partials)."""
         from . import index_state as S
         return S.merge_partials(self.buf[:, :, 2:], self.buf[:, :, :2], out=out)
+
+
+class PeerPartialsExchange:
+    """The exchange of sequence-sharded decode over NVLink peer memory, fused with the merge
+    (hira_exchange_merge): every rank owns a buffer its peers map through CUDA IPC; one kernel per
+    step stores this rank's (m, l, normalised out) rows into every rank's buffer with plain peer
+    stores, flags them with the step number, waits (bounded) for the peers' rows of the same step and
+    merges.  No library collective is on the data path; torch.distributed only carries the 64-byte
+    handles at set-up.  Same surface as PartialsExchange: the attention kernel writes `local_out` /
+    `local_ml`, `all_gather()` is a no-op, `merge(out=)` runs the fused step.
+
+    peers=... (a list of already mapped buffer addresses with this rank's own at [rank]) skips the
+    IPC set-up: several emulated ranks of one process on one GPU, driven with `phases`."""
+
+    def __init__(self, n_qheads: int, vdim: int, device, group=None, *, rank: Optional[int] = None,
+                 world: Optional[int] = None, peers=None, wait_seconds: float = 2.0):
+        import ctypes as C
+        import torch.distributed as dist
+        from . import _lib as L
+        self._L, self._C = L, C
+        self.lib = L.load()
+        self.group = group
+        ok = dist.is_available() and dist.is_initialized()
+        self.world = world if world is not None else (dist.get_world_size(group) if ok else 1)
+        self.rank = rank if rank is not None else (dist.get_rank(group) if ok else 0)
+        if not 1 <= self.world <= L.MAX_PEERS:
+            raise ValueError(f"PeerPartialsExchange serves up to {L.MAX_PEERS} ranks, got {self.world}")
+        self.n_qheads, self.vdim, self.device = n_qheads, vdim, torch.device(device)
+        self.wait_seconds = float(wait_seconds)
+        self.local = torch.zeros((n_qheads, vdim + 2), dtype=torch.float32, device=device)
+        self.local_ml = self.local[:, :2]
+        self.local_out = self.local[:, 2:]
+        self.status = torch.zeros((1,), dtype=torch.int32, device=device)
+        self.seq = 0
+        self._own = None
+        self._opened = []
+        if peers is not None:
+            addrs = [int(a) for a in peers]
+        else:
+            nbytes = int(self.lib.hira_exchange_bytes(self.world, n_qheads, vdim))
+            own = C.c_void_p()
+            handle = C.create_string_buffer(L.PEER_HANDLE_BYTES)
+            with torch.cuda.device(self.device):
+                L.check(self.lib.hira_peer_alloc(nbytes, C.byref(own), handle), "hira_peer_alloc")
+            self._own = own.value
+            addrs = [None] * self.world
+            addrs[self.rank] = own.value
+            if self.world > 1:
+                handles = [None] * self.world
+                dist.all_gather_object(handles, bytes(handle.raw), group=group)
+                with torch.cuda.device(self.device):
+                    for r, hb in enumerate(handles):
+                        if r == self.rank:
+                            continue
+                        p = C.c_void_p()
+                        L.check(self.lib.hira_peer_open(hb, C.byref(p)), f"hira_peer_open(rank {r})")
+                        addrs[r] = p.value
+                        self._opened.append(p.value)
+        self.peer_addrs = addrs
+        self._peers = (C.c_void_p * self.world)(*addrs)
+
+    @property
+    def message_bytes(self) -> int:
+        return self.n_qheads * (self.vdim + 2) * 4
+
+    def all_gather(self):
+        """Nothing to enqueue: the rows travel inside `merge`."""
+        return None
+
+    def merge(self, out: Optional[torch.Tensor] = None, out_ml: Optional[torch.Tensor] = None, *, phases: int = 3,
+              seq: Optional[int] = None) -> torch.Tensor:
+        """One step: push, wait, merge (phases=3) on the current stream; `check()` reads the status."""
+        L = self._L
+        if out is None:
+            out = torch.empty((self.n_qheads, self.vdim), dtype=torch.float32, device=self.device)
+        if seq is None:
+            self.seq += 1
+            seq = self.seq
+        rc = self.lib.hira_exchange_merge(L.ptr(self.local), self._peers, self.world, self.rank, self.n_qheads, self.vdim,
+                                          seq, phases, self.wait_seconds, L.ptr(out), L.ptr(out_ml), L.ptr(self.status),
+                                          L.current_stream(self.device))
+        L.check(rc, "hira_exchange_merge")
+        return out
+
+    def check(self):
+        """Synchronises and raises if a wait for a peer's rows ran out in any step since the last check."""
+        if int(self.status.item()) != 0:
+            self.status.zero_()
+            raise RuntimeError("hira_exchange_merge: a peer's partials did not arrive within "
+                               f"{self.wait_seconds} s (rank {self.rank} of {self.world})")
+
+    def close(self):
+        """Unmaps the peers' buffers; call on every rank, then a host barrier, then `free()`."""
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            for p in self._opened:
+                self.lib.hira_peer_close(p)
+        self._opened = []
+
+    def free(self):
+        if self._own is not None:
+            with torch.cuda.device(self.device):
+                self.lib.hira_peer_free(self._own)
+            self._own = None
 
 
 def gather_partials(out: torch.Tensor, ml: torch.Tensor, group=None) -> Tuple[torch.Tensor, torch.Tensor]:

@@ -229,6 +229,47 @@ int hira_merge_partials(const float* part_o, const float* part_ml,
                         float* out, float* out_ml, void* stream);
 
 /* ------------------------------------------------------------------------- */
+/* Sequence shards over several GPUs of one node: exchange of the partials over
+ * NVLink peer memory, fused with their merge (no counterpart in the reference,
+ * which is single-device).  One process per GPU.  Every rank allocates one
+ * exchange buffer of hira_exchange_bytes() with hira_peer_alloc, passes the
+ * 64-byte handle to its peers by any host channel, opens theirs with
+ * hira_peer_open, and then calls hira_exchange_merge once per decode step
+ * after hira_sparse_attn:
+ *
+ *   local_rows [n_qheads][2 + vdim] fp32: this rank's (m, l, normalised out)
+ *              rows -- point hira_sparse_attn's out_ml at row + 0 and out at
+ *              row + 2 with head strides of 2 + vdim
+ *   peer_bufs  HOST array of `world` device pointers: entry r is rank r's
+ *              exchange buffer as mapped in THIS process (entry `rank` is the
+ *              pointer hira_peer_alloc returned)
+ *   seq        step number, the same on every rank, never 0, +1 per step
+ *   phases     3 = push this rank's rows to every peer, wait for every
+ *              source's rows, merge (the decode step); 1 = push only,
+ *              2 = wait + merge only (for drivers that run several ranks'
+ *              kernels on one GPU, where kernels must not wait on each other)
+ *   wait_seconds bound of the wait (0 = 2 s); when it runs out *status (device
+ *              int32, zeroed by the caller) becomes 1 and `out` is not written
+ *   out [n_qheads][vdim], out_ml [n_qheads][2] or NULL: as hira_merge_partials,
+ *              whose arithmetic this reproduces bit for bit
+ *
+ * Buffers are written with plain peer stores; nothing is multicast.  Close the
+ * peers' mappings (hira_peer_close) before their owners free them
+ * (hira_peer_free), with a host barrier in between. */
+#define HIRA_MAX_PEERS 16
+#define HIRA_PEER_HANDLE_BYTES 64
+int64_t hira_exchange_bytes(int32_t world, int32_t n_qheads, int32_t vdim);
+int hira_peer_alloc(int64_t bytes, void** dev_ptr, unsigned char* handle);
+int hira_peer_open(const unsigned char* handle, void** dev_ptr);
+int hira_peer_close(void* dev_ptr);
+int hira_peer_free(void* dev_ptr);
+int hira_exchange_merge(const float* local_rows, void* const* peer_bufs,
+                        int32_t world, int32_t rank, int32_t n_qheads,
+                        int32_t vdim, uint32_t seq, int32_t phases,
+                        float wait_seconds, float* out, float* out_ml,
+                        int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------- */
 /* Append.  Replaces CUDAIndexer.update (indexer/cuda.py:544-701) and its
  * Triton kernels (kernels/triton_update_kernels.py:6-418) for decode-time
  * insertion: nearest valid parent by ||c||^2 - 2 x.c (ties -> lowest index),

@@ -1,7 +1,8 @@
 """Two-GPU checks (skipped on a single GPU): sequence-sharded decode -- every rank indexes its
 slice of the sequence, all ranks search with the same threshold, the per-shard softmax
 partials are all-gathered over NCCL and merged on the device -- against attention over the
-whole sequence; and KV-head sharding against the unsharded result."""
+whole sequence; the one-kernel exchange over NVLink peer memory against that; and KV-head sharding
+against the unsharded result."""
 import os
 import sys
 from pathlib import Path
@@ -62,6 +63,25 @@ def _worker(rank, world, port, ret):
     torch.cuda.synchronize()
     err_seq = float((merged.cpu() - want).abs().max() / want.abs().max())
 
+    # (1b) the same exchange as ONE kernel over NVLink peer memory (push, wait, merge): bit-identical
+    # to the all-gather + merge, step after step on both buffer parities
+    from hira_b200.parallel import PeerPartialsExchange
+    ex = PeerPartialsExchange(h * g, d, "cuda")
+    same = True
+    for step in range(4):
+        f = 1.0 + 0.25 * step                                    # different rows every step
+        ex.local_out.copy_(out * f)
+        ex.local_ml.copy_(ml)
+        po, pml = gather_partials(out * f, ml)
+        want_step = merge_gathered(po, pml)
+        got = ex.merge()
+        ex.check()
+        same = same and torch.equal(got, want_step)
+    dist.barrier()
+    ex.close()
+    dist.barrier()
+    ex.free()
+
     # (2) KV-head shards: no exchange on the data path, only the comparison gathers
     mine = list(shard_heads(h, world, rank))
     out_h, _ = attend(keys[mine], vals[mine], mine)
@@ -69,7 +89,7 @@ def _worker(rank, world, port, ret):
     dist.all_gather(gathered, out_h)
     torch.cuda.synchronize()
     err_head = float((torch.cat(gathered).cpu() - want).abs().max() / want.abs().max())
-    ret[rank] = (err_seq, err_head)
+    ret[rank] = (err_seq, err_head, same)
     dist.barrier()
     dist.destroy_process_group()
 
@@ -83,5 +103,6 @@ def test_sequence_and_head_sharding_on_two_gpus():
         ret = mgr.dict()
         mp.spawn(_worker, args=(2, port, ret), nprocs=2, join=True)
         assert len(ret) == 2
-        for err_seq, err_head in ret.values():
+        for err_seq, err_head, same in ret.values():
             assert err_seq < 2e-3 and err_head < 2e-3, (err_seq, err_head)
+            assert same, "the peer-memory exchange differs from all-gather + merge"

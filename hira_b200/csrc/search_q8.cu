@@ -131,6 +131,10 @@ search_q8_prepare_kernel(const float* __restrict__ q, const float* __restrict__ 
                          int group, int gt, int dim, unsigned char* __restrict__ out) {
     constexpr int GT = 4;
     __shared__ float s_red[4][8];
+    // The search kernel behind this one is launched with programmatic stream serialisation: its CTAs may
+    // start (barriers, tensor memory, gates) while this grid runs, and wait for it (griddepcontrol.wait)
+    // where they first need the query terms or the hint words.
+    asm volatile("griddepcontrol.launch_dependents;");
     const int tid = threadIdx.x, warp = tid >> 5, wl = tid & 31;
     const int chunk = blockIdx.x, h = blockIdx.y;
     int nq = group - chunk * gt;
@@ -343,8 +347,7 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const uint
             // The first stages of a tile that holds keys are requested at once, before the gates are
             // known (they are nearly always needed; at most Q8_SLOTS stages are read for nothing when
             // the gates prune the whole tile); the rest follows the gates.
-            mbar_expect_tx(bar_q, Q8_QBYTES);
-            bulk_load(s_base + Q8Smem::BQ, qterms + ((size_t)h * P.n_chunks + chunk) * Q8_QBYTES, Q8_QBYTES, bar_q);
+            // the stage requests first: the query terms come from the kernel launched just before this one
             const int8_t* rows_g = k8 + ((size_t)h * cap_children + tile_c0) * Q8_DIM;
             const uint32_t* meta_g = k8_meta + (size_t)h * cap_children + tile_c0;
             int order[Q8_MAX_STAGES] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -362,6 +365,9 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const uint
             for (int i = 0; i < spec; ++i) order[i] = i;
             for (; issued < spec && issued < Q8_SLOTS; ++issued) issue(issued);
             Q8_STAMP(8, Q8_WORKERS);
+            asm volatile("griddepcontrol.wait;" ::: "memory");   // the query terms are written
+            mbar_expect_tx(bar_q, Q8_QBYTES);
+            bulk_load(s_base + Q8Smem::BQ, qterms + ((size_t)h * P.n_chunks + chunk) * Q8_QBYTES, Q8_QBYTES, bar_q);
             for (int k = 0; !failed; ++k) {
                 if (!got_go && k >= spec) {
                     if (!mbar_wait(bar_go, 0)) { failed = true; break; }
@@ -623,6 +629,7 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const uint
         if (tid == 0) {
             mbar_arrive(bar_go);
             if (chunk == 0 && tile_in_use) {   // what the gates kept, for the next search's streaming mode
+                asm volatile("griddepcontrol.wait;" ::: "memory");   // the counters of the last search are consumed
                 atomicAdd(hint, (uint32_t)__popc(*reinterpret_cast<volatile int*>(&s_need)));
                 atomicAdd(hint + 1, (uint32_t)n_stage_tile);
             }
@@ -827,11 +834,24 @@ static int launch_q8(SearchParams P, int chunks, const hira_index_t* ix, cudaStr
     search_q8_prepare_kernel<<<dim3((unsigned)chunks, (unsigned)P.n_heads), Q8_WORKERS, 0, stream>>>(
         P.q, ix->q8_chan_scale, ix->q8_chan_scale, P.group, GT, P.dim, qterms);
     HIRA_CHECK_LAUNCH("hira_search (int8 pre-filter, query terms) launch");
-    dim3 grid((unsigned)chunks, (unsigned)P.n_tiles_active, (unsigned)P.n_heads);
-    kern<<<grid, Q8_THREADS, smem, stream>>>(P, reinterpret_cast<const int8_t*>(ix->children_q8),
-                                            reinterpret_cast<const uint32_t*>(ix->children_q8_meta), qterms,
-                                            reinterpret_cast<uint32_t*>(ix->q8_chan_scale));
-    HIRA_CHECK_LAUNCH("hira_search (int8 pre-filter) launch");
+    // launched so that its CTAs may start while the query terms are still being prepared (see above)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)chunks, (unsigned)P.n_tiles_active, (unsigned)P.n_heads);
+    cfg.blockDim = dim3(Q8_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, kern, P, reinterpret_cast<const int8_t*>(ix->children_q8),
+                           reinterpret_cast<const uint32_t*>(ix->children_q8_meta),
+                           reinterpret_cast<const unsigned char*>(qterms), reinterpret_cast<uint32_t*>(ix->q8_chan_scale));
+    if (e != cudaSuccess) {
+        set_error("hira_search (int8 pre-filter) launch: %s", cudaGetErrorString(e));
+        return HIRA_ERR_CUDA;
+    }
     return HIRA_OK;
 }
 

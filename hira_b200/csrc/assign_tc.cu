@@ -4,11 +4,12 @@
 // Per CTA: one tile of 128 points (A, 32 KB, loaded once by TMA) against all centroids of
 // the head in tiles of 128 (B, 32 KB per tile, double-buffered TMA).  One elected thread
 // issues tcgen05.mma (M=128, N=128, K=16, bf16 in, fp32 accumulate in TMEM: 128 lanes x 128
-// columns), tcgen05.commit signals an mbarrier, then each of the 128 threads reads its own
-// point's row of the accumulator with tcgen05.ld and folds score = ||c||^2 - 2 x.c into a
-// running arg-min, so the (points x centroids) matrix never leaves the SM.  Two TMEM
-// accumulators alternate (the MMAs of the next centroid tile run while the previous one is
-// read out) and two CTAs are resident per SM.
+// columns), tcgen05.commit signals an mbarrier, then 256 threads read the accumulator with
+// tcgen05.ld (two threads per point, 64 columns each, the next 32 columns in flight while 32 are
+// reduced) and fold score = ||c||^2 - 2 x.c into a running arg-min, so the (points x centroids)
+// matrix never leaves the SM.  The tile's ||c||^2 sit in shared memory, fetched one tile ahead.
+// Two TMEM accumulators alternate (the MMAs of the next centroid tile run while the previous one
+// is read out) and two CTAs are resident per SM.
 //
 // Every wait on an mbarrier is bounded; on a timeout the CTA writes index -1 for its points
 // and leaves in an orderly way (TMEM freed).  No TMA multicast is used.
@@ -25,13 +26,16 @@ constexpr int TC_BN = 128;       // centroids per tile
 constexpr int TC_K = 128;        // D
 constexpr int TC_BOX_K = 64;     // elements per 128-byte swizzle row
 constexpr int TC_BOX_BYTES = TC_BM * TC_BOX_K * 2;   // 16 KB
-constexpr int TC_THREADS = 160;      // 4 epilogue warps + 1 producer/MMA warp
+constexpr int TC_EPI_THREADS = 256;  // 8 epilogue warps: warp w reads TMEM lanes 32 (w & 3) .. + 31, columns 64 (w >> 2) .. + 63 of a tile
+constexpr int TC_THREADS = TC_EPI_THREADS + 32;   // + 1 producer/MMA warp
 
 struct TcSmem {
     // offsets in the 1024-byte aligned dynamic shared memory
     static constexpr int A = 0;                          // 2 boxes
     static constexpr int B = 2 * TC_BOX_BYTES;           // 2 stages x 2 boxes
-    static constexpr int BAR = B + 4 * TC_BOX_BYTES;     // bar_a, bar_b[2], bar_bfree[2], bar_full[2], bar_empty[2]
+    static constexpr int CSQ = B + 4 * TC_BOX_BYTES;     // 2 stages x 128 squared centroid norms
+    static constexpr int COMB = CSQ + 2 * TC_BN * 4;     // (score, index) of the upper column half, per point
+    static constexpr int BAR = COMB + TC_BM * 8;         // bar_a, bar_b[2], bar_bfree[2], bar_full[2], bar_empty[2]
     static constexpr int TMEM_SLOT = BAR + 9 * 8;
     static constexpr int TOTAL = TMEM_SLOT + 16;
 };
@@ -52,6 +56,27 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a, uint64_t b
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
 }
+// tcgen05.ld without its wait: the registers are valid only after tmem_ld_wait(r), which names them as
+// in/out operands so that no use of them can be scheduled ahead of the wait
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                   "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                   "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                 :: "memory");
+}
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -65,10 +90,11 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// Warps 0-3 (128 threads) own the 128 TMEM lanes = the 128 points and run the arg-min
-// epilogue; lane 0 of warp 4 issues the TMA loads and the MMAs.  Two accumulators (2 x 128
-// TMEM columns) alternate, so the MMAs of centroid tile j+1 run while tile j is being read
-// out.  All hand-offs are mbarriers with bounded waits.
+// Warps 0-7 (256 threads) run the arg-min epilogue: warp w owns TMEM lanes 32 (w & 3) .. + 31 = 32 of
+// the 128 points, over the column half w >> 2 of every centroid tile (a warp may only read the lane
+// quarter of its index mod 4, so two warps share each quarter); lane 0 of warp 8 issues the TMA loads
+// and the MMAs.  Two accumulators (2 x 128 TMEM columns) alternate, so the MMAs of centroid tile j+1
+// run while tile j is being read out.  All hand-offs are mbarriers with bounded waits.
 __global__ void __launch_bounds__(TC_THREADS, 2)
 assign_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                  const __nv_bfloat16* __restrict__ points, long long p_head_stride,
@@ -97,12 +123,12 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             mbar_init(bar_b + 8 * i, 1);
             mbar_init(bar_bfree + 8 * i, 1);
             mbar_init(bar_full + 8 * i, 1);
-            mbar_init(bar_empty + 8 * i, TC_BM);
+            mbar_init(bar_empty + 8 * i, TC_EPI_THREADS);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    if (warp == 4) {
+    if (warp == TC_EPI_THREADS / 32) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                      ::"r"(s_base + TcSmem::TMEM_SLOT), "r"(2 * TC_BN) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -113,8 +139,8 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     const uint32_t tmem = *s_tmem;
     bool failed = false;
 
-    if (warp == 4) {
-        if (tid == 4 * 32) {
+    if (warp == TC_EPI_THREADS / 32) {
+        if (tid == TC_EPI_THREADS) {
             // ---- producer + MMA issuer -------------------------------------------------------
             mbar_expect_tx(bar_a, 2 * TC_BOX_BYTES);
             tma_load_3d(s_base + TcSmem::A, &map_a, 0, m0, h, bar_a);
@@ -151,43 +177,55 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             if (failed) s_fail = 1;
         }
     } else {
-        // ---- arg-min epilogue: thread t owns point m0 + t = TMEM lane t ------------------------
+        // ---- arg-min epilogue: thread (w, l) owns point m0 + 32 (w & 3) + l = that TMEM lane, over the
+        //      column half w >> 2 of every tile; the two halves of a point are combined at the end ------
+        const int pt = (warp & 3) * 32 + (tid & 31);   // point within the CTA
+        const int half = warp >> 2;
         float best = CUDART_INF_F;
         int best_i = 0x7fffffff;
         const float* cs = csq + (size_t)h * k;
-        const bool cs_aligned = (reinterpret_cast<uintptr_t>(cs) & 15) == 0;
+        // The squared norms of a centroid tile sit in shared memory: every thread fetches one norm of the
+        // NEXT tile while it reads the current one out (past the last centroid: +inf, never the minimum),
+        // and the 128 epilogue threads meet once per tile, so the fetch is never waited for.
+        float* s_csq = reinterpret_cast<float*>(sm + TcSmem::CSQ);
+        if (tid < TC_BN) s_csq[tid] = tid < k ? __ldg(cs + tid) : CUDART_INF_F;
         for (int j = 0; j < nt; ++j) {
             const int st = j & 1;
-            if (!mbar_wait(bar_full + 8 * st, (j >> 1) & 1) || *reinterpret_cast<volatile int*>(&s_fail)) { failed = true; break; }
+            const int cn = (j + 1) * TC_BN + tid;
+            const float cnext = (tid < TC_BN && j + 1 < nt && cn < k) ? __ldg(cs + cn) : CUDART_INF_F;
+            // everyone is done with tile j - 1 (whose norms stage st ^ 1 held) and has stored its norm of tile j
+            asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_THREADS) : "memory");
+            if (tid < TC_BN) s_csq[(st ^ 1) * TC_BN + tid] = cnext;
+            // A thread whose wait ran out keeps walking the tiles (it only meets the others at the barrier
+            // above, so nobody is left waiting there) and reports -1 for its point.
+            if (failed) continue;
+            if (!mbar_wait(bar_full + 8 * st, (j >> 1) & 1) || *reinterpret_cast<volatile int*>(&s_fail)) {
+                failed = true;
+                continue;
+            }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const bool full_tile = (j + 1) * TC_BN <= k;
-#pragma unroll 1
-            for (int cb = 0; cb < TC_BN; cb += 32) {
-                uint32_t r[32];
-                tmem_ld32(tmem + ((uint32_t)(warp * 32) << 16) + st * TC_BN + cb, r);
-                // scores of 32 centroids and their minimum; the index is looked up only when the
-                // running minimum improves (rare after the first tiles), which keeps the common
-                // path at one load, one FMA and one min per element
-                const int c0 = j * TC_BN + cb;
-                const float* cp = cs + c0;
-                float cq[32];
-                if (full_tile && cs_aligned) {
+            const uint32_t t0 = tmem + ((uint32_t)((warp & 3) * 32) << 16) + st * TC_BN + half * (TC_BN / 2);
+            uint32_t r[2][32];
+            tmem_ld32_nowait(t0, r[0]);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float4 v = __ldg(reinterpret_cast<const float4*>(cp) + i);
-                        cq[4 * i] = v.x; cq[4 * i + 1] = v.y; cq[4 * i + 2] = v.z; cq[4 * i + 3] = v.w;
-                    }
-                } else if (full_tile) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) cq[i] = __ldg(cp + i);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) cq[i] = (c0 + i < k) ? __ldg(cp + i) : CUDART_INF_F;  // past the last centroid
-                }
+            for (int q = 0; q < TC_BN / 64; ++q) {
+                // the next 32 columns are on their way while these 32 are reduced
+                tmem_ld_wait(r[q & 1]);
+                if (q + 1 < TC_BN / 64) tmem_ld32_nowait(t0 + (q + 1) * 32, r[(q + 1) & 1]);
+                const int c0 = j * TC_BN + half * (TC_BN / 2) + q * 32;
+                const float4* cq4 = reinterpret_cast<const float4*>(s_csq + st * TC_BN + half * (TC_BN / 2) + q * 32);
                 float sc[32];
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    sc[i] = __fmaf_rn(-2.0f, __uint_as_float(r[i]), cq[i]);  // 2*x.c is exact: same bits as csq - 2*dot
+                for (int i = 0; i < 8; ++i) {
+                    const float4 v = cq4[i];
+                    // 2*x.c is exact: same bits as csq - 2*dot
+                    sc[4 * i] = __fmaf_rn(-2.0f, __uint_as_float(r[q & 1][4 * i]), v.x);
+                    sc[4 * i + 1] = __fmaf_rn(-2.0f, __uint_as_float(r[q & 1][4 * i + 1]), v.y);
+                    sc[4 * i + 2] = __fmaf_rn(-2.0f, __uint_as_float(r[q & 1][4 * i + 2]), v.z);
+                    sc[4 * i + 3] = __fmaf_rn(-2.0f, __uint_as_float(r[q & 1][4 * i + 3]), v.w);
+                }
+                // the minimum of the 32 scores; the index is looked up only when the running minimum
+                // improves (rare after the first tiles)
                 float m01[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) m01[i] = fminf(sc[2 * i], sc[2 * i + 1]);
@@ -208,8 +246,18 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(bar_empty + 8 * st);
         }
-        const int p = m0 + tid;
-        if (p < n) {
+        // the two column halves of a point: the smaller score, on a tie the lower centroid (the earlier in the scan)
+        float2* s_comb = reinterpret_cast<float2*>(sm + TcSmem::COMB);
+        if (half == 1) s_comb[pt] = make_float2(failed ? CUDART_NAN_F : best, __int_as_float(best_i));
+        asm volatile("bar.sync 1, %0;" ::"n"(TC_EPI_THREADS) : "memory");
+        if (half == 0) {
+            const float2 o = s_comb[pt];
+            const int oi = __float_as_int(o.y);
+            if (o.x != o.x) failed = true;   // the other half gave up
+            else if (o.x < best || (o.x == best && oi < best_i)) { best = o.x; best_i = oi; }
+        }
+        const int p = m0 + pt;
+        if (half == 0 && p < n) {
             if (failed) {
                 out_idx[(size_t)h * n + p] = -1;
                 out_d2[(size_t)h * n + p] = 0.f;
@@ -228,14 +276,14 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             }
         }
     }
-    if (tid == 4 * 32 && failed) {
+    if (tid == TC_EPI_THREADS && failed) {
         // let copies that may still be in flight land before the shared memory is given back (bounded)
         mbar_wait(bar_b, 0);
         mbar_wait(bar_b + 8, 0);
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (warp == 4) {
+    if (warp == TC_EPI_THREADS / 32) {
         __syncwarp();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(2 * TC_BN) : "memory");
     }

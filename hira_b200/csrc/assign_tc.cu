@@ -56,6 +56,11 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a, uint64_t b
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
 }
+__device__ __forceinline__ float min3f(float a, float b, float c) {
+    float d;
+    asm("min.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 // tcgen05.ld without its wait: the registers are valid only after tmem_ld_wait(r), which names them as
 // in/out operands so that no use of them can be scheduled ahead of the wait
 __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
@@ -218,22 +223,23 @@ assign_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const float4 v = cq4[i];
-                    // 2*x.c is exact: same bits as csq - 2*dot
-                    sc[4 * i] = __fmaf_rn(-2.0f, __uint_as_float(r[q & 1][4 * i]), v.x);
-                    sc[4 * i + 1] = __fmaf_rn(-2.0f, __uint_as_float(r[q & 1][4 * i + 1]), v.y);
-                    sc[4 * i + 2] = __fmaf_rn(-2.0f, __uint_as_float(r[q & 1][4 * i + 2]), v.z);
-                    sc[4 * i + 3] = __fmaf_rn(-2.0f, __uint_as_float(r[q & 1][4 * i + 3]), v.w);
+                    // 2*x.c is exact: same bits as csq - 2*dot; two scores per packed FMA
+                    const float2 m2 = make_float2(-2.0f, -2.0f);
+                    const float2 lo = __ffma2_rn(m2, make_float2(__uint_as_float(r[q & 1][4 * i]), __uint_as_float(r[q & 1][4 * i + 1])),
+                                                 make_float2(v.x, v.y));
+                    const float2 hi = __ffma2_rn(m2, make_float2(__uint_as_float(r[q & 1][4 * i + 2]), __uint_as_float(r[q & 1][4 * i + 3])),
+                                                 make_float2(v.z, v.w));
+                    sc[4 * i] = lo.x; sc[4 * i + 1] = lo.y; sc[4 * i + 2] = hi.x; sc[4 * i + 3] = hi.y;
                 }
-                // the minimum of the 32 scores; the index is looked up only when the running minimum
-                // improves (rare after the first tiles)
-                float m01[16];
+                // the minimum of the 32 scores by three-input minima (16 instead of 31 operations); the
+                // index is looked up only when the running minimum improves (rare after the first tiles)
+                float m1[12];
 #pragma unroll
-                for (int i = 0; i < 16; ++i) m01[i] = fminf(sc[2 * i], sc[2 * i + 1]);
-#pragma unroll
-                for (int w = 8; w >= 1; w >>= 1)
-#pragma unroll
-                    for (int i = 0; i < w; ++i) m01[i] = fminf(m01[i], m01[i + w]);
-                const float cmin = m01[0];
+                for (int i = 0; i < 10; ++i) m1[i] = min3f(sc[3 * i], sc[3 * i + 1], sc[3 * i + 2]);
+                m1[10] = sc[30];
+                m1[11] = sc[31];
+                const float cmin = fminf(min3f(min3f(m1[0], m1[1], m1[2]), min3f(m1[3], m1[4], m1[5]), min3f(m1[6], m1[7], m1[8])),
+                                         min3f(m1[9], m1[10], m1[11]));
                 if (cmin < best) {   // strict: an equal score later in the scan never replaces an earlier centroid
                     best = cmin;
                     int first = 31;

@@ -53,7 +53,7 @@ E2E_REPEATS = 5
 # from an ncu capture of this bench at --batch 2 (16 groups); traffic grows in proportion to the
 # groups a launch covers.  Keyed by kernel variant; None = not captured.
 SEARCH_DRAM_BYTES_PER_GROUP = {"search_kernel": (559.073280e6 + 7.247872e6) / 16,
-                               "search_q8_kernel": (323.394304e6 + 4.631552e6) / 16}
+                               "search_q8_kernel": (323.377408e6 + 4.551936e6) / 16}
 
 
 def peaks():

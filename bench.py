@@ -552,7 +552,7 @@ def secondary_cfg4(args, dev, rank, world, dist, barrier, peak):
     # if the peers' buffers cannot be mapped on this node (every rank takes the same branch)
     ex, why = None, ""
     try:
-        ex = PeerPartialsExchange(w.q_heads, DIM, dev)
+        ex = PeerPartialsExchange(w.q_heads, DIM, dev, wait_seconds=1.0)
     except Exception as e:   # noqa: BLE001 - reported in the result line
         why = f"{type(e).__name__}: {e}"[:160]
     if dist is not None:
@@ -582,6 +582,29 @@ def secondary_cfg4(args, dev, rank, world, dist, barrier, peak):
     barrier()                        # the ranks enter their first exchange together (its wait is bounded)
     b.step(0, append=False)
     torch.cuda.synchronize()
+
+    def exchange_flagged() -> bool:
+        """True on every rank if on any rank a wait for a peer's rows ran out."""
+        if not isinstance(b.exchange, PeerPartialsExchange):
+            return False
+        f = b.exchange.status.clone()
+        if dist is not None:
+            dist.all_reduce(f, op=dist.ReduceOp.MAX)
+        return int(f.item()) != 0
+
+    if exchange_flagged():
+        # the peer route does not work on this node: every rank falls back to all-gather + merge
+        barrier()
+        ex.close()
+        barrier()
+        ex.free()
+        ex = PartialsExchange(w.q_heads, DIM, dev)
+        exchange_kind = ("NCCL all-gather of (m, l, out) rows into a preallocated buffer + merge kernel "
+                         "(a peer's rows did not arrive within 1 s in the first step)")
+        b.exchange, b.out, b.out_ml = ex, ex.local_out, ex.local_ml
+        barrier()
+        b.step(0, append=False)
+        torch.cuda.synchronize()
     merged_dist = b.merged.clone()
     last = rank == world - 1
     # the last shard's append runs beside its attention and exchange on a second stream
@@ -591,8 +614,10 @@ def secondary_cfg4(args, dev, rank, world, dist, barrier, peak):
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     total_ms, search_ms, attn_ms, exch_ms, append_ms = t.tolist()
+    exchange_error = None
     if isinstance(ex, PeerPartialsExchange):
-        ex.check()                       # no wait for a peer's rows ran out
+        if exchange_flagged():           # reported, never fatal for the headline
+            exchange_error = "a wait for a peer's rows ran out during the timed loop: the step time is not valid"
         if dist is not None:
             dist.barrier()
         ex.close()
@@ -624,7 +649,7 @@ def secondary_cfg4(args, dev, rank, world, dist, barrier, peak):
             "exchange": exchange_kind,
             "exchange_bytes_per_gpu": ex.message_bytes, "algorithmic_bytes_per_gpu": c["search_bytes"] + c["attn_bytes"],
             "search_gbs_per_gpu": ach, "frac": ach / peak, "scanned_fraction": c["scanned_fraction"],
-            "merged_vs_one_rank_max_rel_err": check}
+            "merged_vs_one_rank_max_rel_err": check, **({"exchange_error": exchange_error} if exchange_error else {})}
 
 
 def phase_profile(args):

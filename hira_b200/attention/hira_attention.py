@@ -207,11 +207,19 @@ class HiraDecodeStep:
         step.synchronize()                                   # out_host is ready, the key is indexed
 
     The indexer must have been built with room for the appends (`max_context`): the step never
-    reallocates."""
+    reallocates.
+
+    `graph_steps=G` (> 0) replays the step from CUDA graphs: the first call with a given set of host
+    buffers (and threshold tensor) records the library call into a graph, later calls with the same
+    buffers replay it -- the host refills its buffers in place, nothing else is launched.  Grids are
+    frozen in a graph, so a recording covers the slots the index can reach within the next G appends
+    (a few empty tiles are visited meanwhile) and is made anew after G appends.  Worth it when the step
+    is short (small batch per GPU), where the launches rather than the kernels bound it."""
 
     def __init__(self, indexer, n_qheads: int, *, q_dtype: torch.dtype = torch.float32, gate: str = "ge",
                  scaling: Optional[float] = None, threshold_method: str = "sample_mean_topk", sample_size: int = 1000,
-                 topk: int = 16, fused_scan: bool = False, side_stream: Optional["torch.cuda.Stream"] = None):
+                 topk: int = 16, fused_scan: bool = False, side_stream: Optional["torch.cuda.Stream"] = None,
+                 graph_steps: int = 0):
         st: S.IndexState = indexer.state
         if st is None:
             raise ValueError("Indexer is not built")
@@ -225,6 +233,35 @@ class HiraDecodeStep:
                                   tau_k=1 if samples is None else min(topk, samples.shape[1]))
         self.sm_scale = float(scaling) if scaling is not None else st.dim ** -0.5
         self.side = side_stream if side_stream is not None else torch.cuda.Stream(device=st.device)
+        self.graph_steps = int(graph_steps)
+        self._graphs = {}            # addresses of the caller's buffers -> recorded step
+        self._graph_left = 0         # appends the recorded grids still cover
+        self._graph_active = 0       # the bound on the slots in use they were recorded with
+
+    def _run_graphed(self, q_host, out_host, threshold, k_host, v_host):
+        ix, st = self.indexer, self.indexer.state
+        if self._graph_left <= 0 or ix.active_parents > self._graph_active:
+            # record anew, for the slots the index can reach within the next graph_steps appends
+            self._graphs.clear()
+            saved = ix._parents_bound, ix._gp_bound
+            ix._parents_bound += self.graph_steps
+            ix._gp_bound += self.graph_steps
+            self._graph_active = ix.active_parents
+            ix._parents_bound, ix._gp_bound = saved
+            self._graph_left = self.graph_steps
+        key = (q_host.data_ptr(), out_host.data_ptr(), 0 if threshold is None else threshold.data_ptr(),
+               0 if k_host is None else k_host.data_ptr(), 0 if v_host is None else v_host.data_ptr())
+        g = self._graphs.get(key)
+        if g is None:
+            st.active_parents = self._graph_active
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._step.run(q_host, out_host, sm_scale=self.sm_scale, tau=threshold, k_host=k_host, v_host=v_host,
+                               side_stream=self.side)
+            self._graphs[key] = g
+        g.replay()
+        if k_host is not None:
+            self._graph_left -= 1
 
     def __call__(self, q_host: torch.Tensor, out_host: torch.Tensor, *, threshold: Optional[torch.Tensor] = None,
                  k_host: Optional[torch.Tensor] = None, v_host: Optional[torch.Tensor] = None):
@@ -241,8 +278,11 @@ class HiraDecodeStep:
             ix._parents_bound += 1          # the append may open a new parent and a new grandparent
             ix._gp_bound += 1
         st.active_parents = ix.active_parents
-        self._step.run(q_host, out_host, sm_scale=self.sm_scale, tau=threshold, k_host=k_host, v_host=v_host,
-                       side_stream=self.side)
+        if self.graph_steps > 0:
+            self._run_graphed(q_host, out_host, threshold, k_host, v_host)
+        else:
+            self._step.run(q_host, out_host, sm_scale=self.sm_scale, tau=threshold, k_host=k_host, v_host=v_host,
+                           side_stream=self.side)
         if k_host is not None:
             ix._n_keys += 1
             ix._appended += 1

@@ -161,6 +161,12 @@ extern "C" int hira_decode_step(const hira_index_t* index, const hira_step_t* st
     const size_t qe = hira::elem_size(q_dtype), ke = hira::elem_size(index->dtype), ve = hira::elem_size(index->vdtype);
     const bool fused = append && st->scan != nullptr;
 
+    // The second stream joins the step here: it starts behind whatever precedes the step on `stream` (under
+    // stream capture this is what makes its work part of the recorded graph).
+    if (append && side_s != main_s) {
+        HIRA_CUDA_OK(cudaEventRecord(copied, main_s), "event record");
+        HIRA_CUDA_OK(cudaStreamWaitEvent(side_s, copied, 0), "stream wait");
+    }
     HIRA_CUDA_OK(cudaMemcpyAsync(st->q_dev, q_host, (size_t)n_qheads * index->dim * qe, cudaMemcpyHostToDevice, main_s),
                  "query copy");
     if (append) {

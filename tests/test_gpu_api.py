@@ -383,6 +383,43 @@ def test_update_on_a_side_stream_beside_the_attention():
         assert x is None and y is None or torch.equal(x, y), name
 
 
+@pytest.mark.parametrize("levels", [3, 2])
+def test_decode_step_replayed_from_cuda_graphs_equals_the_plain_step(levels):
+    """HiraDecodeStep(graph_steps=5): the library call recorded into a CUDA graph per set of host buffers
+    and replayed while the host refills the buffers in place, recorded anew every 5 appends (12 steps:
+    three recordings, two buffer sets) -- same outputs and the same index as the plain step."""
+    from hira_b200 import HiraDecodeStep
+    h, hq, n, d, bf = 2, 8, 4096, 128, 16
+    keys, vals = _keys(h, n, d, 211, torch.bfloat16), _keys(h, n, d, 212, torch.bfloat16)
+    a = CUDAIndexer(levels, 1, bf, max_context=n + 64, reserve_worst_case=True, seed=9).build(keys, vals)
+    b = CUDAIndexer(levels, 1, bf, max_context=n + 64, reserve_worst_case=True, seed=9).build(keys, vals)
+    plain, graphed = HiraDecodeStep(a, hq), HiraDecodeStep(b, hq, graph_steps=5)
+    steps = 12
+    more_k = _keys(h, steps, d, 213, torch.bfloat16)[0].transpose(0, 1).contiguous().cpu()   # (steps, h, d)
+    more_v = _keys(h, steps, d, 214, torch.bfloat16)[0].transpose(0, 1).contiguous().cpu()
+    tau = torch.full((hq,), 0.12, device="cuda")
+    bufs = [dict(q=torch.empty((hq, d)).pin_memory(), k=torch.empty((h, d), dtype=torch.bfloat16).pin_memory(),
+                 v=torch.empty((h, d), dtype=torch.bfloat16).pin_memory(), o=torch.empty((hq, d)).pin_memory())
+            for _ in range(2)]
+    out_plain = torch.empty((hq, d), dtype=torch.float32).pin_memory()
+    g = torch.Generator().manual_seed(6)
+    for i in range(steps):
+        s = bufs[i % 2]
+        s["q"].copy_(torch.randn((hq, d), generator=g))
+        s["k"].copy_(more_k[i])
+        s["v"].copy_(more_v[i])
+        plain(s["q"], out_plain, threshold=tau, k_host=s["k"], v_host=s["v"])
+        plain.synchronize()
+        graphed(s["q"], s["o"], threshold=tau, k_host=s["k"], v_host=s["v"])
+        graphed.synchronize()
+        assert torch.allclose(out_plain, s["o"], rtol=1e-5, atol=1e-6), i
+    assert len(graphed._graphs) <= 2
+    a.check_status(), b.check_status()
+    for name in a.state.ARRAYS:
+        x, y = getattr(a.state, name), getattr(b.state, name)
+        assert x is None and y is None or torch.equal(x, y), name
+
+
 @pytest.mark.parametrize("levels,fused", [(3, False), (3, True), (2, False)])
 def test_decode_step_from_host_buffers_equals_the_separate_calls(levels, fused):
     """HiraDecodeStep (one hira_decode_step call per token: host query in, host output out, the

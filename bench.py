@@ -612,7 +612,7 @@ def secondary_cfg3(args, dev):
     append_bytes = h * ((k1 + k1 // bf) * (DIM * e + 4) + 2 * DIM * e)
     return {"workload": w.name, "heads": h, "prefix": prefix, "appends": steps, "rebuild_every": every,
             "append_us_per_step": statistics.mean(append_us), "append_us_by_window": append_us,
-            "append_algorithmic_bytes": append_bytes, "rebuild_ms": statistics.mean(rebuild_ms) if rebuild_ms else None,
+            "append_algorithmic_bytes": append_bytes, "rebuild_ms": statistics.median(rebuild_ms) if rebuild_ms else None, "rebuild_ms_each": rebuild_ms,
             "rebuilds": len(rebuild_ms), "initial_build_ms": build_ms,
             "note": "append step = 8 heads, launch-latency bound (one small kernel pair per step)"}
 

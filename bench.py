@@ -338,8 +338,12 @@ class DecodeBench:
                    search_ms=statistics.mean(ev[j][0].elapsed_time(ev[j][1]) for j in range(steps)),
                    attn_ms=statistics.mean(ev[j][1].elapsed_time(ev[j][2]) for j in range(steps)),
                    append_ms=statistics.mean(ev[j][3].elapsed_time(ev[j][4]) for j in range(steps)) if has_append else 0.0)
+        # every step on its own (start of step j to start of step j + 1): a single stall of the host or of a
+        # peer shows up here instead of hiding in the mean
+        res["step_ms_each"] = [ev[j][0].elapsed_time(ev[j + 1][0] if j + 1 < steps else t_end) for j in range(steps)]
         if nccl:
             res["exchange_ms"] = statistics.mean(nccl[j][0].elapsed_time(nccl[j][1]) for j in range(steps))
+            res["exchange_ms_median"] = statistics.median(nccl[j][0].elapsed_time(nccl[j][1]) for j in range(steps))
         status = int(self.st.status.item())
         if status:
             raise RuntimeError(f"index capacity exhausted during the bench (status {status})")
@@ -577,7 +581,10 @@ def secondary_cfg3(args, dev):
     w = W.CFG3
     h, prefix, steps, every, bf = w.kv_heads, w.context, args.stream_steps, 1024, w.branching
     keys, vals = W.make_kv(h, prefix + steps, 1300, dev, dist=w.dist, dtype=w.dtype)
-    ix = CUDAIndexer(3, 1, bf, max_context=prefix + every + 8, reserve_worst_case=True, use_tensor_cores=not args.no_tc)
+    # room for the whole stream is reserved once (as a server that knows its maximum context does), so that the
+    # rebuilds reuse the index arrays instead of growing them
+    ix = CUDAIndexer(3, 1, bf, max_context=prefix + steps + every + 8, reserve_worst_case=True,
+                     use_tensor_cores=not args.no_tc)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ix.build(keys[None, :, :prefix], vals[None, :, :prefix])         # warm: allocations, first launches
     e0.record()
@@ -601,7 +608,6 @@ def secondary_cfg3(args, dev):
         ix._gp_bound += n
         ix.check_status()
         if pos < prefix + steps:
-            ix.max_context = pos + every + 8
             e0.record()
             ix.rebuild()
             e1.record()
@@ -685,13 +691,16 @@ def secondary_cfg4(args, dev, rank, world, dist, barrier, peak):
         torch.cuda.synchronize()
     merged_dist = b.merged.clone()
     last = rank == world - 1
+    fb0 = S.q8_fallback_count(dev)
     # the last shard's append runs beside its attention and exchange on a second stream
     r = b.timed_loop(steps, warm, barrier, fused=False, side=torch.cuda.Stream(dev) if last else None, append=last)
-    t = torch.tensor([r["total_ms"], r["search_ms"], r["attn_ms"], r.get("exchange_ms", 0.0), r["append_ms"]],
-                     device=dev, dtype=torch.float64)
+    each = r["step_ms_each"]
+    t = torch.tensor([r["total_ms"], r["search_ms"], r["attn_ms"], r.get("exchange_ms", 0.0), r["append_ms"],
+                      statistics.median(each), max(each), r.get("exchange_ms_median", 0.0),
+                      float(S.q8_fallback_count(dev) - fb0)], device=dev, dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, search_ms, attn_ms, exch_ms, append_ms = t.tolist()
+    total_ms, search_ms, attn_ms, exch_ms, append_ms, step_median_ms, step_max_ms, exch_median_ms, fallbacks = t.tolist()
     exchange_error = None
     if isinstance(ex, PeerPartialsExchange):
         if exchange_flagged():           # reported, never fatal for the headline
@@ -721,8 +730,10 @@ def secondary_cfg4(args, dev, rank, world, dist, barrier, peak):
         check = float((alone - merged_dist).abs().max() / alone.abs().max())
     ach = c["search_bytes"] / (search_ms * 1e-3) / 1e9
     return {"workload": w.name, "n_gpus": world, "context": w.context * world, "tokens_per_gpu": w.context,
-            "step_us": total_ms / steps * 1e3, "search_us": search_ms * 1e3, "sparse_attn_and_exchange_us": attn_ms * 1e3,
-            "exchange_us": exch_ms * 1e3, "exchange_note": "max over ranks; includes waiting for the slowest rank's rows",
+            "step_us": total_ms / steps * 1e3, "step_us_median": step_median_ms * 1e3, "step_us_max": step_max_ms * 1e3,
+            "search_ctas_that_fell_back": int(fallbacks),
+            "search_us": search_ms * 1e3, "sparse_attn_and_exchange_us": attn_ms * 1e3,
+            "exchange_us": exch_ms * 1e3, "exchange_us_median": exch_median_ms * 1e3, "exchange_note": "max over ranks; includes waiting for the slowest rank's rows",
             "append_us_last_shard": append_ms * 1e3,
             "exchange": exchange_kind,
             "exchange_bytes_per_gpu": ex.message_bytes, "algorithmic_bytes_per_gpu": c["search_bytes"] + c["attn_bytes"],
@@ -968,6 +979,8 @@ def run_ours(args):
         secondary["cfg4"] = secondary_cfg4(args, dev, rank, world, dist, barrier, peak)
         barrier()
 
+    from hira_b200 import index_state as S_
+    q8_fallbacks = S_.q8_fallback_count(dev)
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -1019,6 +1032,8 @@ def run_ours(args):
         "dense_attention_us": None if dense_ms is None else dense_max * 1e3,
         "vs_dense": None if dense_ms is None else dense_max / ms_per_step,
         "secondary": secondary, "clocks": clocks, "cpu_baseline": cpu,
+        # CTAs of the pre-filter search (rank 0, whole run) whose bounded wait ran out and that took the exact fallback
+        "search_ctas_that_fell_back": q8_fallbacks,
     }
     print(json.dumps(line), flush=True)
     if dist is not None:

@@ -27,7 +27,7 @@ EXPORTED_SYMBOLS = [
     "hira_threshold", "hira_kth_score", "hira_prepare_query", "hira_build_workspace_bytes", "hira_build",
     "hira_recompute_radii", "hira_export", "hira_assign", "hira_sparse_attn_noalloc", "hira_decode_attention",
     "hira_search_scan", "hira_append_scanned", "hira_step_events_create", "hira_step_events_destroy",
-    "hira_decode_step", "hira_q8_refresh",
+    "hira_decode_step", "hira_q8_refresh", "hira_q8_fallback_count",
     "hira_exchange_bytes", "hira_peer_alloc", "hira_peer_open", "hira_peer_close", "hira_peer_free", "hira_exchange_merge",
 ]
 MAX_PEERS = 16            # HIRA_MAX_PEERS
@@ -103,6 +103,8 @@ def _declare(lib):
     lib.hira_sparse_attn_noalloc.argtypes = [IX, P, P, P, I32, I32, P, P, P, P, P, I32, I64, I32, P, P, I64, I64, P]
     lib.hira_merge_partials.restype = C.c_int
     lib.hira_merge_partials.argtypes = [P, P, I32, I32, I32, I64, I64, I64, I64, P, P, P]
+    lib.hira_q8_fallback_count.restype = C.c_int
+    lib.hira_q8_fallback_count.argtypes = [C.POINTER(C.c_uint32)]
     lib.hira_exchange_bytes.restype = I64
     lib.hira_exchange_bytes.argtypes = [I32, I32, I32]
     lib.hira_peer_alloc.restype = C.c_int

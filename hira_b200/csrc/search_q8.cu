@@ -47,6 +47,10 @@ constexpr int Q8_TMEM_COLS = Q8_MAX_STAGES * Q8_NCOL;     // 128
 constexpr int Q8_THREADS = 160;                           // 4 worker warps + 1 producer/MMA warp
 constexpr int Q8_WORKERS = 128;
 constexpr int Q8_MAX_TP = 128;                            // parents per tile (bf >= 8)
+// Bound of every mbarrier wait of the search kernel: 20 M cycles (about 10 ms), three orders of magnitude
+// above the longest legitimate wait (a bulk copy, four MMAs).  A CTA whose wait runs out falls back to the
+// exact path, so the bound only limits what such an event costs the step.
+constexpr unsigned long long Q8_WAIT_CYCLES = 20ull * 1000 * 1000;
 constexpr int Q8_HINT = 132;   // q8_chan_scale[h][132..134] as uint32: stages kept / stages of the last search, stream-all flag
 constexpr int Q8_QBYTES = HIRA_Q8_QUERY_BYTES;            // prepared query terms of one (kv head, chunk of 4 heads)
 static_assert(Q8_QBYTES == 2048 + 64, "B operand (16 rows x 128 B) + (c1, c2, A, B) of 4 heads");
@@ -196,6 +200,10 @@ search_q8_prepare_kernel(const float* __restrict__ q, const float* __restrict__ 
         qc[3] = 127.0f * l1[j] * 1.001f + A * (127.0f * 11.32f * 3.9e-6f);
     }
 }
+
+// CTAs of this device that took the exact fallback because a bounded wait ran out (or the shared-memory
+// window was misaligned) since the library was loaded: read with hira_q8_fallback_count
+__device__ unsigned int g_q8_fallbacks;
 
 #ifdef HIRA_Q8_PROFILE
 __device__ unsigned long long g_q8_prof[16384][16];
@@ -370,7 +378,7 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const uint
             bulk_load(s_base + Q8Smem::BQ, qterms + ((size_t)h * P.n_chunks + chunk) * Q8_QBYTES, Q8_QBYTES, bar_q);
             for (int k = 0; !failed; ++k) {
                 if (!got_go && k >= spec) {
-                    if (!mbar_wait(bar_go, 0)) { failed = true; break; }
+                    if (!mbar_wait(bar_go, 0, Q8_WAIT_CYCLES)) { failed = true; break; }
                     got_go = true;
                     const int need = *reinterpret_cast<volatile int*>(&s_need);
                     for (int s = spec; s < n_stage_tile; ++s)
@@ -379,14 +387,14 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const uint
                 if (k >= n) break;
                 while (issued < n && issued < k + Q8_SLOTS) {
                     // the slot held stage issued - Q8_SLOTS: free once its MMAs are complete
-                    if (issued >= Q8_SLOTS && !mbar_wait(bar_done + 8 * (issued - Q8_SLOTS), 0)) { failed = true; break; }
+                    if (issued >= Q8_SLOTS && !mbar_wait(bar_done + 8 * (issued - Q8_SLOTS), 0, Q8_WAIT_CYCLES)) { failed = true; break; }
                     issue(issued);
                     ++issued;
                 }
                 if (failed) break;
                 const int slot = k % Q8_SLOTS;
-                if (k == 0 && !mbar_wait(bar_q, 0)) { failed = true; break; }
-                if (!mbar_wait(bar_full + 8 * slot, (k / Q8_SLOTS) & 1)) { failed = true; break; }
+                if (k == 0 && !mbar_wait(bar_q, 0, Q8_WAIT_CYCLES)) { failed = true; break; }
+                if (!mbar_wait(bar_full + 8 * slot, (k / Q8_SLOTS) & 1, Q8_WAIT_CYCLES)) { failed = true; break; }
                 if (k == 0) Q8_STAMP(9, Q8_WORKERS);
                 if (k == 3) Q8_STAMP(11, Q8_WORKERS);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -400,8 +408,8 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const uint
             if (failed) {
                 *reinterpret_cast<volatile int*>(&s_fail) = 1;
                 // let copies that may still be in flight land before the ring is reused (bounded)
-                mbar_wait(bar_q, 0);
-                for (int i = 0; i < issued && i < Q8_SLOTS; ++i) mbar_wait(bar_full + 8 * i, ((issued - 1 - i) / Q8_SLOTS) & 1);
+                mbar_wait(bar_q, 0, Q8_WAIT_CYCLES);
+                for (int i = 0; i < issued && i < Q8_SLOTS; ++i) mbar_wait(bar_full + 8 * i, ((issued - 1 - i) / Q8_SLOTS) & 1, Q8_WAIT_CYCLES);
             }
         }
     } else {
@@ -647,7 +655,7 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const uint
         {
             bool failed = !aligned;
             if (aligned) {   // the prepared query terms and their constants arrive by a bulk copy
-                const bool ok = mbar_wait(bar_q, 0);
+                const bool ok = mbar_wait(bar_q, 0, Q8_WAIT_CYCLES);
                 if (!__all_sync(0xffffffffu, ok)) {
                     failed = true;
                     if (wl == 0) *reinterpret_cast<volatile int*>(&s_fail) = 1;
@@ -667,7 +675,7 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const uint
                 if (failed) break;
                 if (!((need >> s) & 1)) continue;
                 // warp-uniform outcome: tcgen05.ld below is a warp-wide instruction
-                const bool ok = mbar_wait(bar_done + 8 * k, 0) && !*reinterpret_cast<volatile int*>(&s_fail);
+                const bool ok = mbar_wait(bar_done + 8 * k, 0, Q8_WAIT_CYCLES) && !*reinterpret_cast<volatile int*>(&s_fail);
                 if (!__all_sync(0xffffffffu, ok)) {
                     failed = true;
                     if (wl == 0) *reinterpret_cast<volatile int*>(&s_fail) = 1;
@@ -707,6 +715,7 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const uint
             Q8_STAMP(4, 0);
             if (*reinterpret_cast<volatile int*>(&s_fail)) {   // the same for every worker after the barrier
                 // a bounded wait ran out: every filled row of a kept parent is a candidate (exact, only slower)
+                if (tid == 0) atomicAdd(&g_q8_fallbacks, 1u);
                 for (int s = 0; s < n_stage_tile; ++s) {
                     const int r = s * Q8_STAGE_ROWS + tid;
                     const int pl = div_bf(r, bf, P.bf_magic);
@@ -990,6 +999,18 @@ extern "C" int hira_q8_profile_read(unsigned long long* host_out) {
     return cudaMemcpyFromSymbol(host_out, hira::g_q8_prof, sizeof(hira::g_q8_prof)) == cudaSuccess ? 0 : -1;
 }
 #endif
+
+extern "C" int hira_q8_fallback_count(uint32_t* host_out) {
+    HIRA_CHECK_ARG(host_out != nullptr, HIRA_ERR_ARG, "hira_q8_fallback_count: NULL argument");
+    unsigned int v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, hira::g_q8_fallbacks, sizeof(v));
+    if (e != cudaSuccess) {
+        hira::set_error("hira_q8_fallback_count: %s", cudaGetErrorString(e));
+        return HIRA_ERR_CUDA;
+    }
+    *host_out = v;
+    return HIRA_OK;
+}
 
 extern "C" int hira_q8_refresh(const hira_index_t* ix, void* stream) {
     int rc = hira::validate_index(ix, false);

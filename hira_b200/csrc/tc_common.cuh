@@ -27,10 +27,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 // bounded wait: false on timeout
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned long long limit = TC_WAIT_CYCLES) {
     const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity)) {
-        if ((unsigned long long)(clock64() - t0) > TC_WAIT_CYCLES) return false;
+        if ((unsigned long long)(clock64() - t0) > limit) return false;
     }
     return true;
 }

@@ -237,6 +237,16 @@ def search(st: IndexState, q: torch.Tensor, tau: torch.Tensor, *, scaling=None, 
     return out_dense, compact
 
 
+def q8_fallback_count(device=None) -> int:
+    """CTAs of the int8 pre-filter search on `device` (default: current) that took their exact fallback
+    because a bounded wait ran out, since the library was loaded (hira_q8_fallback_count; synchronises)."""
+    import ctypes as C
+    v = C.c_uint32(0)
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        L.check(L.load().hira_q8_fallback_count(C.byref(v)), "hira_q8_fallback_count")
+    return int(v.value)
+
+
 def new_stats(hq: int, device) -> torch.Tensor:
     """Zeroed traffic counters for `search(..., stats=)`: (H_q, HIRA_SEARCH_STATS) int32."""
     return torch.zeros((hq, L.SEARCH_STATS), dtype=torch.int32, device=device)

@@ -458,6 +458,14 @@ int hira_recompute_radii(const hira_index_t* index, void* stream);
  * they are stored now: after the index arrays were loaded from elsewhere. */
 int hira_q8_refresh(const hira_index_t* index, void* stream);
 
+/* Diagnostic: the number of CTAs of the int8 pre-filter search on the current
+ * device that took their exact fallback (every row of a kept parent re-scored
+ * in the index dtype) because one of their bounded waits ran out, since the
+ * library was loaded.  Results are unaffected by such an event, the search is
+ * only slower; a non-zero count explains an outlier in the step times.
+ * Synchronises the device. */
+int hira_q8_fallback_count(uint32_t* host_out);
+
 /* Gather the stored keys/values back into token order (slot2token) for a
  * rebuild: out_k [n_heads][n_out][dim]; rows of tokens not present are left
  * untouched.  token_base is subtracted from slot2token. */

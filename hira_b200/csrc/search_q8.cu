@@ -256,6 +256,7 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const uint
     int& s_ncand = misc[14];
     int& s_fail = misc[15];
     int* s_wcount = misc + 16;                                // [Q8_MAX_STAGES * 4] candidates per segment
+    int& s_stream_all = misc[48];                             // the head's streaming mode, read once for the whole CTA
     static_assert(GROUP * NCH * 8 * 4 <= 2 * MAX_TILE_ROWS, "the scanned key fits in the candidate segments' place");
 
     const int TP = P.tile_parents;
@@ -320,6 +321,10 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const uint
         s_fail = aligned ? 0 : 1;
         s_need = 0;
         s_ncand = 0;
+        // One thread reads the streaming mode for the whole CTA: the kernel that prepares the query terms
+        // (and may flip the mode word) can still be running when this CTA starts, and the producer and the
+        // workers must agree on the stages that are requested up front.
+        s_stream_all = (int)*reinterpret_cast<volatile uint32_t*>(hints + (size_t)h * HIRA_Q8_CHAN + Q8_HINT + 2);
         for (int i = 0; i < Q8_SLOTS; ++i) mbar_init(bar_full + 8 * i, 1);
         for (int i = 0; i < Q8_MAX_STAGES; ++i) mbar_init(bar_done + 8 * i, 1);
         mbar_init(bar_go, 1);
@@ -346,7 +351,7 @@ search_q8_kernel(const SearchParams P, const int8_t* __restrict__ k8, const uint
                                              : (P.tile_gp_shift == -1 ? tile * P.ng : div_bf(tile * TP, bf, P.bf_magic))) < P.used[h * 4 + 1]
                                           : tile_p0 < P.used[h * 4 + 0];
     uint32_t* hint = hints + (size_t)h * HIRA_Q8_CHAN + Q8_HINT;
-    const bool stream_all = hint[2] != 0u;
+    const bool stream_all = s_stream_all != 0;
     const int spec = tile_in_use ? ((stream_all || n_stage_tile < Q8_SLOTS) ? n_stage_tile : Q8_SLOTS) : 0;
 
     if (!worker) {

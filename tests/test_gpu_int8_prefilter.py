@@ -108,6 +108,40 @@ def test_prefilter_equals_streaming_kernel_and_oracle(h, n, bf, depth, dtype, gr
     assert total == 17 * hq and int(st.q8_chan_scale.view(torch.int32)[0, 134]) == 1
 
 
+def test_mode_flips_between_back_to_back_searches_never_cost_a_fallback():
+    """The search kernel starts while the kernel that prepares its query terms (and decides the streaming
+    mode from the last search's gates) may still be running.  Searches whose gates keep everything and
+    searches whose gates keep nothing alternate without a pause, so the mode word flips before every other
+    launch: every CTA must still agree with itself on the stages requested up front -- no bounded wait may
+    run out (no CTA takes the exact fallback), and the results are those of the streaming kernel."""
+    h, n, bf, group = 4, 32768, 32, 4
+    st, keys = _build(h, n, bf, 3, torch.bfloat16, "rope_outlier", 77)
+    hq = h * group
+    q = W.make_queries(hq, 78, "cuda", pos=n)
+    q_hat = (q / q.norm(dim=-1, keepdim=True)).contiguous()
+    scores = torch.einsum("hgd,hnd->hgn", q_hat.view(h, group, 128), keys.float()).reshape(hq, n)
+    tau_mid = W.guard_banded_tau(scores, 600)
+    tau_all = torch.full((hq,), float("-inf"), device="cuda")
+    tau_none = torch.full((hq,), float("inf"), device="cuda")
+    flags = RULES[0]
+    st.enable_int8_copy(False)
+    _, want = S.search(st, q_hat, tau_mid, flags=flags, want_compact=True)
+    want_sets = compact_sets(want)
+    st.enable_int8_copy(True)
+    before = S.q8_fallback_count()
+    compact = S.alloc_compact(st, hq)
+    other = S.alloc_compact(st, hq)
+    for i in range(40):                       # no synchronisation inside: the launches follow one another
+        S.search(st, q_hat, tau_all if i % 2 == 0 else tau_none, flags=flags, compact=other)
+        S.search(st, q_hat, tau_mid, flags=flags, compact=compact)
+    torch.cuda.synchronize()
+    assert S.q8_fallback_count() == before
+    got_sets = compact_sets(compact)
+    for qh in range(hq):
+        assert np.array_equal(got_sets[qh][0], want_sets[qh][0])
+        assert np.array_equal(got_sets[qh][1].view(np.uint32), want_sets[qh][1].view(np.uint32))
+
+
 def test_prefilter_prunes_the_exact_pass_to_a_few_per_cent():
     """On the decode workload (RoPE + outlier channels, tau at 2 %) the union of candidates over a
     group of 4 query heads stays near the union of the true survivors."""

@@ -22,7 +22,7 @@
 
 namespace hira {
 
-int q8_refresh(const hira_index_t* ix, cudaStream_t s);
+int q8_refresh(const hira_index_t* ix, cudaStream_t s, long long parents_bound);
 int launch_assign_tc(const void* points, long long p_head_stride, const void* cents, const float* csq,
                      int n_heads, int n, int k, int dim, int32_t* out_idx, float* out_d2, cudaStream_t s);
 bool assign_tc_supported(int dtype, int n, int k, int dim);
@@ -550,11 +550,12 @@ static int launch_radii(const hira_index_t* ix, cudaStream_t s) {
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void export_rows_kernel(const T* __restrict__ src, const int32_t* __restrict__ slot2token,
-                                   long long head_rows, int dim, int token_base, int n_out, T* __restrict__ dst) {
+                                   long long head_rows, long long visit_rows, int dim, int token_base, int n_out,
+                                   T* __restrict__ dst) {
     const int chunks = dim / 8;
     const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const int h = blockIdx.y;
-    if (t >= head_rows * chunks) return;
+    if (t >= visit_rows * chunks) return;
     const long long s = t / chunks;
     const int ch = (int)(t % chunks);
     const int tok = slot2token[(size_t)h * head_rows + s];
@@ -792,7 +793,8 @@ static int build_impl(const hira_index_t* ix, const void* keys_v, const void* va
     HIRA_CHECK_LAUNCH("set used launch");
     rc = launch_radii<T>(ix, s);
     if (rc != HIRA_OK) return rc;
-    return q8_refresh(ix, s);   // the int8 side copy of the children, when the index carries one
+    // the int8 side copy of the children, when the index carries one: over the slots this build filled
+    return q8_refresh(ix, s, ix->depth == 3 ? (long long)k2 * bf : (long long)k1);
 }
 
 }  // namespace hira
@@ -852,29 +854,31 @@ extern "C" int hira_export(const hira_index_t* ix, int32_t token_base, int32_t n
     HIRA_CHECK_ARG(!out_v || ix->values, HIRA_ERR_ARG, "hira_export: out_v given but the index stores no values");
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     const long long rows = (long long)ix->cap_parents * ix->bf;
+    // only the slots that can hold keys are visited (the host's bound, hira_index_t::active_parents)
+    const long long visit = (ix->active_parents > 0 ? (long long)ix->active_parents : (long long)ix->cap_parents) * ix->bf;
     {
         const int chunks = ix->dim / 8;
-        dim3 grid((unsigned)((rows * chunks + 255) / 256), (unsigned)ix->n_heads);
+        dim3 grid((unsigned)((visit * chunks + 255) / 256), (unsigned)ix->n_heads);
         if (ix->dtype == HIRA_BF16)
             export_rows_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(ix->children),
-                                                                   ix->slot2token, rows, ix->dim, token_base, n_out,
+                                                                   ix->slot2token, rows, visit, ix->dim, token_base, n_out,
                                                                    reinterpret_cast<__nv_bfloat16*>(out_k));
         else
             export_rows_kernel<float><<<grid, 256, 0, s>>>(reinterpret_cast<const float*>(ix->children), ix->slot2token,
-                                                           rows, ix->dim, token_base, n_out,
+                                                           rows, visit, ix->dim, token_base, n_out,
                                                            reinterpret_cast<float*>(out_k));
         HIRA_CHECK_LAUNCH("export keys launch");
     }
     if (out_v) {
         const int chunks = ix->vdim / 8;
-        dim3 grid((unsigned)((rows * chunks + 255) / 256), (unsigned)ix->n_heads);
+        dim3 grid((unsigned)((visit * chunks + 255) / 256), (unsigned)ix->n_heads);
         if (ix->vdtype == HIRA_BF16)
             export_rows_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(ix->values),
-                                                                   ix->slot2token, rows, ix->vdim, token_base, n_out,
+                                                                   ix->slot2token, rows, visit, ix->vdim, token_base, n_out,
                                                                    reinterpret_cast<__nv_bfloat16*>(out_v));
         else
             export_rows_kernel<float><<<grid, 256, 0, s>>>(reinterpret_cast<const float*>(ix->values), ix->slot2token,
-                                                           rows, ix->vdim, token_base, n_out,
+                                                           rows, visit, ix->vdim, token_base, n_out,
                                                            reinterpret_cast<float*>(out_v));
         HIRA_CHECK_LAUNCH("export values launch");
     }

@@ -132,7 +132,7 @@ __device__ __forceinline__ void load_row_raw(RawChunk<T> (&raw)[NCH], const T* r
 
 // set by search.cu's host code, consumed by the kernel launchers of both files
 int launch_search_q8(const SearchParams& P, const hira_index_t* ix, int max_group, cudaStream_t stream);
-int q8_refresh(const hira_index_t* ix, cudaStream_t s);
+int q8_refresh(const hira_index_t* ix, cudaStream_t s, long long parents_bound);
 bool search_q8_applicable(const hira_index_t* ix, const SearchParams& P);
 
 }  // namespace hira

@@ -959,13 +959,13 @@ __global__ void q8_chan_finish_kernel(const hira_index_t ix) {
 
 // one 8-lane group per child slot: quantise the row (see q8_write_row in common.cuh)
 template <typename T>
-__global__ void q8_quantize_kernel(const hira_index_t ix) {
+__global__ void q8_quantize_kernel(const hira_index_t ix, const size_t slots_bound) {
     const int lane = threadIdx.x & (GROUP - 1);
     const size_t capC = (size_t)ix.cap_parents * ix.bf;
-    const size_t w = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) / GROUP;   // (head, slot)
-    if (w >= (size_t)ix.n_heads * capC) return;
-    const int h = (int)(w / capC);
-    const size_t slot = w % capC;
+    const int h = blockIdx.y;
+    const size_t slot = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) / GROUP;
+    if (slot >= slots_bound) return;
+    const size_t w = (size_t)h * capC + slot;   // (head, slot)
     // slots beyond the blocks in use hold no keys (and never did since the last clear): nothing to write
     const size_t in_use = (size_t)(ix.depth == 3 ? ix.used[h * 4 + 1] * ix.bf : ix.used[h * 4 + 0]) * ix.bf;
     if (slot >= in_use) return;
@@ -976,22 +976,24 @@ __global__ void q8_quantize_kernel(const hira_index_t ix) {
                  reinterpret_cast<uint32_t*>(ix.children_q8_meta) + w, (int)(slot & 7), lane);
 }
 
-int q8_refresh(const hira_index_t* ix, cudaStream_t s) {
+// parents_bound: parent slots that can hold keys (0 = the whole capacity); the grid covers only those
+int q8_refresh(const hira_index_t* ix, cudaStream_t s, long long parents_bound) {
     if (!ix->children_q8) return HIRA_OK;
     HIRA_CHECK_ARG(ix->dim == Q8_DIM && ix->children_q8_meta && ix->q8_chan_scale, HIRA_ERR_ARG,
                    "the int8 side copy needs dim == 128 and its meta / channel-scale arrays");
-    const size_t rows = (size_t)ix->n_heads * ix->cap_parents * ix->bf;
-    const unsigned blocks = (unsigned)((rows * GROUP + 255) / 256);
+    if (parents_bound <= 0 || parents_bound > ix->cap_parents) parents_bound = ix->cap_parents;
+    const size_t slots_bound = (size_t)parents_bound * ix->bf;
+    const dim3 blocks((unsigned)((slots_bound * GROUP + 255) / 256), (unsigned)ix->n_heads);
     cudaMemsetAsync(ix->q8_chan_scale, 0, (size_t)ix->n_heads * HIRA_Q8_CHAN * sizeof(float), s);
     const dim3 parts(Q8_CHAN_PARTS, (unsigned)ix->n_heads);
     if (ix->dtype == HIRA_BF16) {
         q8_chan_sums_kernel<__nv_bfloat16><<<parts, Q8_DIM, 0, s>>>(*ix);
         q8_chan_finish_kernel<<<ix->n_heads, Q8_DIM, 0, s>>>(*ix);
-        q8_quantize_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(*ix);
+        q8_quantize_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(*ix, slots_bound);
     } else {
         q8_chan_sums_kernel<float><<<parts, Q8_DIM, 0, s>>>(*ix);
         q8_chan_finish_kernel<<<ix->n_heads, Q8_DIM, 0, s>>>(*ix);
-        q8_quantize_kernel<float><<<blocks, 256, 0, s>>>(*ix);
+        q8_quantize_kernel<float><<<blocks, 256, 0, s>>>(*ix, slots_bound);
     }
     HIRA_CHECK_LAUNCH("int8 side copy launch");
     return HIRA_OK;
@@ -1021,5 +1023,5 @@ extern "C" int hira_q8_refresh(const hira_index_t* ix, void* stream) {
     int rc = hira::validate_index(ix, false);
     if (rc != HIRA_OK) return rc;
     HIRA_CHECK_ARG(ix->children_q8 != nullptr, HIRA_ERR_ARG, "hira_q8_refresh: the index has no int8 side copy");
-    return hira::q8_refresh(ix, reinterpret_cast<cudaStream_t>(stream));
+    return hira::q8_refresh(ix, reinterpret_cast<cudaStream_t>(stream), ix->active_parents);
 }

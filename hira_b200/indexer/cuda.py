@@ -395,6 +395,7 @@ class CUDAIndexer(BaseIndexer):
         self.wait_pending_update() if self.state is not None else None
         st = self.state
         n = self._n_keys
+        st.active_parents = self.active_parents     # the export visits only the slots that can hold keys
         keys, values = S.export(st, n)
         self._build(keys.unsqueeze(0), None if values is None else values.unsqueeze(0), reuse=st)
         return self

@@ -455,7 +455,8 @@ int hira_build(const hira_index_t* index, const void* keys, const void* values,
 int hira_recompute_radii(const hira_index_t* index, void* stream);
 
 /* (Re)computes the int8 side copy (per-channel scales, rows, error bounds) from the children as
- * they are stored now: after the index arrays were loaded from elsewhere. */
+ * they are stored now: after the index arrays were loaded from elsewhere.  Visits the parent
+ * slots below index->active_parents (0 = all). */
 int hira_q8_refresh(const hira_index_t* index, void* stream);
 
 /* Diagnostic: the number of CTAs of the int8 pre-filter search on the current
@@ -468,7 +469,8 @@ int hira_q8_fallback_count(uint32_t* host_out);
 
 /* Gather the stored keys/values back into token order (slot2token) for a
  * rebuild: out_k [n_heads][n_out][dim]; rows of tokens not present are left
- * untouched.  token_base is subtracted from slot2token. */
+ * untouched.  token_base is subtracted from slot2token.  Visits the parent
+ * slots below index->active_parents (0 = all). */
 int hira_export(const hira_index_t* index, int32_t token_base, int32_t n_out,
                 void* out_k, void* out_v, void* stream);
 

@@ -15,6 +15,7 @@
 // for which every peer had pushed s + 1, which a peer does (stream order) after its merge of step s.
 // If a wait runs out (a peer died or never launched) the block sets *status and leaves `out` untouched.
 #include <atomic>
+#include <cstring>
 
 #include "common.cuh"
 #include "merge_row.cuh"

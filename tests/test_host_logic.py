@@ -36,6 +36,12 @@ def test_argument_errors_are_reported_without_a_gpu():
         _lib.check(rc, "hira_search")
     assert lib.hira_build_workspace_bytes(ctypes.byref(ix), 10) == 0
     assert lib.hira_attn_default_splits(512, 128) >= 1
+    # the peer exchange: buffer size = 2 parities x world x heads x ((2 + V) floats + one flag); host-side refusals
+    assert lib.hira_exchange_bytes(8, 64, 128) == 2 * 8 * 64 * ((128 + 2) * 4 + 4)
+    assert lib.hira_exchange_bytes(0, 64, 128) == 0
+    rc = lib.hira_exchange_merge(None, None, 2, 0, 8, 64, 1, 3, 0.0, None, None, None, None)
+    assert rc == _lib.HIRA_ERR_ARG and b"NULL" in lib.hira_last_error()
+    assert lib.hira_q8_fallback_count(None) == _lib.HIRA_ERR_ARG
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

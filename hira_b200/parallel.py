@@ -82,7 +82,11 @@ class PeerPartialsExchange:
     `local_ml`, `all_gather()` is a no-op, `merge(out=)` runs the fused step.
 
     peers=... (a list of already mapped buffer addresses with this rank's own at [rank]) skips the
-    IPC set-up: several emulated ranks of one process on one GPU, driven with `phases`."""
+    IPC set-up: several emulated ranks of one process on one GPU, driven with `phases`.
+
+    The step number is an argument of the launch: a step recorded into a CUDA graph carries its number
+    with it, so such a graph can be replayed once per recording, not over and over (the peers' flags would
+    already hold that number)."""
 
     def __init__(self, n_qheads: int, vdim: int, device, group=None, *, rank: Optional[int] = None,
                  world: Optional[int] = None, peers=None, wait_seconds: float = 2.0):

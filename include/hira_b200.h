@@ -243,7 +243,9 @@ int hira_merge_partials(const float* part_o, const float* part_ml,
  *   peer_bufs  HOST array of `world` device pointers: entry r is rank r's
  *              exchange buffer as mapped in THIS process (entry `rank` is the
  *              pointer hira_peer_alloc returned)
- *   seq        step number, the same on every rank, never 0, +1 per step
+ *   seq        step number, the same on every rank, never 0, +1 per step (a
+ *              launch argument: a captured step carries its number, so a graph
+ *              holding this call is good for one replay per recording)
  *   phases     3 = push this rank's rows to every peer, wait for every
  *              source's rows, merge (the decode step); 1 = push only,
  *              2 = wait + merge only (for drivers that run several ranks'
